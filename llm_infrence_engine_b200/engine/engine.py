@@ -1,0 +1,210 @@
+"""The engine: a model folder in, generated tokens out, with the reference's calls where it has them.
+
+``Engine.add_request`` / ``step`` / ``has_work`` / ``run_until_idle`` / ``cancel`` / ``stats`` follow
+src/miniserve/engine.py:143-205 and src/miniserve/paged_engine.py:57-80; ``Engine.generate`` and the
+module-level ``generate`` take the options of src/miniserve/generate.py:85-96 and return its
+``GenerationResult``. Below the surface nothing is the reference's: one step function runs prompt
+portions and decoded tokens together, and the pages, slots and decisions are in
+``cache.CacheManager`` and ``engine.Scheduler``.
+"""
+from __future__ import annotations
+
+import json
+import time
+from pathlib import Path
+from typing import Callable, List, Optional, Sequence, Union
+
+import torch
+
+from ..cache.manager import CacheManager
+from ..config.engine_config import EngineConfig
+from ..config.model_config import read_config_json
+from ..models.registry import build_model_spec
+from ..models.spec import ModelSpec
+from ..sampling.sampler import Sampler, SamplingParams
+from ..weights.loader import load_weights
+from .request import GenerationResult, Request, StepRecord
+from .scheduler import Scheduler, StepPlan
+from .step import ModelRunner, StepEntry, group_layout
+
+_TORCH_DTYPE = {"bfloat16": torch.bfloat16, "float32": torch.float32}
+
+
+def build_runner(folder: Union[str, Path], config: EngineConfig, kernels=None):
+    """config.json -> registry -> parts -> weights -> cache; returns (spec, cache manager, runner)."""
+    config.validate()
+    if kernels is None:
+        from ..csrc import get_kernels  # compiles at its first call; raises if there is no CUDA device or compiler
+
+        kernels = get_kernels()
+    spec = build_model_spec(read_config_json(folder))
+    dtype = _TORCH_DTYPE[config.dtype]
+    load_weights(spec, folder, dtype, config.device)
+    groups, of_entry = group_layout(spec.cache_specs())
+    num_pages = config.pool_blocks()
+    cache = CacheManager(groups, num_pages, config.block_size, config.max_seqs)
+    runner = ModelRunner(spec, kernels, cache, of_entry, dtype, config.device, num_pages, config.block_size, config.max_seqs)
+    return spec, cache, runner
+
+
+class Engine:
+    def __init__(self, model: Union[str, Path], config: Optional[EngineConfig] = None, kernels=None,
+                 on_token: Optional[Callable[[Request, int], None]] = None,
+                 on_finish: Optional[Callable[[Request], None]] = None,
+                 clock: Callable[[], float] = time.perf_counter, **overrides):
+        self.config = config or EngineConfig()
+        for k, v in overrides.items():
+            if not hasattr(self.config, k):
+                raise TypeError(f"EngineConfig has no option '{k}'")
+            setattr(self.config, k, v)
+        self.spec, self.cache, self.runner = build_runner(model, self.config, kernels)
+        self.scheduler = Scheduler(self.cache, self.config.max_seqs, self.config.max_len, self.config.max_num_batched_tokens)
+        self.sampler = Sampler(self.runner.K)
+        self.on_token, self.on_finish, self.clock = on_token, on_finish, clock
+        self.finished: List[Request] = []
+        self.steps: List[StepRecord] = []
+        self.peak_running = 0
+        self.peak_pages_in_use = 0
+        self.prefill_tokens_computed = 0
+
+    @classmethod
+    def from_pretrained(cls, model: Union[str, Path], **kw) -> "Engine":
+        return cls(model, **kw)
+
+    # ------------------------------------------------------------------ the reference's calls
+    @property
+    def waiting(self):
+        return self.scheduler.waiting
+
+    @property
+    def running(self):
+        return self.scheduler.running
+
+    @property
+    def preemptions(self) -> int:
+        return self.scheduler.preemptions
+
+    def add_request(self, req: Request) -> Request:
+        vocab = self.spec.vocab_size()
+        for t in req.prompt_ids:
+            if not 0 <= int(t) < vocab:
+                raise ValueError(f"token {t} is outside the vocabulary of {vocab}")
+        SamplingParams(req.temperature, req.top_k, req.top_p).validate()
+        self.scheduler.add(req)
+        req.arrival_time = self.clock()
+        return req
+
+    def has_work(self) -> bool:
+        return self.scheduler.has_work()
+
+    def cancel(self, req: Request) -> None:
+        """Honoured at the start of the next step (src/miniserve/engine.py:163-177)."""
+        req.cancelled = True
+
+    def run_until_idle(self) -> None:
+        while self.has_work():
+            self.step()
+
+    def step(self) -> StepRecord:
+        t0 = self.clock()
+        plan = self.scheduler.schedule()
+        now = self.clock()
+        for r in plan.aborted:
+            r.finish_reason, r.finish_time = "abort", now
+            if self.on_finish:
+                self.on_finish(r)
+        useful = 0
+        if plan.items:
+            entries = []
+            for s in plan.items:
+                ids = s.req.all_ids[s.start:s.start + s.count]
+                if s.req.admitted_time is None:
+                    s.req.admitted_time = now
+                entries.append(StepEntry(s.req.id, ids, s.start, (s.count - 1,) if s.samples else ()))
+            logits = self.runner.step(entries)
+            self.scheduler.advance(plan)
+            rows = [s.req for s in plan.items if s.samples]
+            if rows:
+                params = [SamplingParams(r.temperature, r.top_k, r.top_p, self._seed(r)) for r in rows]
+                tokens = self.sampler.sample(logits, params, [len(r.output_ids) for r in rows])
+                for r, tok in zip(rows, tokens):
+                    self._emit(r, int(tok))
+                    useful += 1
+        decode = sum(1 for s in plan.items if s.count == 1 and s.start > 0)
+        n_tok = plan.num_tokens
+        self.prefill_tokens_computed += n_tok - decode
+        self.peak_running = max(self.peak_running, len(self.scheduler.running))
+        if self.cache.pools:
+            self.peak_pages_in_use = max(self.peak_pages_in_use, max(p.capacity - p.num_free for p in self.cache.pools))
+        rec = StepRecord(plan.admitted, decode, useful, self.clock() - t0, plan.preempted, n_tok, n_tok - decode)
+        self.steps.append(rec)
+        return rec
+
+    def stats(self) -> dict:
+        """src/miniserve/paged_engine.py:68-80, without the prefix-cache figures."""
+        return {
+            "prefill_tokens_computed": self.prefill_tokens_computed,
+            "preemptions": self.preemptions,
+            "peak_running": self.peak_running,
+            "peak_blocks_in_use": self.peak_pages_in_use,
+            "pool_blocks": self.cache.pools[0].capacity if self.cache.pools else 0,
+            "pool_mib": self.runner.kv_bytes_per_token * self.config.pool_blocks() * self.config.block_size / 2**20,
+            "steps": len(self.steps),
+        }
+
+    # ------------------------------------------------------------------ internals
+    def _seed(self, r: Request) -> int:
+        return int(r.seed) if r.seed is not None else (self.config.seed * 1000003 + r.id) & ((1 << 62) - 1)
+
+    def _emit(self, req: Request, tok: int) -> None:
+        """src/miniserve/engine.py:279-291: a stop token ends the request and is not kept."""
+        now = self.clock()
+        if tok in req.eos_ids:
+            self._finish(req, "stop", now)
+            return
+        req.output_ids.append(tok)
+        req.token_times.append(now)
+        if req.first_token_time is None:
+            req.first_token_time = now
+        if self.on_token:
+            self.on_token(req, tok)
+        if len(req.output_ids) >= req.max_new_tokens:
+            self._finish(req, "length", now)
+
+    def _finish(self, req: Request, reason: str, now: float) -> None:
+        self.scheduler.finish(req)
+        req.finish_reason, req.finish_time = reason, now
+        self.finished.append(req)
+        if self.on_finish:
+            self.on_finish(req)
+
+    # ------------------------------------------------------------------ the Python entry point
+    def generate(self, prompts: Union[Sequence[int], Sequence[Sequence[int]]], max_new_tokens: int = 64,
+                 eos_ids: Sequence[int] = (), temperature: float = 0.0, top_k: int = 0, top_p: float = 1.0,
+                 seed: Optional[int] = None) -> Union[GenerationResult, List[GenerationResult]]:
+        """Generate for one prompt (a list of token ids) or for several at once (a list of lists).
+
+        Options as src/miniserve/generate.py:85-96. Several prompts run together under the scheduler;
+        each result is what the prompt would give alone.
+        """
+        single = len(prompts) > 0 and not isinstance(prompts[0], (list, tuple))
+        batch = [list(prompts)] if single else [list(p) for p in prompts]
+        t0 = self.clock()
+        reqs = [self.add_request(Request(p, max_new_tokens, tuple(eos_ids), temperature, top_k, top_p,
+                                         None if seed is None else seed + i)) for i, p in enumerate(batch)]
+        while any(r.state != "finished" for r in reqs):
+            self.step()
+        total = self.clock() - t0
+        out = []
+        for r in reqs:
+            times = [b - a for a, b in zip(r.token_times, r.token_times[1:])]
+            out.append(GenerationResult(r.output_ids, len(r.prompt_ids), (r.first_token_time or self.clock()) - t0, total,
+                                        times, r.finish_reason or "length",
+                                        self.runner.kv_bytes_per_token * (len(r.prompt_ids) + len(r.output_ids))))
+        return out[0] if single else out
+
+
+def generate(engine: Engine, prompt_ids: Sequence[int], max_new_tokens: int = 64, eos_ids: Sequence[int] = (),
+             temperature: float = 0.0, top_k: int = 0, top_p: float = 1.0, seed: Optional[int] = None) -> GenerationResult:
+    """The reference's ``generate(model, prompt_ids, ...)`` (src/miniserve/generate.py:85) with an engine in the model's place."""
+    return engine.generate(list(prompt_ids), max_new_tokens, eos_ids, temperature, top_k, top_p, seed)

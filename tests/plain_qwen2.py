@@ -184,16 +184,19 @@ def plain_uniform(seed: int, counter: int) -> float:
     return (z >> 40) / float(1 << 24)
 
 
-def plain_sample(logits: torch.Tensor, temperature: float, top_k: int, top_p: float, seed: int, counter: int) -> int:
+def plain_draw(logits: torch.Tensor, temperature: float, top_k: int, top_p: float, u: float) -> int:
     """sampler.py:44-55 with the draw by inverse CDF in index order: the first token whose running mass exceeds u."""
     if temperature <= 0.0:  # sampler.py:52-53
         return int(logits.argmax(-1))
     probs = plain_logits_to_probs(logits, temperature, top_k, top_p).double()
-    u = plain_uniform(seed, counter) * float(probs.sum())
     cdf = probs.cumsum(-1)
-    idx = int(torch.searchsorted(cdf, torch.tensor(u, dtype=torch.float64), right=True))
+    idx = int(torch.searchsorted(cdf, torch.tensor(u * float(cdf[-1]), dtype=torch.float64), right=True))
     keep = torch.nonzero(probs > 0).flatten()
     return min(max(idx, int(keep[0])), int(keep[-1]))
+
+
+def plain_sample(logits: torch.Tensor, temperature: float, top_k: int, top_p: float, seed: int, counter: int) -> int:
+    return plain_draw(logits, temperature, top_k, top_p, plain_uniform(seed, counter))
 
 
 # ----------------------------------------------------------------------------- generation

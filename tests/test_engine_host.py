@@ -1,0 +1,85 @@
+"""The host side of the engine on the CPU: step building, block tables, pages that are used again,
+scheduler and entry point, with the kernels replaced by their plain torch statements
+(tests/torch_kernels.py). What the CUDA kernels compute is checked by the gpu tests."""
+import pytest
+import torch
+
+from helpers import cut, make_model_folder, random_prompt
+from plain_qwen2 import plain_forward, plain_generate, plain_load
+from tiny_configs import CONFIGS, PAGE_SIZES
+from torch_kernels import TorchKernels
+
+from llm_infrence_engine_b200.engine import Engine, Request, TraceReplayer
+
+TOL = 2e-5
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    tmp = tmp_path_factory.mktemp("models")
+    return {n: make_model_folder(tmp, n) for n in CONFIGS}
+
+
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_replay_cuts_match_plain(folders, name):
+    cfg, w = plain_load(folders[name])
+    vocab = cfg["vocab_size"]
+    prompts = {"a": random_prompt(vocab, 70, 1), "b": random_prompt(vocab, 45, 2), "c": random_prompt(vocab, 33, 3)}
+    want = {k: plain_forward(cfg, w, p) for k, p in prompts.items()}
+    rp = TraceReplayer(str(folders[name]), "float32", 192, device="cpu", kernels=TorchKernels(), block_size=PAGE_SIZES[name])
+    # whole
+    for k, p in prompts.items():
+        got = rp.step({"step": 0, "entries": [{"id": k, "tokens": p, "want": list(range(len(p)))}], "end": [k]})
+        assert (got - want[k]).abs().max() < TOL
+        rp.cache.check_invariants()
+    # portions of changing size, two requests interleaved, a third joining on pages given back
+    live = {"a": cut(70, [16, 5, 2, 9]), "b": cut(45, [2, 7, 30])}
+    step = 0
+    got = {k: [] for k in prompts}
+    while live:
+        entries = []
+        for k in list(live):
+            lo, hi = live[k].pop(0)
+            entries.append({"id": k, "tokens": prompts[k][lo:hi], "want": list(range(hi - lo))})
+        end = [k for k in live if not live[k]]
+        out = rp.step({"step": step, "entries": entries, "end": end})
+        o = 0
+        for e in entries:
+            n = len(e["tokens"])
+            got[e["id"]].append(out[o:o + n]); o += n
+        for k in end:
+            del live[k]
+            if k == "b":
+                live["c"] = cut(33, [1, 1, 31])
+        rp.cache.check_invariants()
+        step += 1
+    for k in prompts:
+        assert (torch.cat(got[k]) - want[k]).abs().max() < TOL, k
+    assert all(p.num_free == p.capacity for p in rp.cache.pools)
+
+
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_engine_greedy_matches_plain(folders, name):
+    cfg, w = plain_load(folders[name])
+    vocab = cfg["vocab_size"]
+    prompts = [random_prompt(vocab, n, 10 + n) for n in (1, 7, 19, 33)]
+    eng = Engine(str(folders[name]), dtype="float32", device="cpu", kernels=TorchKernels(), block_size=PAGE_SIZES[name],
+                 num_blocks=14, max_seqs=3, max_len=64, max_num_batched_tokens=24)
+    reqs = [eng.add_request(Request(p, max_new_tokens=8)) for p in prompts]
+    while eng.has_work():
+        eng.step()
+        eng.cache.check_invariants()
+    for r, p in zip(reqs, prompts):
+        assert r.output_ids == plain_generate(cfg, w, p, 8), (name, len(p))
+    assert all(pool.num_free == pool.capacity for pool in eng.cache.pools)
+    assert eng.cache.num_free_slots() == 3
+
+
+def test_engine_sampled_matches_plain(folders):
+    cfg, w = plain_load(folders["B"])
+    prompts = [random_prompt(320, n, 20 + n) for n in (3, 12, 40)]
+    eng = Engine(str(folders["B"]), dtype="float32", device="cpu", kernels=TorchKernels(), block_size=8,
+                 num_blocks=40, max_seqs=4, max_len=128, max_num_batched_tokens=16)
+    res = eng.generate(prompts, max_new_tokens=6, temperature=0.8, top_k=50, top_p=0.95, seed=7)
+    for i, (r, p) in enumerate(zip(res, prompts)):
+        assert r.token_ids == plain_generate(cfg, w, p, 6, temperature=0.8, top_k=50, top_p=0.95, seed=7 + i)
