@@ -1,0 +1,160 @@
+// Embedding, rotary tables, residual add + RMS norm, QKV bias + rotation + cache write, SiLU * up.
+// Every kernel takes its sizes as arguments; T is the compute dtype (float or bfloat16). The
+// residual stream, the norms' reductions, the rotation angles and the activation are 32-bit.
+#include "common.cuh"
+
+// ------------------------------------------------------------------------------------------------
+// x[n, :] = table[ids[n], :]  widened to float (the residual stream)
+template <typename T>
+__global__ void embed_kernel(const int* __restrict__ ids, const T* __restrict__ table, float* __restrict__ out, int H) {
+    const int n = blockIdx.x;
+    const T* row = table + (size_t)ids[n] * H;
+    float* o = out + (size_t)n * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = to_f32(row[i]);
+}
+
+LLMIE_API int llmie_embed(const int* ids, const void* table, float* out, int N, int H, int dtype, cudaStream_t s) {
+    if (N <= 0) return 0;
+    const int threads = H >= 1024 ? 256 : 128;
+    if (dtype == DT_F32) embed_kernel<float><<<N, threads, 0, s>>>(ids, (const float*)table, out, H);
+    else embed_kernel<bf16><<<N, threads, 0, s>>>(ids, (const bf16*)table, out, H);
+    return launch_status();
+}
+
+// ------------------------------------------------------------------------------------------------
+// cos/sin[n, j] of the angle float(position[n]) * inv_freq[j], all in 32-bit
+__global__ void rope_tables_kernel(const int* __restrict__ pos, const float* __restrict__ inv_freq, float* __restrict__ cos_out,
+                                   float* __restrict__ sin_out, int N, int half) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= N * half) return;
+    const int n = i / half, j = i % half;
+    const float ang = __int2float_rn(pos[n]) * inv_freq[j];
+    cos_out[i] = cosf(ang);
+    sin_out[i] = sinf(ang);
+}
+
+LLMIE_API int llmie_rope_tables(const int* pos, const float* inv_freq, float* cos_out, float* sin_out, int N, int half,
+                                cudaStream_t s) {
+    if (N <= 0) return 0;
+    const int total = N * half;
+    rope_tables_kernel<<<(total + 127) / 128, 128, 0, s>>>(pos, inv_freq, cos_out, sin_out, N, half);
+    return launch_status();
+}
+
+// ------------------------------------------------------------------------------------------------
+// One block per output row.
+//   rows == nullptr: r = blockIdx.x; residual[r] += delta[r] (stored); out[r] = norm(residual[r])
+//   rows != nullptr: r = rows[blockIdx.x]; out[blockIdx.x] = norm(residual[r] + delta[r]); residual untouched
+// norm(x) = weight * T(x / sqrt(mean(x^2) + eps)), the mean and the scaling in 32-bit.
+template <typename T>
+__global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __restrict__ delta, const float* __restrict__ weight,
+                                   T* __restrict__ out, const int* __restrict__ rows, int H, float eps) {
+    extern __shared__ float row_buf[];  // H floats, then 33 for the reduction
+    float* scratch = row_buf + H;
+    const int r = rows ? rows[blockIdx.x] : blockIdx.x;
+    float* x = residual + (size_t)r * H;
+    const T* d = delta ? delta + (size_t)r * H : nullptr;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float v = x[i];
+        if (d) v += to_f32(d[i]);
+        row_buf[i] = v;
+        if (d && !rows) x[i] = v;
+        ss += v * v;
+    }
+    ss = block_sum(ss, scratch);
+    const float rstd = 1.0f / sqrtf(ss / (float)H + eps);
+    T* o = out + (size_t)blockIdx.x * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = from_f32<T>(weight[i] * round_through<T>(row_buf[i] * rstd));
+}
+
+LLMIE_API int llmie_add_rmsnorm(float* residual, const void* delta, const float* weight, void* out, const int* rows,
+                                int n_out, int H, float eps, int dtype, cudaStream_t s) {
+    if (n_out <= 0) return 0;
+    const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+    const size_t smem = (size_t)(H + 33) * sizeof(float);
+    if (smem > 200 * 1024) return LLMIE_ERR_BAD_ARGUMENT;
+    if (dtype == DT_F32) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(add_rmsnorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        add_rmsnorm_kernel<float><<<n_out, threads, smem, s>>>(residual, (const float*)delta, weight, (float*)out, rows, H, eps);
+    } else {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(add_rmsnorm_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        add_rmsnorm_kernel<bf16><<<n_out, threads, smem, s>>>(residual, (const bf16*)delta, weight, (bf16*)out, rows, H, eps);
+    }
+    return launch_status();
+}
+
+// ------------------------------------------------------------------------------------------------
+// qkv[n] is [num_heads + 2 num_kv_heads][d]. Adds the bias, rotates the query and key heads by the
+// token's angle (pairs (j, j + d/2)), writes everything back in place and, if asked, copies the key
+// and value heads into the token's cache slot: pool[page][kv head][offset][d], slot = page * page_size + offset.
+template <typename T>
+__global__ void rope_kv_write_kernel(T* __restrict__ qkv, const float* __restrict__ bias, const float* __restrict__ cos_t,
+                                     const float* __restrict__ sin_t, const int* __restrict__ slots, T* __restrict__ k_pool,
+                                     T* __restrict__ v_pool, int nq, int nkv, int d, int page_size, int write_kv) {
+    const int n = blockIdx.x;
+    const int half = d >> 1;
+    const int heads = nq + 2 * nkv;
+    T* row = qkv + (size_t)n * heads * d;
+    const float* c = cos_t + (size_t)n * half;
+    const float* sn = sin_t + (size_t)n * half;
+    const int slot = write_kv ? slots[n] : -1;
+    const int page = slot >= 0 ? slot / page_size : 0, off = slot >= 0 ? slot % page_size : 0;
+    for (int i = threadIdx.x; i < heads * half; i += blockDim.x) {
+        const int h = i / half, j = i % half;
+        const int a = h * d + j, b = a + half;
+        float x1 = to_f32(row[a]), x2 = to_f32(row[b]);
+        if (bias) { x1 += bias[a]; x2 += bias[b]; }
+        float y1 = x1, y2 = x2;
+        if (h < nq + nkv) {
+            y1 = x1 * c[j] - x2 * sn[j];
+            y2 = x2 * c[j] + x1 * sn[j];
+        }
+        const T o1 = from_f32<T>(y1), o2 = from_f32<T>(y2);
+        row[a] = o1;
+        row[b] = o2;
+        if (slot >= 0 && h >= nq) {
+            const int kvh = h < nq + nkv ? h - nq : h - nq - nkv;
+            T* pool = h < nq + nkv ? k_pool : v_pool;
+            T* dst = pool + (((size_t)page * nkv + kvh) * page_size + off) * d;
+            dst[j] = o1;
+            dst[j + half] = o2;
+        }
+    }
+}
+
+LLMIE_API int llmie_rope_kv_write(void* qkv, const float* bias, const float* cos_t, const float* sin_t, const int* slots,
+                                  void* k_pool, void* v_pool, int N, int nq, int nkv, int d, int page_size, int write_kv,
+                                  int dtype, cudaStream_t s) {
+    if (N <= 0) return 0;
+    if (d <= 0 || (d & 1) || page_size <= 0) return LLMIE_ERR_BAD_ARGUMENT;
+    const int work = (nq + 2 * nkv) * (d / 2);
+    const int threads = work >= 512 ? 256 : 128;
+    if (dtype == DT_F32)
+        rope_kv_write_kernel<float><<<N, threads, 0, s>>>((float*)qkv, bias, cos_t, sin_t, slots, (float*)k_pool, (float*)v_pool,
+                                                          nq, nkv, d, page_size, write_kv);
+    else
+        rope_kv_write_kernel<bf16><<<N, threads, 0, s>>>((bf16*)qkv, bias, cos_t, sin_t, slots, (bf16*)k_pool, (bf16*)v_pool, nq,
+                                                         nkv, d, page_size, write_kv);
+    return launch_status();
+}
+
+// ------------------------------------------------------------------------------------------------
+// out[n, i] = silu(gu[n, i]) * gu[n, I + i], silu(z) = z / (1 + exp(-z)) in 32-bit
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int N, int I) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (size_t)N * I) return;
+    const size_t n = idx / I, i = idx % I;
+    const float g = to_f32(gu[n * 2 * I + i]), u = to_f32(gu[n * 2 * I + I + i]);
+    out[idx] = from_f32<T>(g / (1.0f + expf(-g)) * u);
+}
+
+LLMIE_API int llmie_silu_mul(const void* gu, void* out, int N, int I, int dtype, cudaStream_t s) {
+    if (N <= 0) return 0;
+    const size_t total = (size_t)N * I;
+    const int blocks = (int)((total + 255) / 256);
+    if (dtype == DT_F32) silu_mul_kernel<float><<<blocks, 256, 0, s>>>((const float*)gu, (float*)out, N, I);
+    else silu_mul_kernel<bf16><<<blocks, 256, 0, s>>>((const bf16*)gu, (bf16*)out, N, I);
+    return launch_status();
+}

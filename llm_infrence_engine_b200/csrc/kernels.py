@@ -1,0 +1,249 @@
+"""The Python face of the CUDA kernels: argument checks, output allocation, launches on torch's current stream.
+
+Every method checks what the kernel cannot (device, dtype, contiguity, sizes the kernel refuses)
+and raises a clear error instead of launching; a wrong result is never an option. The kernels are
+the package's only implementation of these operations: if the library cannot be built or there is
+no CUDA device, ``get_kernels`` raises.
+
+Matrix products: in float32 always the package's own CUDA-core kernel (true 32-bit multiply-add in
+one fixed order). In bfloat16 the product goes to cuBLAS through ``torch.matmul`` where the
+reference's engine also uses the library (its ``nn.Linear`` calls, src/miniserve/model.py:108-111,
+160-162,204), except for the 32-bit logits of the output head, which the package's own kernel
+produces from bfloat16 inputs with a 32-bit accumulator.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from .build import load_library
+
+_DT = {torch.float32: 0, torch.bfloat16: 1}
+_ERR_BAD_ARGUMENT = 100001
+NUM_SMS_FALLBACK = 148
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+class CudaKernels:
+    name = "cuda-sm100a"
+
+    def __init__(self):
+        if not torch.cuda.is_available():
+            raise KernelError("no CUDA device: the kernels of this package run on a GPU only")
+        self.lib = load_library()
+        self.launches = 0
+        self.use_cublas = True
+        self._attn_scratch: Optional[torch.Tensor] = None
+        self.num_sms = torch.cuda.get_device_properties(0).multi_processor_count or NUM_SMS_FALLBACK
+        for fn in ("llmie_embed", "llmie_rope_tables", "llmie_add_rmsnorm", "llmie_rope_kv_write", "llmie_silu_mul",
+                   "llmie_gemm_simt", "llmie_paged_attention_f32", "llmie_paged_attention_bf16", "llmie_argmax", "llmie_sample"):
+            getattr(self.lib, fn).restype = ctypes.c_int
+
+    # ------------------------------------------------------------------ helpers
+    @staticmethod
+    def _stream():
+        return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def _check(self, rc: int, what: str) -> None:
+        self.launches += 1
+        if rc == 0:
+            return
+        if rc == _ERR_BAD_ARGUMENT:
+            raise KernelError(f"{what}: the kernel refused its arguments")
+        raise KernelError(f"{what}: CUDA error {rc}")
+
+    @staticmethod
+    def _need(t: torch.Tensor, name: str, dtype=None, dims: Optional[int] = None) -> None:
+        if not t.is_cuda:
+            raise KernelError(f"{name} must be on a CUDA device")
+        if not t.is_contiguous():
+            raise KernelError(f"{name} must be contiguous")
+        if dtype is not None and t.dtype != dtype:
+            raise KernelError(f"{name} must be {dtype}, got {t.dtype}")
+        if dims is not None and t.dim() != dims:
+            raise KernelError(f"{name} must have {dims} dimensions, got {t.dim()}")
+
+    @staticmethod
+    def _dt(t: torch.Tensor, name: str) -> int:
+        if t.dtype not in _DT:
+            raise KernelError(f"{name} must be float32 or bfloat16, got {t.dtype}")
+        return _DT[t.dtype]
+
+    # ------------------------------------------------------------------ kernels
+    def embed(self, token_ids, table):
+        self._need(token_ids, "token_ids", torch.int32, 1)
+        self._need(table, "table", None, 2)
+        N, H = token_ids.shape[0], table.shape[1]
+        out = torch.empty((N, H), dtype=torch.float32, device=table.device)
+        self._check(self.lib.llmie_embed(_ptr(token_ids), _ptr(table), _ptr(out), N, H, self._dt(table, "table"), self._stream()),
+                    "embed")
+        return out
+
+    def rope_tables(self, positions, inv_freq):
+        self._need(positions, "positions", torch.int32, 1)
+        self._need(inv_freq, "inv_freq", torch.float32, 1)
+        N, half = positions.shape[0], inv_freq.shape[0]
+        cos = torch.empty((N, half), dtype=torch.float32, device=positions.device)
+        sin = torch.empty_like(cos)
+        self._check(self.lib.llmie_rope_tables(_ptr(positions), _ptr(inv_freq), _ptr(cos), _ptr(sin), N, half, self._stream()),
+                    "rope_tables")
+        return cos, sin
+
+    def _norm(self, residual, delta, weight, eps, rows, out_dtype, what):
+        self._need(residual, "residual", torch.float32, 2)
+        self._need(weight, "weight", torch.float32, 1)
+        H = residual.shape[1]
+        if weight.shape[0] != H:
+            raise KernelError(f"{what}: weight has {weight.shape[0]} elements, rows have {H}")
+        if delta is not None:
+            self._need(delta, "delta", out_dtype, 2)
+            if delta.shape != residual.shape:
+                raise KernelError(f"{what}: delta is {list(delta.shape)}, residual is {list(residual.shape)}")
+        if H > 50000:
+            raise KernelError(f"{what}: rows of {H} elements do not fit the kernel's shared memory (at most 50000)")
+        n_out = residual.shape[0] if rows is None else rows.shape[0]
+        if rows is not None:
+            self._need(rows, "rows", torch.int32, 1)
+        out = torch.empty((n_out, H), dtype=out_dtype, device=residual.device)
+        self._check(self.lib.llmie_add_rmsnorm(_ptr(residual), _ptr(delta), _ptr(weight), _ptr(out), _ptr(rows), n_out, H,
+                                               ctypes.c_float(eps), _DT[out_dtype], self._stream()), what)
+        return out
+
+    def add_rmsnorm(self, residual, delta, weight, eps, out_dtype):
+        return self._norm(residual, delta, weight, eps, None, out_dtype, "add_rmsnorm")
+
+    def rmsnorm_rows(self, residual, delta, weight, eps, rows, out_dtype):
+        return self._norm(residual, delta, weight, eps, rows, out_dtype, "rmsnorm_rows")
+
+    def linear(self, x, w, out_dtype=None):
+        self._need(x, "x", None, 2)
+        self._need(w, "w", x.dtype, 2)
+        if x.shape[1] != w.shape[1]:
+            raise KernelError(f"linear: x has {x.shape[1]} columns, w has {w.shape[1]}")
+        out_dtype = out_dtype or x.dtype
+        M, K, N = x.shape[0], x.shape[1], w.shape[0]
+        if self.use_cublas and x.dtype == torch.bfloat16 and out_dtype == torch.bfloat16:
+            self.launches += 1
+            return torch.matmul(x, w.t())
+        out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+        self._check(self.lib.llmie_gemm_simt(_ptr(x), _ptr(w), _ptr(out), M, N, K, self._dt(x, "x"), self._dt(out, "out"),
+                                             self._stream()), "linear")
+        return out
+
+    def rope_kv_write(self, qkv, bias, cos, sin, slot_mapping, k_pool, v_pool, num_heads, num_kv_heads, head_dim, page_size,
+                      write_kv=True):
+        self._need(qkv, "qkv", None, 2)
+        N = qkv.shape[0]
+        heads = num_heads + 2 * num_kv_heads
+        if qkv.shape[1] != heads * head_dim:
+            raise KernelError(f"rope_kv_write: qkv rows have {qkv.shape[1]} elements, the head counts need {heads * head_dim}")
+        if head_dim % 2:
+            raise KernelError(f"rope_kv_write: head_dim {head_dim} must be even")
+        self._need(cos, "cos", torch.float32, 2)
+        self._need(sin, "sin", torch.float32, 2)
+        if tuple(cos.shape) != (N, head_dim // 2) or tuple(sin.shape) != (N, head_dim // 2):
+            raise KernelError("rope_kv_write: cos and sin must be [tokens, head_dim / 2]")
+        if bias is not None:
+            self._need(bias, "bias", torch.float32, 1)
+            if bias.shape[0] != heads * head_dim:
+                raise KernelError("rope_kv_write: bias does not match the projection's width")
+        if write_kv:
+            self._need(slot_mapping, "slot_mapping", torch.int32, 1)
+            for name, pool in (("k_pool", k_pool), ("v_pool", v_pool)):
+                self._need(pool, name, qkv.dtype, 4)
+                if tuple(pool.shape[1:]) != (num_kv_heads, page_size, head_dim):
+                    raise KernelError(f"rope_kv_write: {name} is {list(pool.shape)}, expected [pages, {num_kv_heads}, {page_size}, {head_dim}]")
+        self._check(self.lib.llmie_rope_kv_write(_ptr(qkv), _ptr(bias), _ptr(cos), _ptr(sin), _ptr(slot_mapping), _ptr(k_pool),
+                                                 _ptr(v_pool), N, num_heads, num_kv_heads, head_dim, page_size, int(bool(write_kv)),
+                                                 self._dt(qkv, "qkv"), self._stream()), "rope_kv_write")
+
+    def attention_splits(self, num_tokens: int, num_kv_heads: int, max_context: int) -> int:
+        """Slices of the keys per token: enough blocks to fill the device, at least 256 keys each."""
+        blocks = max(1, num_tokens * num_kv_heads)
+        want = -(-4 * self.num_sms // blocks)
+        return max(1, min(want, -(-max_context // 256), 64))
+
+    def _scratch(self, floats: int, device) -> torch.Tensor:
+        if self._attn_scratch is None or self._attn_scratch.numel() < floats or self._attn_scratch.device != device:
+            self._attn_scratch = torch.empty(max(floats, 1 << 20), dtype=torch.float32, device=device)
+        return self._attn_scratch
+
+    def paged_attention(self, qkv, k_pool, v_pool, block_table, token_seq, positions, num_heads, num_kv_heads, head_dim,
+                        page_size, scale, window, max_context, num_splits=None):
+        self._need(qkv, "qkv", None, 2)
+        dt = self._dt(qkv, "qkv")
+        N = qkv.shape[0]
+        vec = 4 if dt == 0 else 8
+        if head_dim % vec or head_dim > 256:
+            raise KernelError(f"paged_attention: head_dim {head_dim} must be a multiple of {vec} and at most 256")
+        if num_heads % num_kv_heads:
+            raise KernelError("paged_attention: the query heads must be a multiple of the key/value heads")
+        if qkv.shape[1] < num_heads * head_dim or qkv.shape[1] % vec:
+            raise KernelError("paged_attention: qkv rows are too short for the query heads")
+        for name, pool in (("k_pool", k_pool), ("v_pool", v_pool)):
+            self._need(pool, name, qkv.dtype, 4)
+            if tuple(pool.shape[1:]) != (num_kv_heads, page_size, head_dim):
+                raise KernelError(f"paged_attention: {name} is {list(pool.shape)}, expected [pages, {num_kv_heads}, {page_size}, {head_dim}]")
+        self._need(block_table, "block_table", torch.int32, 2)
+        self._need(token_seq, "token_seq", torch.int32, 1)
+        self._need(positions, "positions", torch.int32, 1)
+        if block_table.shape[1] * page_size < max_context:
+            raise KernelError(f"paged_attention: block tables of {block_table.shape[1]} pages cannot hold {max_context} tokens")
+        splits = num_splits or self.attention_splits(N, num_kv_heads, min(max_context, window) if window else max_context)
+        out = torch.empty((N, num_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
+        scratch = self._scratch(N * num_heads * splits * (head_dim + 2), qkv.device) if splits > 1 else None
+        fn = self.lib.llmie_paged_attention_f32 if dt == 0 else self.lib.llmie_paged_attention_bf16
+        self._check(fn(_ptr(qkv), qkv.shape[1], _ptr(k_pool), _ptr(v_pool), _ptr(block_table), block_table.shape[1],
+                       _ptr(token_seq), _ptr(positions), _ptr(out), _ptr(scratch), N, num_heads, num_kv_heads, head_dim, page_size,
+                       ctypes.c_float(scale), int(window), splits, self._stream()), "paged_attention")
+        if splits > 1:
+            self.launches += 1
+        return out
+
+    def silu_mul(self, gu):
+        self._need(gu, "gate_up", None, 2)
+        if gu.shape[1] % 2:
+            raise KernelError("silu_mul: the row must hold gate and up halves of equal width")
+        N, I = gu.shape[0], gu.shape[1] // 2
+        out = torch.empty((N, I), dtype=gu.dtype, device=gu.device)
+        self._check(self.lib.llmie_silu_mul(_ptr(gu), _ptr(out), N, I, self._dt(gu, "gate_up"), self._stream()), "silu_mul")
+        return out
+
+    def argmax(self, logits):
+        self._need(logits, "logits", torch.float32, 2)
+        M, V = logits.shape
+        out = torch.empty((M,), dtype=torch.int32, device=logits.device)
+        self._check(self.lib.llmie_argmax(_ptr(logits), _ptr(out), M, V, self._stream()), "argmax")
+        return out
+
+    def sample(self, logits, temperature, top_k, top_p, uniform):
+        self._need(logits, "logits", torch.float32, 2)
+        M, V = logits.shape
+        for name, t, dt in (("temperature", temperature, torch.float32), ("top_k", top_k, torch.int32),
+                            ("top_p", top_p, torch.float32), ("uniform", uniform, torch.float32)):
+            self._need(t, name, dt, 1)
+            if t.shape[0] != M:
+                raise KernelError(f"sample: {name} needs one value per row")
+        out = torch.empty((M,), dtype=torch.int32, device=logits.device)
+        self._check(self.lib.llmie_sample(_ptr(logits), _ptr(temperature), _ptr(top_k), _ptr(top_p), _ptr(uniform), _ptr(out), M, V,
+                                          self._stream()), "sample")
+        return out
+
+
+_kernels: Optional[CudaKernels] = None
+
+
+def get_kernels() -> CudaKernels:
+    global _kernels
+    if _kernels is None:
+        _kernels = CudaKernels()
+    return _kernels

@@ -1,0 +1,213 @@
+"""The engine on the GPU against the plain implementation, in float32 and in bfloat16: requests whole,
+the last 32 tokens one by one, portions of changing size, mixed batches on few pages, long decoding,
+the first tokens, greedy generation through the entry point, and the replay program itself."""
+import json
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+from helpers import cut, make_model_folder, random_prompt
+from plain_qwen2 import plain_forward, plain_generate, plain_load
+from tiny_configs import CONFIGS, PAGE_SIZES
+
+pytestmark = pytest.mark.gpu
+
+ROOT = Path(__file__).resolve().parent.parent
+MODES = [("float32", "float32"), ("bfloat16", "bfloat16")]
+LENS = {"a": 150, "b": 97, "c": 64, "d": 41, "e": 130}
+
+
+def tolerance(dtype: str, ref: torch.Tensor) -> float:
+    """float32: rounding of a different summation order. bfloat16: 8 bits of mantissa on every stored activation."""
+    return (2e-5 if dtype == "float32" else 3e-2) * max(1.0, ref.abs().max().item())
+
+
+@pytest.fixture(scope="module")
+def models(tmp_path_factory):
+    """Per (config, dtype): folder, config, weights as the plain side sees them, prompts and the plain logits."""
+    tmp = tmp_path_factory.mktemp("models")
+    out = {}
+    for name in CONFIGS:
+        for dtype, store in MODES:
+            folder = make_model_folder(tmp, name, store)
+            cfg, w = plain_load(folder)  # bfloat16 files are widened exactly: both sides hold the same numbers
+            prompts = {k: random_prompt(cfg["vocab_size"], n, 7 + i) for i, (k, n) in enumerate(LENS.items())}
+            want = {k: plain_forward(cfg, w, p) for k, p in prompts.items()}
+            out[(name, dtype)] = (folder, cfg, w, prompts, want)
+    return out
+
+
+def replayer(folder, name, dtype, max_tokens):
+    from llm_infrence_engine_b200.engine import TraceReplayer
+
+    return TraceReplayer(str(folder), dtype, max_tokens, block_size=PAGE_SIZES[name])
+
+
+def check(got, want, dtype, what):
+    err = (got - want).abs().max().item()
+    assert err <= tolerance(dtype, want), f"{what}: max |dlogits| {err:.3g} > {tolerance(dtype, want):.3g}"
+
+
+def first_bad(got, want, dtype):
+    bad = ((got - want).abs().max(-1).values > tolerance(dtype, want)).nonzero().flatten()
+    return int(bad[0]) if len(bad) else None
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_whole(models, name, dtype):
+    folder, cfg, w, prompts, want = models[(name, dtype)]
+    rp = replayer(folder, name, dtype, 192)
+    for i, (k, p) in enumerate(prompts.items()):
+        got = rp.step({"step": i, "entries": [{"id": k, "tokens": p, "want": list(range(len(p)))}], "end": [k]})
+        assert first_bad(got, want[k], dtype) is None, f"{k}: first wrong position {first_bad(got, want[k], dtype)}"
+        rp.cache.check_invariants()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_last_32_one_by_one(models, name, dtype):
+    folder, cfg, w, prompts, want = models[(name, dtype)]
+    rp = replayer(folder, name, dtype, 192)
+    for k, p in prompts.items():
+        n = len(p)
+        head = n - 32
+        got = [rp.step({"step": 0, "entries": [{"id": k, "tokens": p[:head], "want": list(range(head))}], "end": []})]
+        for i in range(head, n):
+            got.append(rp.step({"step": i, "entries": [{"id": k, "tokens": [p[i]], "want": [0]}], "end": [k] if i == n - 1 else []}))
+        got = torch.cat(got)
+        assert first_bad(got, want[k], dtype) is None, f"{k}: first wrong position {first_bad(got, want[k], dtype)} (decoding starts at {head})"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_portions_of_changing_size(models, name, dtype):
+    folder, cfg, w, prompts, want = models[(name, dtype)]
+    rp = replayer(folder, name, dtype, 192)
+    for sizes in ([16, 5, 2, 9], [2, 2, 33, 3, 64], [31, 1, 17]):
+        for k in ("a", "b"):
+            p = prompts[k]
+            parts = cut(len(p), sizes)
+            got = []
+            for i, (lo, hi) in enumerate(parts):
+                got.append(rp.step({"step": i, "entries": [{"id": k, "tokens": p[lo:hi], "want": list(range(hi - lo))}],
+                                    "end": [k] if hi == len(p) else []}))
+            got = torch.cat(got)
+            bad = first_bad(got, want[k], dtype)
+            assert bad is None, f"{k} cut {sizes}: first wrong position {bad}; portions {parts}"
+
+
+def mixed_trace(prompts):
+    """Up to four live requests; portions of some beside decoded tokens of others; 'e' and 'd' join late on used pages."""
+    plan = {
+        "a": cut(LENS["a"], [40, 2, 30, 1, 1, 1, 1, 50, 1, 1, 1, 21]),
+        "b": cut(LENS["b"], [1, 1, 60, 1, 1, 1, 1, 1, 30]),
+        "c": cut(LENS["c"], [64]),
+        "d": cut(LENS["d"], [2, 2, 2, 35]),
+        "e": cut(LENS["e"], [17, 64, 1, 1, 1, 46]),
+    }
+    order = ["a", "b", "c", "d", "e"]
+    waiting = list(order)
+    live, steps, step = [], [], 0
+    while waiting or live:
+        while waiting and len(live) < 4:
+            live.append(waiting.pop(0))
+        entries, end = [], []
+        for k in list(live):
+            if step % 3 == 2 and k == live[0] and len(live) > 1 and plan[k]:
+                continue  # a request sits a step out and goes on later
+            lo, hi = plan[k].pop(0)
+            entries.append({"id": k, "tokens": prompts[k][lo:hi], "want": list(range(hi - lo))})
+            if not plan[k]:
+                end.append(k)
+        steps.append({"step": step, "entries": entries, "end": end})
+        for k in end:
+            live.remove(k)
+        step += 1
+    return steps
+
+
+def run_mixed(rp, prompts):
+    got = {k: [] for k in prompts}
+    for rec in mixed_trace(prompts):
+        out = rp.step(rec)
+        o = 0
+        for e in rec["entries"]:
+            n = len(e["tokens"])
+            got[e["id"]].append(out[o:o + n])
+            o += n
+        rp.cache.check_invariants()
+    return {k: torch.cat(v) for k, v in got.items()}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_mixed_on_few_pages(models, name, dtype):
+    folder, cfg, w, prompts, want = models[(name, dtype)]
+    # a(150)->192, b(97)->128, c(64)->64, d(41)->64 live together = 448; e takes pages that b, c or d gave back
+    rp = replayer(folder, name, dtype, 448 + 128)
+    got = run_mixed(rp, prompts)
+    for k in prompts:
+        bad = first_bad(got[k], want[k], dtype)
+        assert bad is None, f"request {k}: first wrong position {bad}"
+    assert all(p.num_free == p.capacity for p in rp.cache.pools)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_and_first_tokens(models, dtype):
+    folder, cfg, w, prompts, want = models[("B", dtype)]
+    rp = replayer(folder, "B", dtype, 192)
+    p = prompts["a"]
+    got = [rp.step({"step": i, "entries": [{"id": "x", "tokens": [t], "want": [0]}], "end": []}) for i, t in enumerate(p)]
+    got = torch.cat(got)
+    bad = first_bad(got, want["a"], dtype)
+    assert bad is None, f"decoding from the first token on: first wrong position {bad}"
+    check(got[:3], want["a"][:3], dtype, "the first three tokens")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_greedy_generation_through_entry_point(models, name, dtype):
+    from llm_infrence_engine_b200.engine import Engine
+
+    folder, cfg, w, prompts, want = models[(name, dtype)]
+    ps = [random_prompt(cfg["vocab_size"], n, 50 + n) for n in (1, 7, 19, 33)]
+    eng = Engine(str(folder), dtype=dtype, block_size=PAGE_SIZES[name], num_blocks=20, max_seqs=3, max_len=64, max_num_batched_tokens=24)
+    res = eng.generate(ps, max_new_tokens=16)
+    agree = total = 0
+    for r, p in zip(res, ps):
+        ref = plain_generate(cfg, w, p, 16)
+        if dtype == "float32":
+            assert r.token_ids == ref, (name, len(p))
+        n = next((i for i, (a, b) in enumerate(zip(r.token_ids, ref)) if a != b), 16)
+        agree += n
+        total += 16
+    # bfloat16 may leave the plain sequence at a near tie; most tokens before that agree (the reference reports 95.8 %)
+    assert agree >= 0.6 * total, f"only {agree} of {total} greedy tokens agree"
+    assert eng.preemptions >= 0 and all(pool.num_free == pool.capacity for pool in eng.cache.pools)
+
+
+def test_trace_run_program(models, tmp_path):
+    folder, cfg, w, prompts, want = models[("A", "float32")]
+    p = prompts["c"]
+    lines = [
+        {"step": 0, "entries": [{"id": "r", "tokens": p[:30], "want": [0, 29]}], "end": []},
+        {"step": 1, "entries": [{"id": "r", "tokens": p[30:32], "want": []}], "end": []},
+        {"step": 2, "entries": [{"id": "r", "tokens": p[32:], "want": [len(p) - 33]}, {"id": "s", "tokens": p[:5], "want": [4]}], "end": ["r", "s"]},
+    ]
+    out = tmp_path / "out"
+    r = subprocess.run([sys.executable, str(ROOT / "bin" / "trace_run"), "--model", str(folder), "--dtype", "float32", "--out", str(out),
+                        "--max-tokens", "128"], input="\n".join(json.dumps(x) for x in lines) + "\n", capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert r.stdout.split() == ["done", "0", "done", "1", "done", "2"]
+    import numpy as np
+
+    v = cfg["vocab_size"]
+    s0 = torch.from_numpy(np.fromfile(out / "0.f32", dtype="<f4").reshape(-1, v))
+    s2 = torch.from_numpy(np.fromfile(out / "2.f32", dtype="<f4").reshape(-1, v))
+    assert not (out / "1.f32").exists()
+    check(s0, want["c"][[0, 29]], "float32", "step 0")
+    check(s2, torch.stack([want["c"][len(p) - 1], want["c"][4]]), "float32", "step 2")

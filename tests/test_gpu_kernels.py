@@ -1,0 +1,232 @@
+"""Each CUDA kernel alone against its plain torch statement (tests/torch_kernels.py), in float32 and
+bfloat16, at sizes other than the engine's: odd widths, head sizes in steps of 16 (and 8), any
+number of heads and groups, page edges, windows, several key slices."""
+import math
+
+import pytest
+import torch
+
+from torch_kernels import TorchKernels
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+@pytest.fixture(scope="module")
+def K():
+    from llm_infrence_engine_b200.csrc import get_kernels
+
+    return get_kernels()
+
+
+REF = TorchKernels()
+
+
+def tol(dtype, f32=2e-6, bf16=1e-2):
+    return f32 if dtype == torch.float32 else bf16
+
+
+def close(a, b, t):
+    a, b = a.float().cpu(), b.float().cpu()
+    scale = max(1.0, b.abs().max().item())
+    err = (a - b).abs().max().item()
+    assert err <= t * scale, f"max |difference| {err:.3g} > {t * scale:.3g}"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("V,H,N", [(50, 24, 7), (1000, 1030, 3)])
+def test_embed(K, dtype, V, H, N):
+    g = torch.Generator().manual_seed(0)
+    table = torch.randn(V, H, generator=g).to(dtype)
+    ids = torch.randint(0, V, (N,), generator=g).int()
+    got = K.embed(ids.cuda(), table.cuda())
+    assert torch.equal(got.cpu(), REF.embed(ids, table))
+
+
+@pytest.mark.parametrize("half,theta", [(8, 1e4), (24, 1e6), (64, 5e5)])
+def test_rope_tables(K, half, theta):
+    pos = torch.tensor([0, 1, 2, 17, 255, 256, 4095, 8191, 100000], dtype=torch.int32)
+    inv = 1.0 / (theta ** (torch.arange(0, 2 * half, 2).float() / (2 * half)))
+    c, s = K.rope_tables(pos.cuda(), inv.cuda())
+    rc, rs = REF.rope_tables(pos, inv)
+    ang = pos.double()[:, None] * inv.double()[None, :]  # the float32 angle is rounded before cos/sin on both sides
+    close(c, rc, 2e-6)
+    close(s, rs, 2e-6)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("N,H,eps", [(5, 64, 1e-6), (3, 200, 1e-5), (2, 4100, 3e-6), (9, 896, 1e-6)])
+def test_add_rmsnorm(K, dtype, N, H, eps):
+    g = torch.Generator().manual_seed(1)
+    res = torch.randn(N, H, generator=g) * 3
+    delta = (torch.randn(N, H, generator=g)).to(dtype)
+    w = 1 + 0.1 * torch.randn(H, generator=g)
+    for d in (delta, None):
+        r_gpu, r_ref = res.clone().cuda(), res.clone()
+        got = K.add_rmsnorm(r_gpu, None if d is None else d.cuda(), w.cuda(), eps, dtype)
+        want = REF.add_rmsnorm(r_ref, d, w, eps, dtype)
+        close(got, want, tol(dtype, 2e-6, 8e-3))
+        assert torch.equal(r_gpu.cpu(), r_ref)  # the residual sum is exact 32-bit addition on both sides
+    rows = torch.tensor([N - 1, 0, N // 2], dtype=torch.int32)
+    r_gpu = res.clone().cuda()
+    got = K.rmsnorm_rows(r_gpu, delta.cuda(), w.cuda(), eps, rows.cuda(), dtype)
+    close(got, REF.rmsnorm_rows(res, delta, w, eps, rows, dtype), tol(dtype, 2e-6, 8e-3))
+    assert torch.equal(r_gpu.cpu(), res)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("M,N,K_", [(1, 7, 5), (3, 131, 80), (70, 65, 200), (8, 320, 96), (130, 64, 17)])
+def test_linear(K, dtype, M, N, K_):
+    g = torch.Generator().manual_seed(2)
+    x = torch.randn(M, K_, generator=g).to(dtype)
+    w = torch.randn(N, K_, generator=g).to(dtype)
+    want = x.double() @ w.double().T
+    got = K.linear(x.cuda(), w.cuda())
+    close(got, want, tol(dtype, 2e-6, 8e-3))
+    got32 = K.linear(x.cuda(), w.cuda(), out_dtype=torch.float32)
+    close(got32, want, 2e-6)
+    # a row's result does not depend on the rows beside it
+    if M > 1:
+        alone = K.linear(x[M - 1:].contiguous().cuda(), w.cuda(), out_dtype=torch.float32)
+        assert torch.equal(alone[0], got32[M - 1])
+
+
+def test_linear_float32_is_true_32bit(K):
+    """Inputs that a reduced-precision matrix mode (TF32, bfloat16) would round: 1 + 2^-12 squared."""
+    x = torch.full((4, 64), 1 + 2.0 ** -12)
+    w = torch.full((5, 64), 1 + 2.0 ** -12)
+    got = K.linear(x.cuda(), w.cuda()).cpu()
+    want = (x.double() @ w.double().T)
+    assert (got.double() - want).abs().max() < 1e-4  # TF32 would be off by 64 * 2^-11 = 0.03
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nq,nkv,d,ps,bias", [(4, 2, 16, 16, True), (3, 1, 32, 8, True), (6, 3, 48, 16, False), (14, 2, 64, 16, True)])
+def test_rope_kv_write(K, dtype, nq, nkv, d, ps, bias):
+    g = torch.Generator().manual_seed(3)
+    N, pages = 11, 9
+    qkv = torch.randn(N, (nq + 2 * nkv) * d, generator=g).to(dtype)
+    b = torch.randn((nq + 2 * nkv) * d, generator=g) if bias else None
+    pos = torch.randint(0, 500, (N,), generator=g).int()
+    inv = 1.0 / (1e4 ** (torch.arange(0, d, 2).float() / d))
+    cos, sin = REF.rope_tables(pos, inv)
+    slots = torch.randperm(pages * ps, generator=g)[:N].int()
+    kp, vp = torch.zeros(pages, nkv, ps, d, dtype=dtype), torch.zeros(pages, nkv, ps, d, dtype=dtype)
+    q_ref, kp_ref, vp_ref = qkv.clone(), kp.clone(), vp.clone()
+    REF.rope_kv_write(q_ref, b, cos, sin, slots, kp_ref, vp_ref, nq, nkv, d, ps, True)
+    q_gpu, kp_gpu, vp_gpu = qkv.clone().cuda(), kp.cuda(), vp.cuda()
+    K.rope_kv_write(q_gpu, None if b is None else b.cuda(), cos.cuda(), sin.cuda(), slots.cuda(), kp_gpu, vp_gpu, nq, nkv, d, ps, True)
+    close(q_gpu, q_ref, tol(dtype, 1e-6, 8e-3))
+    close(kp_gpu, kp_ref, tol(dtype, 1e-6, 8e-3))
+    close(vp_gpu, vp_ref, tol(dtype, 1e-6, 8e-3))
+    # slots that were not written stay untouched
+    untouched = torch.ones(pages * ps, dtype=torch.bool)
+    untouched[slots.long()] = False
+    assert kp_gpu.cpu().permute(0, 2, 1, 3).reshape(pages * ps, -1)[untouched].abs().sum() == 0
+
+
+def _attention_case(dtype, nq, nkv, d, ps, lens, qlens, window, seed, spike=False):
+    """Requests with ``lens`` cached+new tokens, the last ``qlens`` of each being this step's tokens,
+    pages handed out in a shuffled order."""
+    g = torch.Generator().manual_seed(seed)
+    R = len(lens)
+    max_blocks = max(-(-L // ps) for L in lens) + 1
+    pages = sum(-(-L // ps) for L in lens) + 3
+    perm = (torch.randperm(pages - 1, generator=g) + 1).tolist()
+    table = torch.zeros(R, max_blocks, dtype=torch.int32)
+    kp = torch.randn(pages, nkv, ps, d, generator=g).to(dtype)   # stale values everywhere, also beyond the lengths
+    vp = torch.randn(pages, nkv, ps, d, generator=g).to(dtype)
+    for r, L in enumerate(lens):
+        for i in range(-(-L // ps)):
+            table[r, i] = perm.pop()
+    token_seq, positions = [], []
+    for r, (L, ql) in enumerate(zip(lens, qlens)):
+        token_seq += [r] * ql
+        positions += list(range(L - ql, L))
+    N = len(token_seq)
+    qkv = torch.randn(N, (nq + 2 * nkv) * d, generator=g).to(dtype)
+    if spike:  # one far key gets a score that stands out: a kernel that skips or misplaces it shows
+        r = 0
+        far = 1 if lens[0] > 1 else 0
+        page, off = int(table[r, far // ps]), far % ps
+        qv = qkv[0, :d].float()
+        kp[page, 0, off] = (qv / qv.norm() * 6).to(dtype)
+        vp[page, 0, off] = 10.0
+    return qkv, kp, vp, table, torch.tensor(token_seq, dtype=torch.int32), torch.tensor(positions, dtype=torch.int32)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nq,nkv,d,ps,lens,qlens,window,splits", [
+    (4, 2, 16, 16, [1, 15, 16, 17, 33], [1, 1, 16, 2, 33], 0, None),
+    (3, 1, 32, 8, [40, 9, 64], [1, 9, 5], 0, 1),
+    (6, 3, 48, 16, [70, 31], [70, 1], 24, None),
+    (14, 2, 64, 16, [300, 700, 5], [1, 1, 5], 0, 3),
+    (14, 2, 64, 16, [900], [900], 0, None),
+    (8, 8, 80, 32, [65, 130], [2, 1], 50, 2),
+    (16, 1, 128, 64, [257], [3], 0, 4),
+    (2, 2, 256, 16, [48], [48], 0, None),
+])
+def test_paged_attention(K, dtype, nq, nkv, d, ps, lens, qlens, window, splits):
+    for spike in (False, True):
+        qkv, kp, vp, table, tseq, pos = _attention_case(dtype, nq, nkv, d, ps, lens, qlens, window, 4, spike)
+        scale = 1.0 / math.sqrt(d)
+        want = REF.paged_attention(qkv, kp, vp, table, tseq, pos, nq, nkv, d, ps, scale, window, max(lens))
+        got = K.paged_attention(qkv.cuda(), kp.cuda(), vp.cuda(), table.cuda(), tseq.cuda(), pos.cuda(), nq, nkv, d, ps, scale,
+                                window, max(lens), num_splits=splits)
+        close(got, want, tol(dtype, 3e-6, 1e-2))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_silu_mul(K, dtype):
+    g = torch.Generator().manual_seed(5)
+    gu = (torch.randn(7, 2 * 203, generator=g) * 4).to(dtype)
+    close(K.silu_mul(gu.cuda()), REF.silu_mul(gu), tol(dtype, 1e-6, 8e-3))
+
+
+@pytest.mark.parametrize("V", [17, 320, 151936])
+def test_argmax(K, V):
+    g = torch.Generator().manual_seed(6)
+    logits = torch.randn(5, V, generator=g)
+    logits[1, V // 2] = logits[1, V - 1] = 50.0  # a tie: the lower index wins
+    logits[2, 0] = 60.0
+    logits[3, V - 1] = 60.0
+    got = K.argmax(logits.cuda()).cpu()
+    assert got.tolist() == logits.argmax(-1).tolist()
+    assert got[1] == V // 2
+
+
+@pytest.mark.parametrize("V", [131, 320, 5000])
+def test_sample(K, V):
+    from plain_qwen2 import plain_draw, plain_logits_to_probs
+
+    g = torch.Generator().manual_seed(7)
+    rows = []
+    for temp, k, p in [(0.8, 0, 1.0), (1.3, 20, 1.0), (0.7, 0, 0.9), (1.0, 50, 0.5), (0.0, 0, 1.0), (0.5, 1, 1.0), (2.0, 7, 0.3)]:
+        for u in (0.0, 0.123, 0.5, 0.77, 0.999999):
+            rows.append((temp, k, p, u))
+    M = len(rows)
+    logits = torch.randn(M, V, generator=g) * 3
+    got = K.sample(logits.cuda(), torch.tensor([r[0] for r in rows]).cuda(), torch.tensor([r[1] for r in rows], dtype=torch.int32).cuda(),
+                   torch.tensor([r[2] for r in rows]).cuda(), torch.tensor([r[3] for r in rows]).cuda()).cpu().tolist()
+    for i, (temp, k, p, u) in enumerate(rows):
+        want = plain_draw(logits[i], temp, k, p, u)
+        if got[i] != want:  # only a draw that lands on the edge between two tokens may differ, and then by one kept token
+            probs = plain_logits_to_probs(logits[i], temp, k, p).double()
+            cdf = probs.cumsum(-1)
+            edge = min(abs(float(cdf[got[i]]) - u * float(cdf[-1])), abs(float(cdf[want]) - u * float(cdf[-1])))
+            assert probs[got[i]] > 0 and edge < 1e-6, (i, rows[i], got[i], want)
+
+
+def test_sample_frequencies(K):
+    """Empirical frequencies follow the distribution (the reference's test draws 4,000 times, tests/test_sampler.py:6-44)."""
+    from plain_qwen2 import plain_logits_to_probs
+    from llm_infrence_engine_b200.sampling import uniform_from
+
+    logits = torch.tensor([2.0, 1.0, 0.5, 0.0, -1.0, -3.0])
+    M = 4000
+    u = torch.tensor([uniform_from(11, c) for c in range(M)])
+    got = K.sample(logits.repeat(M, 1).cuda(), torch.full((M,), 0.9).cuda(), torch.zeros(M, dtype=torch.int32).cuda(),
+                   torch.ones(M).cuda(), u.cuda()).cpu()
+    freq = torch.bincount(got.long(), minlength=6).double() / M
+    assert (freq - plain_logits_to_probs(logits, 0.9).double()).abs().max() < 0.03
