@@ -1,0 +1,289 @@
+"""Decode and prefill throughput of the engine on one B200, as one JSON line.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+The default run has the layer sizes of Qwen2.5-0.5B (24 layers, hidden 896, 14 query / 2 key-value
+heads of 64, intermediate 4864, vocabulary 151936, tied head) with random weights in bfloat16, a
+batch of 8 requests and a context of 8192 tokens. A "step" is one decode step of the whole batch.
+
+``value``     decoded tokens per second of the step function alone: W warm-up steps, then K steps
+              between two CUDA events on the launching stream with a synchronize on both sides.
+              The requests' cache pages hold synthetic keys and values (a step's cost does not
+              depend on them); weights plus cache are far larger than L2, so nothing is flushed.
+``e2e``       the same through ``Engine.step()``: requests are added as token lists on the host,
+              their prompts are prefilled by the engine, and every timed step copies its inputs
+              from pinned host memory and reads the sampled tokens back.
+``prefill``   one prompt of 2,048 tokens in one step; ``frac`` = flops / time / bfloat16 peak.
+``roofline``  bytes a decode step must read (every weight once + the live requests' cache) / its time.
+``points``    decode tokens per second at batch 1 and 64, same method as ``value``.
+
+Peaks come from MEASURED_PEAKS.json beside this file when it exists, else 6.65 TB/s and 1.59 PFLOP/s.
+More than one GPU is outside this engine: ``--gpus N`` with N > 1 prints one line and exits with 2.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+MODEL = {
+    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "vocab_size": 151936, "hidden_size": 896,
+    "intermediate_size": 4864, "num_hidden_layers": 24, "num_attention_heads": 14, "num_key_value_heads": 2,
+    "rms_norm_eps": 1e-6, "rope_theta": 1000000.0, "tie_word_embeddings": True, "max_position_embeddings": 32768,
+    "use_sliding_window": False, "hidden_act": "silu",
+}
+CONTEXT = 8192
+PREFILL_TOKENS = 2048
+BLOCK = 16
+
+
+def peaks() -> dict:
+    out = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.is_file():
+        try:
+            d = json.loads(p.read_text())
+            if d.get("hbm_gbs"):
+                out["hbm_gbs"] = float(d["hbm_gbs"])
+            if d.get("bf16_tflops"):
+                out["bf16_tflops"] = float(d["bf16_tflops"])
+            if d.get("bf16_tflops_sustained"):
+                out["bf16_tflops_sustained"] = float(d["bf16_tflops_sustained"])
+            out["source"] = "measured"
+        except (ValueError, OSError):
+            pass
+    return out
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons of GPU 0 every 200 ms while running."""
+
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.rows, self.proc = [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm = sorted(int(r[0]) for r in self.rows if r and r[0].isdigit())
+        mx = [int(r[1]) for r in self.rows if len(r) > 1 and r[1].isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({n for r in self.rows if len(r) >= 6 for n, v in zip(names, r[2:6]) if v.lower().startswith("active")})
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": reasons}
+
+
+def flops_prefill(T: int) -> float:
+    m = MODEL
+    d = m["hidden_size"] // m["num_attention_heads"]
+    per_layer = (m["hidden_size"] * (m["num_attention_heads"] + 2 * m["num_key_value_heads"]) * d
+                 + m["num_attention_heads"] * d * m["hidden_size"] + 3 * m["hidden_size"] * m["intermediate_size"])
+    linear = 2.0 * T * per_layer * m["num_hidden_layers"]
+    attn = m["num_hidden_layers"] * 4.0 * m["num_attention_heads"] * d * (T * (T + 1) / 2)
+    head = 2.0 * m["hidden_size"] * m["vocab_size"]
+    return linear + attn + head
+
+
+def reference_arm() -> int:
+    why = "the reference is a pure-Python package that downloads Qwen2.5-0.5B-Instruct from the network at start; not installed here"
+    ref = ROOT / "baseline" / "_ref" / "miniserve"
+    if ref.is_dir():
+        why = "the reference needs the downloaded Qwen2.5-0.5B-Instruct checkpoint and tokenizer; there is no network"
+    print(json.dumps({"impl": "reference", "unavailable": why}))
+    return 0
+
+
+def decode_point(engine_mod, folder: Path, batch: int, steps: int, warmup: int, torch) -> dict:
+    """Device time of ``steps`` decode steps of ``batch`` requests at CONTEXT tokens, step function + argmax."""
+    from llm_infrence_engine_b200.config import EngineConfig
+    from llm_infrence_engine_b200.engine import StepEntry, build_runner
+
+    per_seq = -(-(CONTEXT + 8) // BLOCK)
+    cfg = EngineConfig(dtype="bfloat16", block_size=BLOCK, num_blocks=batch * per_seq + 1, max_seqs=batch, max_len=CONTEXT + 8,
+                       max_num_batched_tokens=max(batch, 16))
+    spec, cache, runner = build_runner(folder, cfg)
+    K = runner.K
+    for b in runner.bindings:
+        b.k.normal_(0, 0.5)
+        b.v.normal_(0, 0.5)
+    entries = []
+    for i in range(batch):
+        cache.admit(i)
+        cache.reserve(i, 0, CONTEXT)
+        entries.append(StepEntry(i, [(17 * i + 3) % MODEL["vocab_size"]], CONTEXT - 1, (0,)))
+    ctx, rows = runner.make_context(entries)
+
+    def one():
+        ctx._tables.clear()
+        logits = runner.forward(ctx, rows)
+        return K.argmax(logits)
+
+    for _ in range(warmup):
+        one()
+    torch.cuda.synchronize()
+    n0 = K.launches
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        one()
+    stop.record()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(stop) / steps
+    out = {"ms": ms, "tok_s": batch / ms * 1e3, "launches": K.launches - n0,
+           "bytes": runner.weight_bytes_per_step() + batch * CONTEXT * runner.kv_bytes_per_token}
+    del runner, spec, cache
+    torch.cuda.empty_cache()
+    return out
+
+
+def prefill_point(folder: Path, torch, reps: int = 3) -> dict:
+    from llm_infrence_engine_b200.config import EngineConfig
+    from llm_infrence_engine_b200.engine import StepEntry, build_runner
+
+    cfg = EngineConfig(dtype="bfloat16", block_size=BLOCK, num_blocks=PREFILL_TOKENS // BLOCK + 2, max_seqs=1,
+                       max_len=PREFILL_TOKENS, max_num_batched_tokens=PREFILL_TOKENS)
+    spec, cache, runner = build_runner(folder, cfg)
+    g = torch.Generator().manual_seed(5)
+    prompt = torch.randint(0, MODEL["vocab_size"], (PREFILL_TOKENS,), generator=g).tolist()
+    times = []
+    for i in range(reps + 1):
+        cache.admit("p")
+        cache.reserve("p", 0, PREFILL_TOKENS)
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        runner.step([StepEntry("p", prompt, 0, (PREFILL_TOKENS - 1,))])
+        stop.record()
+        torch.cuda.synchronize()
+        cache.free("p")
+        if i:
+            times.append(start.elapsed_time(stop))
+    ms = sorted(times)[len(times) // 2]
+    del runner, spec, cache
+    torch.cuda.empty_cache()
+    return {"ms": ms}
+
+
+def e2e_point(folder: Path, batch: int, steps: int, warmup: int, torch) -> dict:
+    """``Engine.step()`` in a loop: host token lists in, sampled tokens out, after the engine prefilled the prompts itself."""
+    from llm_infrence_engine_b200.engine import Engine, Request
+
+    total = steps + warmup + 2
+    prompt_len = CONTEXT - total
+    per_seq = -(-(CONTEXT + 8) // BLOCK)
+    eng = Engine(str(folder), dtype="bfloat16", block_size=BLOCK, num_blocks=batch * per_seq + 1, max_seqs=batch,
+                 max_len=CONTEXT + 8, max_num_batched_tokens=2048)
+    g = torch.Generator().manual_seed(9)
+    reqs = [eng.add_request(Request(torch.randint(0, MODEL["vocab_size"], (prompt_len,), generator=g).tolist(), max_new_tokens=total))
+            for _ in range(batch)]
+    t0 = time.perf_counter()
+    while any(r.num_computed < prompt_len for r in reqs) or any(len(r.output_ids) < 1 for r in reqs):
+        eng.step()
+    torch.cuda.synchronize()
+    prefill_s = time.perf_counter() - t0
+    for _ in range(warmup):
+        eng.step()
+    torch.cuda.synchronize()
+    before = sum(len(r.output_ids) for r in reqs)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        eng.step()
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    made = sum(len(r.output_ids) for r in reqs) - before
+    h2d = eng.runner.last_h2d_bytes
+    return {"value": made / dt, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * batch,
+            "ms_per_step": dt / steps * 1e3, "prefill_s": round(prefill_s, 2)}
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=MODEL["num_hidden_layers"], help="fewer layers than the model has (named in config)")
+    ap.add_argument("--skip-e2e", action="store_true")
+    a = ap.parse_args()
+    if a.impl == "reference":
+        return reference_arm()
+    if a.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {a.gpus} is not supported")
+        return 2
+    a.warmup = max(a.warmup, 3)
+
+    import torch
+
+    import llm_infrence_engine_b200.engine as engine_mod
+    from llm_infrence_engine_b200.weights import write_random_model
+
+    pk = peaks()
+    model = dict(MODEL)
+    model["num_hidden_layers"] = a.layers
+    with tempfile.TemporaryDirectory() as tmp:
+        folder = write_random_model(model, Path(tmp) / "model", seed=0, store_dtype="bfloat16")
+        sampler = ClockSampler()
+        sampler.start()
+        main_pt = decode_point(engine_mod, folder, a.batch, a.steps, a.warmup, torch)
+        clocks = sampler.stop()
+        b1 = decode_point(engine_mod, folder, 1, a.steps, a.warmup, torch)
+        b64 = decode_point(engine_mod, folder, 64, max(8, a.steps // 4), a.warmup, torch)
+        pre = prefill_point(folder, torch)
+        e2e = None if a.skip_e2e else e2e_point(folder, a.batch, a.steps, a.warmup, torch)
+
+    fl = flops_prefill(PREFILL_TOKENS) * a.layers / MODEL["num_hidden_layers"]
+    achieved = main_pt["bytes"] / (main_pt["ms"] * 1e-3) / 1e9
+    line = {
+        "metric": "decode tok/s at batch 8, context 8192 (Qwen2.5-0.5B shape, bf16, random weights)",
+        "value": round(main_pt["tok_s"], 1), "unit": "tokens/s", "n_gpus": 1, "steps": a.steps, "warmup": a.warmup,
+        "ms_per_step": round(main_pt["ms"], 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: random weights (seed 0), uniform random token ids, synthetic cache contents",
+        "impl": "ours",
+        "config": {"model": "Qwen2.5-0.5B shape", "layers": a.layers, "layers_of_model": MODEL["num_hidden_layers"],
+                   "hidden": 896, "heads": 14, "kv_heads": 2, "head_dim": 64, "intermediate": 4864, "vocab": 151936,
+                   "tied": True, "global_batch": a.batch, "seq_len": CONTEXT, "block_size": BLOCK, "parallelism": "single GPU",
+                   "l2": "inputs larger than L2 (weights + cache per step >> 126 MB), no flush", "peaks": pk["source"]},
+        "clocks": clocks,
+        "gpu_launches": main_pt["launches"],
+        "prefill": {"value": round(PREFILL_TOKENS / (pre["ms"] * 1e-3), 1), "tokens": PREFILL_TOKENS, "ms": round(pre["ms"], 3),
+                    "frac": round(fl / (pre["ms"] * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "points": {"decode_b1": round(b1["tok_s"], 1), "decode_b64": round(b64["tok_s"], 1)},
+    }
+    if e2e is not None:
+        line["e2e"] = {k: (round(v, 2) if isinstance(v, float) else v) for k, v in e2e.items()}
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -101,7 +101,7 @@ class ModelRunner:
             else:
                 raise TypeError(f"cache entry {entry} has a spec of unknown kind {type(cs).__name__}")
         self._pinned: Optional[torch.Tensor] = None
-        self.launches = 0  # kernels launched by the last step, as counted by the kernel library
+        self.last_h2d_bytes = 0  # bytes of step inputs copied to the device by the last step
 
     # ------------------------------------------------------------------ building the step's inputs
     def _build(self, entries: Sequence[StepEntry]) -> tuple:
@@ -161,6 +161,7 @@ class ModelRunner:
 
     def _upload(self, packed: List[int]) -> torch.Tensor:
         n = len(packed)
+        self.last_h2d_bytes = 4 * n
         host = torch.tensor(packed, dtype=torch.int32)
         if self.device.type != "cuda":
             return host.to(self.device)
