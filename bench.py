@@ -195,7 +195,7 @@ def e2e_point(folder: Path, batch: int, steps: int, warmup: int, torch) -> dict:
     """``Engine.step()`` in a loop: host token lists in, sampled tokens out, after the engine prefilled the prompts itself."""
     from llm_infrence_engine_b200.engine import Engine, Request
 
-    total = steps + warmup + 2
+    total = steps + warmup + 96  # nobody finishes before the timed steps, even the request that was admitted first
     prompt_len = CONTEXT - total
     per_seq = -(-(CONTEXT + 8) // BLOCK)
     eng = Engine(str(folder), dtype="bfloat16", block_size=BLOCK, num_blocks=batch * per_seq + 1, max_seqs=batch,

@@ -100,7 +100,8 @@ class ModelRunner:
                 self.bindings.append(None)
             else:
                 raise TypeError(f"cache entry {entry} has a spec of unknown kind {type(cs).__name__}")
-        self._pinned: Optional[torch.Tensor] = None
+        self._staging: List[list] = []  # ring of [pinned buffer, event of the copy that last read it]
+        self._next_staging = 0
         self.last_h2d_bytes = 0  # bytes of step inputs copied to the device by the last step
 
     # ------------------------------------------------------------------ building the step's inputs
@@ -160,15 +161,27 @@ class ModelRunner:
         return packed, N, R, M, max_blocks, starts, lens, ctxs, slots
 
     def _upload(self, packed: List[int]) -> torch.Tensor:
+        """One asynchronous copy of the step's integers from pinned memory. The staging buffers form a
+        ring: a buffer is written again only after the copy that last read it has finished, because
+        the host may run several steps ahead of the device when nothing is read back in between."""
         n = len(packed)
         self.last_h2d_bytes = 4 * n
         host = torch.tensor(packed, dtype=torch.int32)
         if self.device.type != "cuda":
             return host.to(self.device)
-        if self._pinned is None or self._pinned.numel() < n:
-            self._pinned = torch.empty(max(n, 4096) * 2, dtype=torch.int32, pin_memory=True)
-        self._pinned[:n].copy_(host)
-        return self._pinned[:n].to(self.device, non_blocking=True)
+        if not self._staging:
+            self._staging = [[None, None] for _ in range(4)]
+        slot = self._staging[self._next_staging]
+        self._next_staging = (self._next_staging + 1) % len(self._staging)
+        if slot[1] is not None:
+            slot[1].synchronize()
+        if slot[0] is None or slot[0].numel() < n:
+            slot[0] = torch.empty(max(2 * n, 8192), dtype=torch.int32, pin_memory=True)
+        slot[0][:n].copy_(host)
+        dev = slot[0][:n].to(self.device, non_blocking=True)
+        slot[1] = torch.cuda.Event()
+        slot[1].record()
+        return dev
 
     def make_context(self, entries: Sequence[StepEntry]):
         packed, N, R, M, max_blocks, starts, lens, ctxs, slots = self._build(entries)
