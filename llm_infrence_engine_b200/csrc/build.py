@@ -124,6 +124,9 @@ def library_path(build: bool = True) -> Path:
         if r.returncode != 0:
             raise BuildError(f"linking the CUDA library failed:\n{r.stdout}\n{r.stderr}")
         os.replace(tmp, out_dir / name)
+        for old in out_dir.glob("libllmie_kernels_*.so"):  # libraries of earlier source states are never loaded again
+            if old.name != name:
+                old.unlink(missing_ok=True)
     finally:
         shutil.rmtree(work, ignore_errors=True)
     _say(f"built {name} in {time.time() - t0:.0f} s")
