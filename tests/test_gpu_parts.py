@@ -1,0 +1,248 @@
+"""Each part alone against the plain function of the same formula, then parts that only a test defines:
+a mixer with state of its own registered as a new architecture, a running order that names a layer
+twice and lets a layer read another layer's cache."""
+import json
+import math
+from dataclasses import dataclass
+
+import pytest
+import torch
+
+from helpers import make_model_folder, random_prompt
+from plain_qwen2 import (plain_apply_rope, plain_attention, plain_block, plain_config, plain_forward, plain_load, plain_mlp,
+                         plain_rmsnorm, plain_rope_tables)
+from tiny_configs import CONFIGS, PAGE_SIZES
+
+pytestmark = pytest.mark.gpu
+
+
+def _ctx(name, folder, dtype, prompt, block_size):
+    """A runner for the model folder and the context of one whole-prompt step."""
+    from llm_infrence_engine_b200.config import EngineConfig
+    from llm_infrence_engine_b200.engine import StepEntry, build_runner
+
+    cfg = EngineConfig(dtype=dtype, block_size=block_size, num_blocks=40, max_seqs=2, max_len=256, max_num_batched_tokens=256)
+    spec, cache, runner = build_runner(folder, cfg)
+    cache.admit("r")
+    cache.reserve("r", 0, len(prompt))
+    ctx, rows = runner.make_context([StepEntry("r", prompt, 0, list(range(len(prompt))))])
+    return spec, cache, runner, ctx, rows
+
+
+def close(got, want, tol):
+    err = (got.float().cpu() - want.float()).abs().max().item()
+    assert err <= tol * max(1.0, want.float().abs().max().item()), err
+
+
+@pytest.mark.parametrize("dtype,tol", [("float32", 3e-6), ("bfloat16", 2e-2)])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_each_part_alone(tmp_path, name, dtype, tol):
+    folder = make_model_folder(tmp_path, name, dtype)
+    cfg, w = plain_load(folder)
+    c = plain_config(cfg)
+    prompt = random_prompt(cfg["vocab_size"], 37, 4)
+    spec, cache, runner, ctx, rows = _ctx(name, folder, dtype, prompt, PAGE_SIZES[name])
+    td = torch.float32 if dtype == "float32" else torch.bfloat16
+    g = torch.Generator().manual_seed(0)
+    T, H = len(prompt), c["hidden"]
+
+    # embedding
+    x = spec.embedding.forward(ctx)
+    assert torch.equal(x.cpu(), w["model.embed_tokens.weight"][torch.tensor(prompt)].float())
+
+    # norm (with and without the pending addition), also on chosen rows only
+    res = torch.randn(T, H, generator=g)
+    delta = torch.randn(T, H, generator=g).to(td)
+    norm = spec.layers[0].norm1
+    r = res.clone().cuda()
+    close(norm.add_norm(ctx, r, delta.cuda()), plain_rmsnorm(res + delta.float(), w["model.layers.0.input_layernorm.weight"], c["eps"]), tol)
+    close(r, res + delta.float(), 1e-7)
+    close(norm.norm_rows(ctx, res.clone().cuda(), None, rows[3:9]), plain_rmsnorm(res[3:9], w["model.layers.0.input_layernorm.weight"], c["eps"]), tol)
+
+    # position encoding
+    cos, sin = ctx.position_tables(spec.layers[0].mixer.position)
+    pc, ps = plain_rope_tables(torch.arange(T), c["head_dim"], c["theta"], torch.float32)
+    close(cos, pc[:, : c["head_dim"] // 2], 2e-6)
+    close(sin, ps[:, : c["head_dim"] // 2], 2e-6)
+
+    # mixer: every layer's attention alone (different windows in C), on random normalised input
+    h = (torch.randn(T, H, generator=g) * 0.5).to(td)
+    for i, layer in enumerate(spec.layers):
+        b = runner.bindings[i]
+        got = layer.mixer.forward(ctx, h.cuda(), b)
+        want = plain_attention(h.float(), w, f"model.layers.{i}.self_attn", c, pc, ps, c["window"][i])
+        close(got, want, tol)
+
+    # feed-forward
+    got = spec.layers[1].ff.forward(ctx, h.cuda())
+    close(got, plain_mlp(h.float(), w, "model.layers.1.mlp"), tol)
+
+    # block: residual in, residual + owed addend out
+    res2 = torch.randn(T, H, generator=g) * 0.3
+    r = res2.clone().cuda()
+    owed = spec.layers[1].forward(ctx, r, None, runner.bindings[1])
+    close(r + owed.float(), plain_block(res2, w, 1, c, pc, ps), tol)
+
+    # head
+    hn = torch.randn(5, H, generator=g).to(td)
+    head = w["model.embed_tokens.weight"] if c["tied"] else w["lm_head.weight"]
+    got = spec.head.forward(ctx, hn.cuda())
+    assert got.dtype == torch.float32
+    close(got, hn.float() @ head.T, 3e-6 if dtype == "float32" else 3e-3)
+
+
+# ------------------------------------------------------------------------------------------------
+# A toy architecture defined here only: its mixer keeps a running mean of its inputs per request
+# (state of fixed size, no pages) and mixes it back in. It is registered, loaded and stepped through
+# the framework's own files, which know nothing about it.
+def _toy_parts():
+    from llm_infrence_engine_b200.cache import FixedStateSpec
+    from llm_infrence_engine_b200.models import ModelSpec, sequential
+    from llm_infrence_engine_b200.parts import GatedMLP, Mixer, OutputHead, ParamSpec, PreNormBlock, RMSNorm, Source, TokenEmbedding
+
+    class RunningMeanMixer(Mixer):
+        """state = (sum of inputs so far, count); out_t = W (x_t + mean of x_0..x_t)."""
+
+        def __init__(self, hidden, prefix):
+            self.hidden, self.prefix, self.w = hidden, prefix, None
+
+        def params(self):
+            return {"w": ParamSpec((Source(f"{self.prefix}.w.weight", (self.hidden, self.hidden)),))}
+
+        def cache_spec(self):
+            return FixedStateSpec((self.hidden + 1,))
+
+        def forward(self, ctx, h, cache):
+            out = torch.empty_like(h)
+            for start, n, slot in zip(ctx.seq_starts, ctx.seq_lens, ctx.seq_slot_list):
+                x = h[start:start + n].float()
+                st = cache.state[slot]
+                sums = st[: self.hidden] + x.cumsum(0)
+                counts = st[self.hidden] + torch.arange(1, n + 1, device=h.device, dtype=torch.float32)
+                out[start:start + n] = (x + sums / counts[:, None]).to(h.dtype)
+                st[: self.hidden] = sums[-1]
+                st[self.hidden] = counts[-1]
+            return ctx.K.linear(out, self.w)
+
+    @dataclass(frozen=True)
+    class ToyConfig:
+        vocab_size: int
+        hidden_size: int
+        intermediate_size: int
+        num_hidden_layers: int
+        rms_norm_eps: float
+
+        @classmethod
+        def from_dict(cls, d):
+            return cls(d["vocab_size"], d["hidden_size"], d["intermediate_size"], d["num_hidden_layers"], d["rms_norm_eps"])
+
+    def build(cfg):
+        emb = TokenEmbedding(cfg.vocab_size, cfg.hidden_size, "emb.weight")
+        layers = [PreNormBlock(RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, f"l{i}.n1.weight"), RunningMeanMixer(cfg.hidden_size, f"l{i}.mix"),
+                               RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, f"l{i}.n2.weight"),
+                               GatedMLP(cfg.hidden_size, cfg.intermediate_size, f"l{i}.mlp")) for i in range(cfg.num_hidden_layers)]
+        return ModelSpec(cfg, emb, layers, sequential(cfg.num_hidden_layers), RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, "out_norm.weight"),
+                         OutputHead(cfg.vocab_size, cfg.hidden_size, "head.weight", tied_to=emb))
+
+    return ToyConfig, build
+
+
+def _toy_plain(cfg, w, ids):
+    x = w["emb.weight"][torch.tensor(ids)]
+    for i in range(cfg["num_hidden_layers"]):
+        h = plain_rmsnorm(x, w[f"l{i}.n1.weight"], cfg["rms_norm_eps"])
+        mean = h.cumsum(0) / torch.arange(1, len(ids) + 1)[:, None]
+        x = x + (h + mean) @ w[f"l{i}.mix.w.weight"].T
+        h = plain_rmsnorm(x, w[f"l{i}.n2.weight"], cfg["rms_norm_eps"])
+        g = h @ w[f"l{i}.mlp.gate_proj.weight"].T
+        x = x + (torch.nn.functional.silu(g) * (h @ w[f"l{i}.mlp.up_proj.weight"].T)) @ w[f"l{i}.mlp.down_proj.weight"].T
+    return plain_rmsnorm(x, w["out_norm.weight"], cfg["rms_norm_eps"]) @ w["emb.weight"].T
+
+
+def test_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
+    from llm_infrence_engine_b200.engine import Engine, TraceReplayer
+    from llm_infrence_engine_b200.models import register_architecture
+    from llm_infrence_engine_b200.weights import write_random_model
+
+    ToyConfig, build = _toy_parts()
+    register_architecture("ToyRunningMeanLM", ToyConfig, build, replace=True)
+    cfg = {"architectures": ["ToyRunningMeanLM"], "vocab_size": 90, "hidden_size": 40, "intermediate_size": 56, "num_hidden_layers": 2,
+           "rms_norm_eps": 1e-5}
+    folder = write_random_model(cfg, tmp_path / "toy", 5, "float32", std=0.1)
+    _, w = plain_load(folder)
+    prompts = {"a": random_prompt(90, 50, 1), "b": random_prompt(90, 23, 2)}
+    want = {k: _toy_plain(cfg, w, p) for k, p in prompts.items()}
+    rp = TraceReplayer(str(folder), "float32", 128)
+    assert rp.cache.groups == [] and rp.runner.bindings[0].state.shape == (4, 41)
+    # whole, then cut into portions and interleaved with the other request: the state must carry over exactly
+    for k, p in prompts.items():
+        got = rp.step({"step": 0, "entries": [{"id": k, "tokens": p, "want": list(range(len(p)))}], "end": [k]})
+        assert (got - want[k]).abs().max() < 2e-5
+    got = {"a": [], "b": []}
+    cuts = {"a": [(0, 7), (7, 9), (9, 40), (40, 50)], "b": [(0, 1), (1, 2), (2, 23)]}
+    for step in range(4):
+        entries = [{"id": k, "tokens": prompts[k][lo:hi], "want": list(range(hi - lo))} for k in ("a", "b") if step < len(cuts[k])
+                   for lo, hi in [cuts[k][step]]]
+        out = rp.step({"step": step, "entries": entries, "end": [k for k in ("a", "b") if step == len(cuts[k]) - 1]})
+        o = 0
+        for e in entries:
+            got[e["id"]].append(out[o:o + len(e["tokens"])])
+            o += len(e["tokens"])
+    for k in prompts:
+        assert (torch.cat(got[k]) - want[k]).abs().max() < 2e-5
+    # and through the scheduler and the entry point: a slot that is used again starts from zero state
+    eng = Engine(str(folder), dtype="float32", max_seqs=1, max_len=64, max_num_batched_tokens=16)
+    for k, p in prompts.items():
+        ids = list(p[:20])
+        ref = []
+        for _ in range(5):
+            ref.append(int(_toy_plain(cfg, w, ids + ref)[-1].argmax()))
+        assert eng.generate(ids, max_new_tokens=5).token_ids == ref
+
+
+def test_running_order_is_data(tmp_path):
+    """Layer 1 runs twice (each run with its own cache entry) and layer 2 reads layer 0's cache instead of keeping one."""
+    from llm_infrence_engine_b200.config import Qwen2Config
+    from llm_infrence_engine_b200.engine import TraceReplayer
+    from llm_infrence_engine_b200.models import LayerCall, register_architecture
+    from llm_infrence_engine_b200.models.qwen2 import build_qwen2
+
+    def build(cfg):
+        spec = build_qwen2(cfg)
+        spec.schedule = [LayerCall(0, 0), LayerCall(1, 1), LayerCall(1, 2), LayerCall(2, 0, write=False)]
+        return spec
+
+    register_architecture("Qwen2ReorderedForTest", Qwen2Config, build, replace=True)
+    cfg = dict(CONFIGS["B"], architectures=["Qwen2ReorderedForTest"])
+    from llm_infrence_engine_b200.weights import write_random_model
+
+    folder = write_random_model(cfg, tmp_path / "reordered", 3, "float32")
+    pcfg, w = plain_load(folder)
+    # the plain side: layer 2 attends with its own queries over layer 0's keys and values
+    p = random_prompt(320, 45, 8)
+    c = plain_config(pcfg)
+    x = w["model.embed_tokens.weight"][torch.tensor(p)]
+    cos, sin = plain_rope_tables(torch.arange(len(p)), c["head_dim"], c["theta"], torch.float32)
+    x0_in = plain_rmsnorm(x, w["model.layers.0.input_layernorm.weight"], c["eps"])
+    x = plain_block(x, w, 0, c, cos, sin)
+    x = plain_block(x, w, 1, c, cos, sin)
+    x = plain_block(x, w, 1, c, cos, sin)
+    w2 = dict(w)
+    h = plain_rmsnorm(x, w["model.layers.2.input_layernorm.weight"], c["eps"])
+    T, d, nq = len(p), c["head_dim"], c["heads"]
+    q = (h @ w["model.layers.2.self_attn.q_proj.weight"].T + w["model.layers.2.self_attn.q_proj.bias"]).view(T, nq, d).transpose(0, 1)
+    k = (x0_in @ w["model.layers.0.self_attn.k_proj.weight"].T + w["model.layers.0.self_attn.k_proj.bias"]).view(T, 1, d).transpose(0, 1)
+    v = (x0_in @ w["model.layers.0.self_attn.v_proj.weight"].T + w["model.layers.0.self_attn.v_proj.bias"]).view(T, 1, d).transpose(0, 1)
+    q, k = plain_apply_rope(q, cos, sin), plain_apply_rope(k, cos, sin)
+    s = (q @ k.transpose(1, 2)) / math.sqrt(d)
+    s = s.masked_fill(torch.arange(T)[None, :] > torch.arange(T)[:, None], float("-inf"))
+    a = (torch.softmax(s, -1) @ v).transpose(0, 1).reshape(T, nq * d) @ w["model.layers.2.self_attn.o_proj.weight"].T
+    x = x + a
+    x = x + plain_mlp(plain_rmsnorm(x, w["model.layers.2.post_attention_layernorm.weight"], c["eps"]), w, "model.layers.2.mlp")
+    want = plain_rmsnorm(x, w["model.norm.weight"], c["eps"]) @ w["lm_head.weight"].T
+
+    rp = TraceReplayer(str(folder), "float32", 64, block_size=8)
+    assert len(rp.runner.bindings) == 3
+    got = torch.cat([rp.step({"step": 0, "entries": [{"id": "r", "tokens": p[:30], "want": list(range(30))}], "end": []}),
+                     rp.step({"step": 1, "entries": [{"id": "r", "tokens": p[30:], "want": list(range(15))}], "end": ["r"]})])
+    assert (got - want).abs().max() < 2e-5
