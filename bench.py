@@ -120,14 +120,15 @@ def reference_arm() -> int:
     return 0
 
 
-def decode_point(engine_mod, folder: Path, batch: int, steps: int, warmup: int, torch) -> dict:
-    """Device time of ``steps`` decode steps of ``batch`` requests at CONTEXT tokens, step function + argmax."""
+def decode_point(folder: Path, batch: int, steps: int, warmup: int, torch, graphs: bool = True) -> dict:
+    """Device time of ``steps`` decode steps of ``batch`` requests at CONTEXT tokens: the step function
+    (replayed from its CUDA graph unless ``graphs`` is off) plus the argmax over its logits."""
     from llm_infrence_engine_b200.config import EngineConfig
     from llm_infrence_engine_b200.engine import StepEntry, build_runner
 
     per_seq = -(-(CONTEXT + 8) // BLOCK)
     cfg = EngineConfig(dtype="bfloat16", block_size=BLOCK, num_blocks=batch * per_seq + 1, max_seqs=batch, max_len=CONTEXT + 8,
-                       max_num_batched_tokens=max(batch, 16))
+                       max_num_batched_tokens=max(batch, 16), cuda_graphs=graphs)
     spec, cache, runner = build_runner(folder, cfg)
     K = runner.K
     for b in runner.bindings:
@@ -138,17 +139,28 @@ def decode_point(engine_mod, folder: Path, batch: int, steps: int, warmup: int, 
         cache.admit(i)
         cache.reserve(i, 0, CONTEXT)
         entries.append(StepEntry(i, [(17 * i + 3) % MODEL["vocab_size"]], CONTEXT - 1, (0,)))
-    ctx, rows = runner.make_context(entries)
+    if graphs:
+        runner.step(entries)  # captures the graph for this batch size and leaves the step's inputs in its static buffer
+        cap = runner.graphs.captured[batch]
+        per_step = cap.launches + 1
 
-    def one():
-        ctx._tables.clear()
-        logits = runner.forward(ctx, rows)
-        return K.argmax(logits)
+        def one():
+            cap.graph.replay()
+            return K.argmax(cap.logits[:batch])
+    else:
+        ctx, rows = runner.make_context(entries)
+        n0 = K.launches
+
+        def one():
+            ctx._tables.clear()
+            return K.argmax(runner.forward(ctx, rows))
+
+        one()
+        per_step = K.launches - n0
 
     for _ in range(warmup):
         one()
     torch.cuda.synchronize()
-    n0 = K.launches
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record()
     for _ in range(steps):
@@ -156,7 +168,7 @@ def decode_point(engine_mod, folder: Path, batch: int, steps: int, warmup: int, 
     stop.record()
     torch.cuda.synchronize()
     ms = start.elapsed_time(stop) / steps
-    out = {"ms": ms, "tok_s": batch / ms * 1e3, "launches": K.launches - n0,
+    out = {"ms": ms, "tok_s": batch / ms * 1e3, "launches": per_step * steps,
            "bytes": runner.weight_bytes_per_step() + batch * CONTEXT * runner.kv_bytes_per_token}
     del runner, spec, cache
     torch.cuda.empty_cache()
@@ -191,7 +203,7 @@ def prefill_point(folder: Path, torch, reps: int = 3) -> dict:
     return {"ms": ms}
 
 
-def e2e_point(folder: Path, batch: int, steps: int, warmup: int, torch) -> dict:
+def e2e_point(folder: Path, batch: int, steps: int, warmup: int, torch, graphs: bool = True) -> dict:
     """``Engine.step()`` in a loop: host token lists in, sampled tokens out, after the engine prefilled the prompts itself."""
     from llm_infrence_engine_b200.engine import Engine, Request
 
@@ -199,7 +211,7 @@ def e2e_point(folder: Path, batch: int, steps: int, warmup: int, torch) -> dict:
     prompt_len = CONTEXT - total
     per_seq = -(-(CONTEXT + 8) // BLOCK)
     eng = Engine(str(folder), dtype="bfloat16", block_size=BLOCK, num_blocks=batch * per_seq + 1, max_seqs=batch,
-                 max_len=CONTEXT + 8, max_num_batched_tokens=2048)
+                 max_len=CONTEXT + 8, max_num_batched_tokens=2048, cuda_graphs=graphs)
     g = torch.Generator().manual_seed(9)
     reqs = [eng.add_request(Request(torch.randint(0, MODEL["vocab_size"], (prompt_len,), generator=g).tolist(), max_new_tokens=total))
             for _ in range(batch)]
@@ -232,6 +244,8 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=MODEL["num_hidden_layers"], help="fewer layers than the model has (named in config)")
     ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--no-graphs", action="store_true", help="launch every kernel of a decode step from the host instead of replaying a CUDA graph")
+    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"], help="measure one part only (for profiling); the JSON line then lacks the rest")
     a = ap.parse_args()
     if a.impl == "reference":
         return reference_arm()
@@ -239,10 +253,10 @@ def main() -> int:
         print(f"bench.py: this engine runs on one GPU; --gpus {a.gpus} is not supported")
         return 2
     a.warmup = max(a.warmup, 3)
+    graphs = not a.no_graphs
 
     import torch
 
-    import llm_infrence_engine_b200.engine as engine_mod
     from llm_infrence_engine_b200.weights import write_random_model
 
     pk = peaks()
@@ -252,12 +266,12 @@ def main() -> int:
         folder = write_random_model(model, Path(tmp) / "model", seed=0, store_dtype="bfloat16")
         sampler = ClockSampler()
         sampler.start()
-        main_pt = decode_point(engine_mod, folder, a.batch, a.steps, a.warmup, torch)
+        main_pt = decode_point(folder, a.batch, a.steps if a.only != "prefill" else 3, a.warmup, torch, graphs)
         clocks = sampler.stop()
-        b1 = decode_point(engine_mod, folder, 1, a.steps, a.warmup, torch)
-        b64 = decode_point(engine_mod, folder, 64, max(8, a.steps // 4), a.warmup, torch)
-        pre = prefill_point(folder, torch)
-        e2e = None if a.skip_e2e else e2e_point(folder, a.batch, a.steps, a.warmup, torch)
+        b1 = decode_point(folder, 1, a.steps, a.warmup, torch, graphs) if a.only == "all" else None
+        b64 = decode_point(folder, 64, max(8, a.steps // 4), a.warmup, torch, graphs) if a.only == "all" else None
+        pre = prefill_point(folder, torch) if a.only in ("all", "prefill") else None
+        e2e = None if (a.skip_e2e or a.only != "all") else e2e_point(folder, a.batch, a.steps, a.warmup, torch, graphs)
 
     fl = flops_prefill(PREFILL_TOKENS) * a.layers / MODEL["num_hidden_layers"]
     achieved = main_pt["bytes"] / (main_pt["ms"] * 1e-3) / 1e9
@@ -270,14 +284,15 @@ def main() -> int:
         "config": {"model": "Qwen2.5-0.5B shape", "layers": a.layers, "layers_of_model": MODEL["num_hidden_layers"],
                    "hidden": 896, "heads": 14, "kv_heads": 2, "head_dim": 64, "intermediate": 4864, "vocab": 151936,
                    "tied": True, "global_batch": a.batch, "seq_len": CONTEXT, "block_size": BLOCK, "parallelism": "single GPU",
-                   "l2": "inputs larger than L2 (weights + cache per step >> 126 MB), no flush", "peaks": pk["source"]},
+                   "cuda_graphs": graphs, "l2": "inputs larger than L2 (weights + cache per step >> 126 MB), no flush", "peaks": pk["source"]},
         "clocks": clocks,
         "gpu_launches": main_pt["launches"],
-        "prefill": {"value": round(PREFILL_TOKENS / (pre["ms"] * 1e-3), 1), "tokens": PREFILL_TOKENS, "ms": round(pre["ms"], 3),
-                    "frac": round(fl / (pre["ms"] * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)},
+        "prefill": None if pre is None else {
+            "value": round(PREFILL_TOKENS / (pre["ms"] * 1e-3), 1), "tokens": PREFILL_TOKENS, "ms": round(pre["ms"], 3),
+            "frac": round(fl / (pre["ms"] * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm_gbs"], 4)},
-        "points": {"decode_b1": round(b1["tok_s"], 1), "decode_b64": round(b64["tok_s"], 1)},
+        "points": None if b1 is None else {"decode_b1": round(b1["tok_s"], 1), "decode_b64": round(b64["tok_s"], 1)},
     }
     if e2e is not None:
         line["e2e"] = {k: (round(v, 2) if isinstance(v, float) else v) for k, v in e2e.items()}

@@ -69,12 +69,13 @@ class PagePool:
 class _Held:
     """What one live request holds."""
 
-    __slots__ = ("slot", "tables", "length")
+    __slots__ = ("slot", "tables", "length", "versions")
 
-    def __init__(self, slot: int, num_groups: int):
+    def __init__(self, slot: int, num_groups: int, version: int):
         self.slot = slot
         self.tables: List[List[int]] = [[] for _ in range(num_groups)]
         self.length = 0  # positions covered so far
+        self.versions = [version] * num_groups  # changes whenever the group's table changes; never repeats
 
 
 class CacheManager:
@@ -87,6 +88,7 @@ class CacheManager:
         self.pools = [PagePool(num_pages) for _ in self.groups]
         self._free_slots = deque(range(max_seqs))
         self._held: Dict[Hashable, _Held] = {}
+        self._version = 0
         self.max_blocks_per_seq = 0  # grows with the longest table seen; informational
 
     # ------------------------------------------------------------------ capacity
@@ -112,6 +114,15 @@ class CacheManager:
     def block_table(self, req: Hashable, group: int) -> List[int]:
         return self._held[req].tables[group]
 
+    def table_version(self, req: Hashable, group: int) -> int:
+        """A number that changes whenever the request's table in ``group`` changes and is never used twice,
+        so a mirror of the table (for instance on the device) knows when it is stale."""
+        return self._held[req].versions[group]
+
+    def _bump(self, held: "_Held", group: int) -> None:
+        self._version += 1
+        held.versions[group] = self._version
+
     # ------------------------------------------------------------------ lifecycle
     def admit(self, req: Hashable) -> int:
         """Give ``req`` a state slot and empty block tables; returns the slot."""
@@ -120,7 +131,8 @@ class CacheManager:
         if not self._free_slots:
             raise OutOfPages("no free state slot")
         slot = self._free_slots.popleft()
-        self._held[req] = _Held(slot, len(self.groups))
+        self._version += 1
+        self._held[req] = _Held(slot, len(self.groups), self._version)
         return slot
 
     def _first_needed_page(self, group: int, context_len: int) -> int:
@@ -168,11 +180,15 @@ class CacheManager:
             table = held.tables[g]
             want = -(-new_len // self.page_size)
             first = self._first_needed_page(g, context_len)
+            changed = len(table) < want
             while len(table) < want:
                 table.append(NULL_PAGE)
             for i in range(first, want):
                 if table[i] == NULL_PAGE:
                     table[i] = self.pools[g].allocate(req)
+                    changed = True
+            if changed:
+                self._bump(held, g)
             self.max_blocks_per_seq = max(self.max_blocks_per_seq, len(table))
         held.length = max(held.length, new_len)
 
@@ -184,11 +200,14 @@ class CacheManager:
             if self.groups[g].window is None:
                 continue
             table = held.tables[g]
+            before = n
             for i in range(min(self._first_needed_page(g, context_len), len(table))):
                 if table[i] != NULL_PAGE:
                     self.pools[g].free(table[i], req)
                     table[i] = NULL_PAGE
                     n += 1
+            if n != before:
+                self._bump(held, g)
         return n
 
     def free(self, req: Hashable) -> None:

@@ -43,7 +43,8 @@ def build_runner(folder: Union[str, Path], config: EngineConfig, kernels=None):
     groups, of_entry = group_layout(spec.cache_specs())
     num_pages = config.pool_blocks()
     cache = CacheManager(groups, num_pages, config.block_size, config.max_seqs)
-    runner = ModelRunner(spec, kernels, cache, of_entry, dtype, config.device, num_pages, config.block_size, config.max_seqs)
+    runner = ModelRunner(spec, kernels, cache, of_entry, dtype, config.device, num_pages, config.block_size, config.max_seqs,
+                         config.max_len, config.cuda_graphs)
     return spec, cache, runner
 
 

@@ -1,0 +1,102 @@
+"""Decode-only steps replayed from CUDA graphs, one graph per padded batch size.
+
+The reference captures its decode forward per batch size {1, 2, 4, ...} with static input buffers
+and parks padding rows in a scratch slot (src/miniserve/graph_decode.py:23-86), but only for its
+slot cache: its paged path rebuilds block tables on the host every step and cannot be captured
+(src/miniserve/engine.py:125-128). Here the block tables already live on the device, one row per
+state slot, so the captured step reads them in place; a step's own integers (token, position,
+table row, cache slot of every row) are copied into one static buffer before the replay. Padding
+rows carry token 0 at position 0, point at a table row of null pages and write their key and value
+into the null page, which nobody reads.
+
+A graph fixes the launch shapes, so the number of key slices per token is planned for ``max_len``;
+the kernel cuts each token's own keys into that many slices on the device, whatever its length.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Sequence
+
+import torch
+
+from .step import StateBinding, StepContext, StepEntry
+
+
+def bucket_sizes(max_batch: int) -> List[int]:
+    """1, 2, 4, ... up to and including ``max_batch`` (src/miniserve/graph_decode.py:23-30)."""
+    out, b = [], 1
+    while b < max_batch:
+        out.append(b)
+        b *= 2
+    out.append(max_batch)
+    return out
+
+
+class _Captured:
+    def __init__(self, graph, static_in, logits, launches):
+        self.graph, self.static_in, self.logits = graph, static_in, logits
+        self.launches = launches  # kernels that one replay launches
+
+
+class DecodeGraphs:
+    def __init__(self, runner):
+        self.runner = runner
+        self.usable = runner.device.type == "cuda" and all(getattr(p, "graph_safe", False) for p in runner.spec.parts()) \
+            and not any(isinstance(b, StateBinding) for b in runner.bindings)
+        self.buckets = bucket_sizes(runner.max_seqs)
+        self.captured: Dict[int, _Captured] = {}
+        self.pool = None
+        self.replays = 0
+
+    def fits(self, entries: Sequence[StepEntry]) -> bool:
+        return self.usable and len(entries) <= self.buckets[-1] and \
+            all(len(e.tokens) == 1 and e.context_len > 0 and len(e.want) == 1 for e in entries)
+
+    def _layout_len(self, B: int) -> int:
+        return B * (5 + len(self.runner.cache.groups))
+
+    def _capture(self, B: int) -> _Captured:
+        r = self.runner
+        static_in = torch.zeros(self._layout_len(B), dtype=torch.int32, device=r.device)
+        ctx = StepContext(r.K, r.dtype, r.device, r.page_size)
+        rows = r._fill_context(ctx, static_in, B, B, B)
+        ctx.seq_starts, ctx.seq_lens, ctx.seq_context = list(range(B)), [1] * B, [1] * B
+        ctx.seq_slot_list = [r.max_seqs] * B
+        ctx.max_context, ctx.max_seq_len = r.max_len, 1
+        # padding values, so that warm-up and capture run on harmless inputs
+        static_in[2 * B:3 * B] = r.max_seqs
+        static_in[4 * B:5 * B] = torch.arange(B, dtype=torch.int32, device=r.device)
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                ctx._tables.clear()
+                r.forward(ctx, rows)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        if self.pool is None:
+            self.pool = torch.cuda.graph_pool_handle()
+        ctx._tables.clear()
+        before = r.K.launches
+        with torch.cuda.graph(graph, pool=self.pool):
+            logits = r.forward(ctx, rows)
+        return _Captured(graph, static_in, logits, r.K.launches - before)
+
+    @torch.inference_mode()
+    def run(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        r = self.runner
+        n = len(entries)
+        B = next(b for b in self.buckets if b >= n)
+        if B not in self.captured:
+            self.captured[B] = self._capture(B)
+        cap = self.captured[B]
+        packed, N, R, M, changed, *_ = r._build(entries, pad_to=B)
+        dev = r._upload(packed, into=cap.static_in) if not changed else None
+        if changed:
+            # rows of block tables ride behind the step's own integers: stage everything once, then split on the device
+            full = r._upload(packed)
+            cap.static_in.copy_(full[: self._layout_len(B)])
+            r._sync_tables(full, changed)
+        cap.graph.replay()
+        self.replays += 1
+        return cap.logits[:n]

@@ -17,6 +17,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Dict, Hashable, List, Optional, Sequence
 
+import numpy as np
 import torch
 
 from ..cache.manager import CacheManager
@@ -59,9 +60,9 @@ class StepContext:
         self.num_seqs = 0
         self.token_ids: torch.Tensor = None      # [N] int32
         self.positions: torch.Tensor = None      # [N] int32, absolute, 0-based
-        self.token_seq: torch.Tensor = None      # [N] int32, index of the token's request within the step
+        self.token_seq: torch.Tensor = None      # [N] int32, the token's row in the block tables (= its request's state slot)
         self.seq_slots: torch.Tensor = None      # [R] int32, state slot of each request
-        self.block_tables: List[torch.Tensor] = []  # per group [R, max_blocks] int32
+        self.block_tables: List[torch.Tensor] = []  # per group [state slots + 1, max_blocks] int32, a row per state slot
         self.slot_mapping: List[torch.Tensor] = []  # per group [N] int32: page * page_size + offset of the token's key
         self.seq_starts: List[int] = []          # host: first row of each request in the flat batch
         self.seq_lens: List[int] = []            # host: rows of each request
@@ -80,10 +81,11 @@ class StepContext:
 
 class ModelRunner:
     def __init__(self, spec: ModelSpec, kernels, cache: CacheManager, group_of_entry: List[Optional[int]],
-                 dtype: torch.dtype, device, num_pages: int, page_size: int, max_seqs: int):
+                 dtype: torch.dtype, device, num_pages: int, page_size: int, max_seqs: int, max_len: int,
+                 cuda_graphs: bool = False):
         self.spec, self.K, self.cache = spec, kernels, cache
         self.dtype, self.device = dtype, torch.device(device)
-        self.page_size, self.max_seqs = page_size, max_seqs
+        self.page_size, self.max_seqs, self.max_len = page_size, max_seqs, max_len
         self.bindings: List[object] = []
         self.kv_bytes_per_token = 0
         specs = spec.cache_specs()
@@ -100,75 +102,93 @@ class ModelRunner:
                 self.bindings.append(None)
             else:
                 raise TypeError(f"cache entry {entry} has a spec of unknown kind {type(cs).__name__}")
+        # Block tables live on the device, one row per state slot (plus a last row of null pages that padding
+        # rows of a captured graph point at); a row is sent again only when the request's table has changed.
+        self.max_blocks = max(1, -(-max_len // page_size))
+        groups = len(cache.groups)
+        self.tables_dev = [torch.zeros((max_seqs + 1, self.max_blocks), dtype=torch.int32, device=self.device) for _ in range(groups)]
+        self._synced = [[-1] * max_seqs for _ in range(groups)]
         self._staging: List[list] = []  # ring of [pinned buffer, event of the copy that last read it]
         self._next_staging = 0
         self.last_h2d_bytes = 0  # bytes of step inputs copied to the device by the last step
+        self.graphs = None
+        if cuda_graphs:
+            from .graphs import DecodeGraphs
+
+            self.graphs = DecodeGraphs(self)
 
     # ------------------------------------------------------------------ building the step's inputs
-    def _build(self, entries: Sequence[StepEntry]) -> tuple:
+    def _build(self, entries: Sequence[StepEntry], pad_to: int = 0):
+        """The step's integers as one int32 array plus its layout. ``pad_to`` > 0 (decode-only steps replayed
+        from a graph) pads the batch to that many rows with tokens that write to the null page."""
         cache, ps = self.cache, self.page_size
         groups = len(cache.groups)
         vocab = self.spec.embedding.vocab
-        ids: List[int] = []
-        pos: List[int] = []
-        seq: List[int] = []
-        rows: List[int] = []
-        starts, lens, ctxs, slots = [], [], [], []
-        for r, e in enumerate(entries):
-            n = len(e.tokens)
+        R = len(entries)
+        if len(set(e.req for e in entries)) != R:
+            raise ValueError("a request appears twice in one step")
+        lens = [len(e.tokens) for e in entries]
+        ctxs = [int(e.context_len) for e in entries]
+        slots = [cache.slot(e.req) for e in entries]
+        for e, n in zip(entries, lens):
             if n == 0:
                 raise ValueError(f"request {e.req!r} brings no tokens to the step")
-            for t in e.tokens:
-                if not 0 <= int(t) < vocab:
-                    raise ValueError(f"request {e.req!r}: token {t} is outside the vocabulary of {vocab}")
+            if e.context_len + n > self.max_len:
+                raise ValueError(f"request {e.req!r} would reach {e.context_len + n} tokens, more than max_len {self.max_len}")
+        ids = np.concatenate([np.asarray(e.tokens, dtype=np.int64) for e in entries])
+        if ids.min() < 0 or ids.max() >= vocab:
+            bad = int(ids[(ids < 0) | (ids >= vocab)][0])
+            raise ValueError(f"token {bad} is outside the vocabulary of {vocab}")
+        pos = np.concatenate([np.arange(c, c + n, dtype=np.int64) for c, n in zip(ctxs, lens)])
+        starts = np.concatenate([[0], np.cumsum(lens)[:-1]]).astype(np.int64)
+        tok_slot = np.repeat(np.asarray(slots, dtype=np.int64), lens)
+        rows: List[int] = []
+        for st, e, n in zip(starts, entries, lens):
             for w in e.want:
                 if not 0 <= int(w) < n:
                     raise ValueError(f"request {e.req!r}: wanted place {w} is outside its {n} tokens")
-            starts.append(len(ids)); lens.append(n); ctxs.append(e.context_len); slots.append(cache.slot(e.req))
-            ids.extend(int(t) for t in e.tokens)
-            pos.extend(range(e.context_len, e.context_len + n))
-            seq.extend([r] * n)
-            rows.extend(starts[-1] + int(w) for w in e.want)
-        if len(set(e.req for e in entries)) != len(entries):
-            raise ValueError("a request appears twice in one step")
-        N, R, M = len(ids), len(entries), len(rows)
-        max_blocks = 1
-        for e in entries:
-            for g in range(groups):
-                max_blocks = max(max_blocks, len(cache.block_table(e.req, g)))
-        tables: List[List[int]] = []
-        mapping: List[List[int]] = []
+                rows.append(int(st) + int(w))
+        N, M = int(ids.shape[0]), len(rows)
+        pad = max(0, pad_to - N)
+        parts = [ids, np.zeros(pad, np.int64), pos, np.zeros(pad, np.int64), tok_slot, np.full(pad, self.max_seqs, np.int64),
+                 np.asarray(slots, dtype=np.int64), np.zeros(pad, np.int64),
+                 np.asarray(rows, dtype=np.int64), np.arange(N, N + pad, dtype=np.int64) if pad_to else np.zeros(0, np.int64)]
+        changed = []  # (group, slot, offset of the row in the packed array)
+        offset = sum(len(p) for p in parts)
         for g in range(groups):
-            flat_table: List[int] = []
-            flat_map: List[int] = []
-            for e in entries:
+            maps = []
+            for e, c, n in zip(entries, ctxs, lens):
                 t = cache.block_table(e.req, g)
-                need = -(-(e.context_len + len(e.tokens)) // ps)
-                if len(t) < need:
-                    raise ValueError(f"request {e.req!r} has {len(t)} pages in group {g} but the step needs {need}")
-                flat_table.extend(t)
-                flat_table.extend([NULL_PAGE] * (max_blocks - len(t)))
-                for p in range(e.context_len, e.context_len + len(e.tokens)):
-                    page = t[p // ps]
-                    if page == NULL_PAGE:
-                        raise ValueError(f"request {e.req!r}: position {p} has no page in group {g}")
-                    flat_map.append(page * ps + p % ps)
-            tables.append(flat_table)
-            mapping.append(flat_map)
-        packed = ids + pos + seq + slots + rows
+                if len(t) * ps < c + n:
+                    raise ValueError(f"request {e.req!r} has {len(t)} pages in group {g} but the step needs {-(-(c + n) // ps)}")
+                p = np.arange(c, c + n, dtype=np.int64)
+                pages = np.asarray(t, dtype=np.int64)[p // ps]
+                if (pages == NULL_PAGE).any():
+                    raise ValueError(f"request {e.req!r}: a position of the step has no page in group {g}")
+                maps.append(pages * ps + p % ps)
+            parts += maps + [np.zeros(pad, np.int64)]
+            offset += N + pad
         for g in range(groups):
-            packed += mapping[g] + tables[g]
-        return packed, N, R, M, max_blocks, starts, lens, ctxs, slots
+            for e, slot in zip(entries, slots):
+                v = cache.table_version(e.req, g)
+                if self._synced[g][slot] != v:
+                    t = cache.block_table(e.req, g)
+                    if len(t) > self.max_blocks:
+                        raise ValueError(f"request {e.req!r} holds {len(t)} pages, more than max_len allows")
+                    row = np.zeros(self.max_blocks, np.int64)
+                    row[:len(t)] = t
+                    parts.append(row)
+                    changed.append((g, slot, offset, v))
+                    offset += self.max_blocks
+        packed = np.concatenate(parts).astype(np.int32)
+        return packed, N + pad, R + pad, M + (pad if pad_to else 0), changed, [int(x) for x in starts], lens, ctxs, slots
 
-    def _upload(self, packed: List[int]) -> torch.Tensor:
-        """One asynchronous copy of the step's integers from pinned memory. The staging buffers form a
-        ring: a buffer is written again only after the copy that last read it has finished, because
-        the host may run several steps ahead of the device when nothing is read back in between."""
-        n = len(packed)
+    def _stage(self, packed: "np.ndarray") -> torch.Tensor:
+        """The pinned buffer that holds ``packed`` for one asynchronous copy. The buffers form a ring: one is
+        written again only after the copy that last read it has finished, because the host may run
+        several steps ahead of the device when nothing is read back in between."""
+        n = int(packed.shape[0])
         self.last_h2d_bytes = 4 * n
-        host = torch.tensor(packed, dtype=torch.int32)
-        if self.device.type != "cuda":
-            return host.to(self.device)
         if not self._staging:
             self._staging = [[None, None] for _ in range(4)]
         slot = self._staging[self._next_staging]
@@ -177,16 +197,45 @@ class ModelRunner:
             slot[1].synchronize()
         if slot[0] is None or slot[0].numel() < n:
             slot[0] = torch.empty(max(2 * n, 8192), dtype=torch.int32, pin_memory=True)
-        slot[0][:n].copy_(host)
-        dev = slot[0][:n].to(self.device, non_blocking=True)
-        slot[1] = torch.cuda.Event()
-        slot[1].record()
+        slot[0][:n].copy_(torch.from_numpy(packed))
+        self._last_slot = slot
+        return slot[0][:n]
+
+    def _upload(self, packed: "np.ndarray", into: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if self.device.type != "cuda":
+            dev = torch.from_numpy(packed).to(self.device)
+            if into is not None:
+                into[: dev.numel()].copy_(dev)
+                return into
+            return dev
+        pinned = self._stage(packed)
+        if into is not None:
+            into[: pinned.numel()].copy_(pinned, non_blocking=True)
+            dev = into
+        else:
+            dev = pinned.to(self.device, non_blocking=True)
+        self._last_slot[1] = torch.cuda.Event()
+        self._last_slot[1].record()
         return dev
 
-    def make_context(self, entries: Sequence[StepEntry]):
-        packed, N, R, M, max_blocks, starts, lens, ctxs, slots = self._build(entries)
-        dev = self._upload(packed)
+    def _sync_tables(self, dev: torch.Tensor, changed) -> None:
+        for g, slot, off, version in changed:
+            self.tables_dev[g][slot].copy_(dev[off:off + self.max_blocks])
+            self._synced[g][slot] = version
+
+    def make_context(self, entries: Sequence[StepEntry], pad_to: int = 0, into: Optional[torch.Tensor] = None):
+        packed, N, R, M, changed, starts, lens, ctxs, slots = self._build(entries, pad_to)
+        dev = self._upload(packed, into)
+        self._sync_tables(dev, changed)
         ctx = StepContext(self.K, self.dtype, self.device, self.page_size)
+        logit_rows = self._fill_context(ctx, dev, N, R, M)
+        ctx.seq_starts, ctx.seq_lens, ctx.seq_context, ctx.seq_slot_list = starts, lens, ctxs, slots
+        ctx.max_context = max(c + n for c, n in zip(ctxs, lens))
+        ctx.max_seq_len = max(lens)
+        return ctx, logit_rows
+
+    def _fill_context(self, ctx: StepContext, dev: torch.Tensor, N: int, R: int, M: int) -> torch.Tensor:
+        """Point the context's tensors at their places in the packed device array (layout of ``_build``)."""
         ctx.num_tokens, ctx.num_seqs = N, R
         o = 0
         ctx.token_ids = dev[o:o + N]; o += N
@@ -194,13 +243,11 @@ class ModelRunner:
         ctx.token_seq = dev[o:o + N]; o += N
         ctx.seq_slots = dev[o:o + R]; o += R
         logit_rows = dev[o:o + M]; o += M
+        ctx.slot_mapping, ctx.block_tables = [], []
         for g in range(len(self.cache.groups)):
             ctx.slot_mapping.append(dev[o:o + N]); o += N
-            ctx.block_tables.append(dev[o:o + R * max_blocks].view(R, max_blocks)); o += R * max_blocks
-        ctx.seq_starts, ctx.seq_lens, ctx.seq_context, ctx.seq_slot_list = starts, lens, ctxs, slots
-        ctx.max_context = max(c + n for c, n in zip(ctxs, lens))
-        ctx.max_seq_len = max(lens)
-        return ctx, logit_rows
+            ctx.block_tables.append(self.tables_dev[g])
+        return logit_rows
 
     # ------------------------------------------------------------------ the step
     @torch.inference_mode()
@@ -209,6 +256,8 @@ class ModelRunner:
         entries and of their ``want``, or None if nothing was wanted."""
         if not entries:
             return None
+        if self.graphs is not None and self.graphs.fits(entries):
+            return self.graphs.run(entries)
         ctx, logit_rows = self.make_context(entries)
         fresh = [s for s, c in zip(ctx.seq_slot_list, ctx.seq_context) if c == 0]
         if fresh:

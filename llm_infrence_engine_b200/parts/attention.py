@@ -21,6 +21,8 @@ class PagedAttention(Mixer):
     request, or ``p - window + 1 .. p`` when ``window`` is set; the mask is never a tensor.
     """
 
+    graph_safe = True
+
     def __init__(self, hidden: int, num_heads: int, num_kv_heads: int, head_dim: int, position: PositionEncoding,
                  prefix: str, bias: bool = True, window: Optional[int] = None, scale: Optional[float] = None):
         if num_heads % num_kv_heads:

@@ -60,6 +60,10 @@ class ParamSpec:
 class Part:
     """Base of every part: named tensors in, ``bind`` once, then ``forward`` every step."""
 
+    # True if ``forward`` only launches kernels on the current stream and reads nothing of the step on the
+    # host (no host lists of the context, no synchronisation): such a part can be captured in a CUDA graph.
+    graph_safe = False
+
     def params(self) -> Dict[str, ParamSpec]:
         return {}
 

@@ -16,6 +16,8 @@ class PreNormBlock(Part):
     same kernel as its norm: ``forward`` takes the addend still owed to ``x`` and returns the new one.
     """
 
+    graph_safe = True
+
     def __init__(self, norm1: Norm, mixer: Mixer, norm2: Norm, ff: FeedForward):
         self.norm1, self.mixer, self.norm2, self.ff = norm1, mixer, norm2, ff
 

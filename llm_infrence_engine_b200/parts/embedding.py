@@ -11,6 +11,8 @@ from .base import MATRIX, ParamSpec, Part, Source
 class TokenEmbedding(Part):
     """``x = table[token]`` with no scaling (src/miniserve/model.py:229), widened into the 32-bit residual stream."""
 
+    graph_safe = True
+
     def __init__(self, vocab: int, hidden: int, name: str):
         self.vocab, self.hidden, self.name = vocab, hidden, name
         self.table: Optional[torch.Tensor] = None
@@ -25,6 +27,8 @@ class TokenEmbedding(Part):
 class OutputHead(Part):
     """``logits = h W^T`` without bias, in 32-bit. ``tied_to`` makes ``W`` the embedding's own table
     (src/miniserve/model.py:204-206); a tensor of the head's name in the checkpoint is then not needed."""
+
+    graph_safe = True
 
     def __init__(self, vocab: int, hidden: int, name: str, tied_to: Optional[TokenEmbedding] = None):
         self.vocab, self.hidden, self.name, self.tied_to = vocab, hidden, name, tied_to

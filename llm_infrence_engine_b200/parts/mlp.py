@@ -17,6 +17,8 @@ class GatedMLP(FeedForward):
     step multiplies once; the activation and the product are one kernel over its output.
     """
 
+    graph_safe = True
+
     def __init__(self, hidden: int, intermediate: int, prefix: str, activation: str = "silu"):
         if activation not in ACTIVATIONS:
             raise ValueError(f"activation '{activation}' is not one of {ACTIVATIONS}")

@@ -15,6 +15,8 @@ class RMSNorm(Norm):
     (src/miniserve/model.py:69-73). ``eps`` sits inside the square root, added to the mean.
     """
 
+    graph_safe = True
+
     def __init__(self, dim: int, eps: float, weight_name: str):
         self.dim = dim
         self.eps = float(eps)

@@ -14,6 +14,8 @@ class RotaryEncoding(PositionEncoding):
     ``cos`` and ``sin`` on every forward (model.py:86-88), here the step does it once for all layers.
     """
 
+    graph_safe = True
+
     def __init__(self, head_dim: int, theta: float):
         if head_dim % 2:
             raise ValueError(f"rotary head_dim must be even, got {head_dim}")

@@ -211,3 +211,37 @@ def test_trace_run_program(models, tmp_path):
     assert not (out / "1.f32").exists()
     check(s0, want["c"][[0, 29]], "float32", "step 0")
     check(s2, torch.stack([want["c"][len(p) - 1], want["c"][4]]), "float32", "step 2")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_decode_from_cuda_graphs_matches_eager(models, dtype):
+    """Decode-only steps replayed from captured graphs (padded batch sizes included) give the eager step's logits."""
+    from llm_infrence_engine_b200.config import EngineConfig
+    from llm_infrence_engine_b200.engine import StepEntry, build_runner
+
+    folder, cfg, w, prompts, want = models[("A", dtype)]
+    out = {}
+    for graphs in (False, True):
+        ec = EngineConfig(dtype=dtype, block_size=16, num_blocks=40, max_seqs=6, max_len=160, max_num_batched_tokens=256, cuda_graphs=graphs)
+        spec, cache, runner = build_runner(folder, ec)
+        keys = ["a", "b", "c"]
+        for k in keys:
+            cache.admit(k)
+            cache.reserve(k, 0, 33)
+        runner.step([StepEntry(k, prompts[k][:33], 0, ()) for k in keys])
+        got = []
+        for i in range(33, 60):   # crosses page edges at 48; batch of 3 is padded to 4
+            for k in keys:
+                cache.reserve(k, i, i + 1)
+            got.append(runner.step([StepEntry(k, [prompts[k][i]], i, (0,)) for k in keys]).float().cpu())
+        cache.free("b")             # then a batch of 2, exactly a captured size
+        for i in range(60, 64):
+            for k in ("a", "c"):
+                cache.reserve(k, i, i + 1)
+            got.append(runner.step([StepEntry(k, [prompts[k][i]], i, (0,)) for k in ("a", "c")]).float().cpu())
+        out[graphs] = torch.cat(got)
+        if graphs:
+            assert runner.graphs.replays == 27 + 4 and sorted(runner.graphs.captured) == [2, 4]
+    assert torch.equal(out[True], out[False])
+    ref = torch.stack([want[k][i] for i in range(33, 60) for k in ("a", "b", "c")] + [want[k][i] for i in range(60, 64) for k in ("a", "c")])
+    check(out[True], ref, dtype, "graph decode vs plain")
