@@ -1,0 +1,491 @@
+// Paged grouped-query attention in bfloat16 on the tensor cores (mma.sync m16n8k16, 32-bit
+// accumulators and a 32-bit online softmax), for head sizes 64 and 128.
+//
+// The rows of a tile are (token, query head of the group) pairs of ONE key/value head, token-major:
+// row r is token n0 + r / G, head kvh * G + r % G (G = query heads per key/value head). All rows of
+// a tile read the same keys and values, so a page is fetched once for the whole group.
+//
+//   decode kernel   one tile = up to 16 rows (one token of up to 16 heads, or a few tokens). The four
+//                   warps of a block split the KEYS: each warp streams its own 64-key (or 32-key)
+//                   chunks through a private cp.async ring, keeps its own running (max, sum, output)
+//                   and the warps are merged in shared memory at the end.
+//   prefill kernel  one tile = up to 64 rows (64 / G consecutive tokens of one request). The four warps
+//                   split the ROWS, 16 each; the block loads 64-key chunks together, double buffered.
+//
+// Both cut a tile's key range into `num_splits` slices (blockIdx.z). With more than one slice every
+// block writes its partial (max, sum, output) to scratch; the block that arrives last at the tile's
+// counter merges the slices and writes the output row, so no second kernel is needed. Keys are found
+// through the request's block-table row, chunk by chunk; a query at position p sees keys
+// max(0, p - window + 1) .. p, the mask is computed from positions, never stored.
+#include <math.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int WARPS = 4;
+constexpr float LOG2E = 1.4426950408889634f;
+
+struct Params {
+    const bf16* q;          // [tokens][q_stride], query heads first
+    const bf16* k_pool;     // [pages][nkv][page_size][D]
+    const bf16* v_pool;
+    const int* block_table; // [table rows][max_blocks]
+    const int* token_seq;   // [tokens] row of the block table
+    const int* positions;   // [tokens]
+    const int* tile_info;   // [tiles][2] = (first token, tokens) or null: tile i is token i alone
+    bf16* out;              // [tokens][nq * D]
+    float* part_o;          // [tiles][nkv][splits][ROWS][D]
+    float* part_ml;         // [tiles][nkv][splits][ROWS][2]
+    int* counters;          // [tiles * nkv], zero between launches
+    int q_stride, max_blocks, nq, nkv, page_size, window, num_splits;
+    float scale_log2;       // softmax scale * log2(e)
+};
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+    const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gmem));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem) {
+    const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem) {
+    const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+// Element (row, col) of a [rows][D] bfloat16 tile in shared memory; 16-byte chunks of a row are
+// permuted by the row's low bits so that the 8 rows one ldmatrix phase reads fall on different banks.
+template <int D> __device__ __forceinline__ int swz(int row, int col) { return row * D + ((((col >> 3) ^ (row & 7)) << 3) | (col & 7)); }
+
+// Copy `keys` cache rows starting at absolute key `key0` (clamped to `last_key`) into a swizzled tile.
+template <int D, int THREADS>
+__device__ __forceinline__ void load_kv_tile(const Params& p, const int* table, int kvh, int key0, int last_key, int keys, bf16* ks,
+                                             bf16* vs, int tid) {
+    constexpr int CH = D / 8;
+    for (int idx = tid; idx < keys * CH; idx += THREADS) {
+        const int key = idx / CH, ch = idx % CH;
+        const int ka = min(key0 + key, last_key);
+        const int page = table[ka / p.page_size];
+        const size_t row = ((size_t)page * p.nkv + kvh) * p.page_size + ka % p.page_size;
+        const int dst = key * D + ((ch ^ (key & 7)) << 3);
+        cp_async16(ks + dst, p.k_pool + row * D + ch * 8);
+        cp_async16(vs + dst, p.v_pool + row * D + ch * 8);
+    }
+}
+
+// One chunk of BN keys for one warp's 16 rows: S = Q K^T, masked online softmax, O += P V.
+template <int D, int BN>
+__device__ __forceinline__ void attend_chunk(const uint32_t (&qa)[D / 16][4], const bf16* ks, const bf16* vs, float (&o)[D / 8][4],
+                                             float (&m)[2], float (&l)[2], int key0, const int (&row_pos)[2], const bool (&row_ok)[2],
+                                             int window, float scale_log2, int lane) {
+    float s[BN / 8][4];
+#pragma unroll
+    for (int i = 0; i < BN / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk) {
+#pragma unroll
+        for (int nt = 0; nt < BN / 16; ++nt) {
+            uint32_t b[4];
+            const int key = nt * 16 + (lane & 7) + ((lane >> 4) << 3);
+            const int col = kk * 16 + (((lane >> 3) & 1) << 3);
+            ldmatrix_x4(b, ks + swz<D>(key, col));
+            mma_bf16(s[2 * nt], qa[kk], b[0], b[1]);
+            mma_bf16(s[2 * nt + 1], qa[kk], b[2], b[3]);
+        }
+    }
+    // mask and running maximum, in units of log2: x = s * scale * log2(e)
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int nt = 0; nt < BN / 8; ++nt) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int r = e >> 1;
+            const int key = key0 + nt * 8 + ((lane & 3) << 1) + (e & 1);
+            const bool ok = row_ok[r] && key <= row_pos[r] && (window <= 0 || key > row_pos[r] - window);
+            const float x = ok ? s[nt][e] * scale_log2 : -INFINITY;
+            s[nt][e] = x;
+            mx[r] = fmaxf(mx[r], x);
+        }
+    }
+    float corr[2], use[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+        const float m_new = fmaxf(m[r], mx[r]);
+        use[r] = m_new == -INFINITY ? 0.f : m_new;
+        corr[r] = exp2f(m[r] - use[r]);
+        m[r] = m_new;
+        l[r] *= corr[r];
+    }
+#pragma unroll
+    for (int dt = 0; dt < D / 8; ++dt) {
+        o[dt][0] *= corr[0]; o[dt][1] *= corr[0];
+        o[dt][2] *= corr[1]; o[dt][3] *= corr[1];
+    }
+    uint32_t pa[BN / 16][4];
+#pragma unroll
+    for (int nt = 0; nt < BN / 8; ++nt) {
+        const float p0 = exp2f(s[nt][0] - use[0]), p1 = exp2f(s[nt][1] - use[0]);
+        const float p2 = exp2f(s[nt][2] - use[1]), p3 = exp2f(s[nt][3] - use[1]);
+        l[0] += p0 + p1;
+        l[1] += p2 + p3;
+        pa[nt >> 1][(nt & 1) * 2] = pack_bf16(p0, p1);
+        pa[nt >> 1][(nt & 1) * 2 + 1] = pack_bf16(p2, p3);
+    }
+#pragma unroll
+    for (int kk = 0; kk < BN / 16; ++kk) {
+#pragma unroll
+        for (int dt = 0; dt < D / 16; ++dt) {
+            uint32_t b[4];
+            const int key = kk * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
+            const int col = dt * 16 + ((lane >> 4) << 3);
+            ldmatrix_x4_trans(b, vs + swz<D>(key, col));
+            mma_bf16(o[2 * dt], pa[kk], b[0], b[1]);
+            mma_bf16(o[2 * dt + 1], pa[kk], b[2], b[3]);
+        }
+    }
+}
+
+// The block's finished rows are in shared memory as (max, sum, output); write them out, or, with
+// several key slices, store the partial and let the last block of the tile merge all slices.
+template <int D, int ROWS, int THREADS>
+__device__ __forceinline__ void finish_tile(const Params& p, const float* row_m, const float* row_l, const float* row_o, int tile,
+                                            int kvh, int split, int n0, int nrows, int G, int* flag_smem) {
+    const int tid = threadIdx.x;
+    if (p.num_splits == 1) {
+        for (int i = tid; i < nrows * D; i += THREADS) {
+            const int r = i / D, dim = i % D;
+            const float L = row_l[r];
+            const float val = L > 0.f ? row_o[r * D + dim] / L : 0.f;
+            p.out[(size_t)(n0 + r / G) * p.nq * D + (size_t)(kvh * G + r % G) * D + dim] = __float2bfloat16_rn(val);
+        }
+        return;
+    }
+    const size_t base = ((size_t)tile * p.nkv + kvh) * p.num_splits;
+    float* po = p.part_o + (base + split) * ROWS * D;
+    float* pml = p.part_ml + (base + split) * ROWS * 2;
+    for (int i = tid; i < nrows * D; i += THREADS) po[i] = row_o[i];
+    for (int r = tid; r < nrows; r += THREADS) { pml[2 * r] = row_m[r]; pml[2 * r + 1] = row_l[r]; }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        const int prev = atomicAdd(p.counters + tile * p.nkv + kvh, 1);
+        *flag_smem = prev == p.num_splits - 1;
+    }
+    __syncthreads();
+    if (!*flag_smem) return;
+    __threadfence();
+    for (int i = tid; i < nrows * D; i += THREADS) {
+        const int r = i / D, dim = i % D;
+        float M = -INFINITY;
+        for (int s = 0; s < p.num_splits; ++s) M = fmaxf(M, __ldcg(p.part_ml + (base + s) * ROWS * 2 + 2 * r));
+        float L = 0.f, O = 0.f;
+        if (M > -INFINITY) {
+            for (int s = 0; s < p.num_splits; ++s) {
+                const float f = exp2f(__ldcg(p.part_ml + (base + s) * ROWS * 2 + 2 * r) - M);
+                L = fmaf(__ldcg(p.part_ml + (base + s) * ROWS * 2 + 2 * r + 1), f, L);
+                O = fmaf(__ldcg(p.part_o + (base + s) * ROWS * D + i), f, O);
+            }
+        }
+        p.out[(size_t)(n0 + r / G) * p.nq * D + (size_t)(kvh * G + r % G) * D + dim] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+    }
+    if (tid == 0) p.counters[tile * p.nkv + kvh] = 0;  // ready for the next launch
+}
+
+// ---------------------------------------------------------------------------------------------- decode
+template <int D, int BN, int STAGES>
+__global__ void __launch_bounds__(WARPS * 32) attn_mma_decode_kernel(const Params p) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    constexpr int TILE = BN * D;                       // elements of one K or V chunk
+    bf16* my = reinterpret_cast<bf16*>(smem_raw) + (size_t)warp * STAGES * 2 * TILE;
+    __shared__ int flag;
+
+    const int tile = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+    const int n0 = p.tile_info ? p.tile_info[2 * tile] : tile;
+    const int ntok = p.tile_info ? p.tile_info[2 * tile + 1] : 1;
+    const int G = p.nq / p.nkv;
+    const int nrows = ntok * G;  // <= 16
+    const int pos0 = p.positions[n0];
+    const int* table = p.block_table + (size_t)p.token_seq[n0] * p.max_blocks;
+    const int hi = pos0 + ntok;  // one past the last visible key
+    const int lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+    const int chunks = (hi - lo + BN - 1) / BN;
+    const int per = (chunks + p.num_splits - 1) / p.num_splits;
+    const int c_begin = split * per, c_end = min(chunks, c_begin + per);
+
+    int row_pos[2];
+    bool row_ok[2];
+    uint32_t qa[D / 16][4];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int row = (lane >> 2) + 8 * r;
+        row_ok[r] = row < nrows;
+        row_pos[r] = pos0 + row / G;
+        const bf16* qp = p.q + (size_t)(n0 + (row_ok[r] ? row / G : 0)) * p.q_stride + (size_t)(kvh * G + (row_ok[r] ? row % G : 0)) * D;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+            const int col = kk * 16 + ((lane & 3) << 1);
+            qa[kk][r] = row_ok[r] ? *reinterpret_cast<const uint32_t*>(qp + col) : 0u;
+            qa[kk][r + 2] = row_ok[r] ? *reinterpret_cast<const uint32_t*>(qp + col + 8) : 0u;
+        }
+    }
+    float o[D / 8][4];
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+
+    // this warp's chunks: c_begin + warp, + WARPS, ...
+    const int first = c_begin + warp;
+    const int mine = first < c_end ? (c_end - first + WARPS - 1) / WARPS : 0;
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; ++s) {
+        if (s < mine) load_kv_tile<D, 32>(p, table, kvh, lo + (first + s * WARPS) * BN, hi - 1, BN, my + s * 2 * TILE, my + s * 2 * TILE + TILE, lane);
+        cp_async_commit();
+    }
+    for (int it = 0; it < mine; ++it) {
+        const int nxt = it + STAGES - 1;
+        if (nxt < mine) {
+            bf16* dst = my + (nxt % STAGES) * 2 * TILE;
+            load_kv_tile<D, 32>(p, table, kvh, lo + (first + nxt * WARPS) * BN, hi - 1, BN, dst, dst + TILE, lane);
+        }
+        cp_async_commit();
+        cp_async_wait<STAGES - 1>();
+        __syncwarp();
+        const bf16* cur = my + (it % STAGES) * 2 * TILE;
+        attend_chunk<D, BN>(qa, cur, cur + TILE, o, m, l, lo + (first + it * WARPS) * BN, row_pos, row_ok, p.window, p.scale_log2, lane);
+        __syncwarp();
+    }
+    cp_async_wait<0>();
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+    }
+    __syncthreads();  // every warp is done with its ring; the space is reused for the merge
+    float* wm = reinterpret_cast<float*>(smem_raw);        // [WARPS][16]
+    float* wl = wm + WARPS * 16;                           // [WARPS][16]
+    float* wo = wl + WARPS * 16;                           // [WARPS][16][D]
+    float* fm = wo + WARPS * 16 * D;                       // merged [16], [16], [16][D]
+    float* fl = fm + 16;
+    float* fo = fl + 16;
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int row = (lane >> 2) + 8 * r;
+        if ((lane & 3) == 0) { wm[warp * 16 + row] = m[r]; wl[warp * 16 + row] = l[r]; }
+#pragma unroll
+        for (int dt = 0; dt < D / 8; ++dt) {
+            const int col = dt * 8 + ((lane & 3) << 1);
+            wo[(warp * 16 + row) * D + col] = o[dt][2 * r];
+            wo[(warp * 16 + row) * D + col + 1] = o[dt][2 * r + 1];
+        }
+    }
+    __syncthreads();
+    for (int i = tid; i < 16 * D; i += WARPS * 32) {
+        const int r = i / D, dim = i % D;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) M = fmaxf(M, wm[w * 16 + r]);
+        float L = 0.f, O = 0.f;
+        if (M > -INFINITY) {
+#pragma unroll
+            for (int w = 0; w < WARPS; ++w) {
+                const float f = exp2f(wm[w * 16 + r] - M);
+                L = fmaf(wl[w * 16 + r], f, L);
+                O = fmaf(wo[(w * 16 + r) * D + dim], f, O);
+            }
+        }
+        fo[i] = O;
+        if (dim == 0) { fm[r] = M; fl[r] = L; }
+    }
+    __syncthreads();
+    finish_tile<D, 16, WARPS * 32>(p, fm, fl, fo, tile, kvh, split, n0, nrows, G, &flag);
+}
+
+// ---------------------------------------------------------------------------------------------- prefill
+template <int D>
+__global__ void __launch_bounds__(WARPS * 32) attn_mma_prefill_kernel(const Params p) {
+    constexpr int BM = 64, BN = 64, TILE = BN * D;
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    bf16* qs = reinterpret_cast<bf16*>(smem_raw);   // [BM][D]
+    bf16* kv = qs + BM * D;                         // [2 stages][K, V][BN][D]
+    __shared__ int flag;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int tile = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+    const int n0 = p.tile_info ? p.tile_info[2 * tile] : tile;
+    const int ntok = p.tile_info ? p.tile_info[2 * tile + 1] : 1;
+    const int G = p.nq / p.nkv;
+    const int nrows = ntok * G;  // <= 64
+    const int pos0 = p.positions[n0];
+    const int* table = p.block_table + (size_t)p.token_seq[n0] * p.max_blocks;
+    const int hi = pos0 + ntok;
+    const int lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+    const int chunks = (hi - lo + BN - 1) / BN;
+    const int per = (chunks + p.num_splits - 1) / p.num_splits;
+    const int c_begin = split * per, c_end = min(chunks, c_begin + per);
+
+    // queries of the tile into shared memory (zeros for rows beyond the tile), first key chunk behind them
+    constexpr int CH = D / 8;
+    for (int idx = tid; idx < BM * CH; idx += WARPS * 32) {
+        const int row = idx / CH, ch = idx % CH;
+        bf16* dst = qs + row * D + ((ch ^ (row & 7)) << 3);
+        if (row < nrows) cp_async16(dst, p.q + (size_t)(n0 + row / G) * p.q_stride + (size_t)(kvh * G + row % G) * D + ch * 8);
+        else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+    }
+    if (c_begin < c_end) load_kv_tile<D, WARPS * 32>(p, table, kvh, lo + c_begin * BN, hi - 1, BN, kv, kv + TILE, tid);
+    cp_async_commit();
+
+    int row_pos[2];
+    bool row_ok[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int row = warp * 16 + (lane >> 2) + 8 * r;
+        row_ok[r] = row < nrows;
+        row_pos[r] = pos0 + row / G;
+    }
+    const int warp_last_pos = pos0 + min(ntok - 1, (warp * 16 + 15) / G);  // the furthest key any row of this warp sees
+    const int warp_first_pos = pos0 + min(ntok - 1, (warp * 16) / G);
+    const bool warp_has_rows = warp * 16 < nrows;
+
+    uint32_t qa[D / 16][4];
+    float o[D / 8][4];
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+
+    for (int c = c_begin; c < c_end; ++c) {
+        const int stage = (c - c_begin) & 1;
+        if (c + 1 < c_end) {
+            bf16* dst = kv + (stage ^ 1) * 2 * TILE;
+            load_kv_tile<D, WARPS * 32>(p, table, kvh, lo + (c + 1) * BN, hi - 1, BN, dst, dst + TILE, tid);
+        }
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        if (c == c_begin) {
+#pragma unroll
+            for (int kk = 0; kk < D / 16; ++kk) {
+                const int row = warp * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
+                const int col = kk * 16 + ((lane >> 4) << 3);
+                ldmatrix_x4(qa[kk], qs + swz<D>(row, col));
+            }
+        }
+        const int key0 = lo + c * BN;
+        const bool visible = warp_has_rows && key0 <= warp_last_pos && (p.window <= 0 || key0 + BN - 1 > warp_first_pos - p.window);
+        if (visible) {
+            const bf16* cur = kv + stage * 2 * TILE;
+            attend_chunk<D, BN>(qa, cur, cur + TILE, o, m, l, key0, row_pos, row_ok, p.window, p.scale_log2, lane);
+        }
+        __syncthreads();
+    }
+    cp_async_wait<0>();
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+    }
+    __syncthreads();
+    float* fm = reinterpret_cast<float*>(smem_raw);  // [64], [64], [64][D]: reuses the tiles' space
+    float* fl = fm + BM;
+    float* fo = fl + BM;
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int row = warp * 16 + (lane >> 2) + 8 * r;
+        if ((lane & 3) == 0) { fm[row] = m[r]; fl[row] = l[r]; }
+#pragma unroll
+        for (int dt = 0; dt < D / 8; ++dt) {
+            const int col = dt * 8 + ((lane & 3) << 1);
+            fo[row * D + col] = o[dt][2 * r];
+            fo[row * D + col + 1] = o[dt][2 * r + 1];
+        }
+    }
+    __syncthreads();
+    finish_tile<D, BM, WARPS * 32>(p, fm, fl, fo, tile, kvh, split, n0, nrows, G, &flag);
+}
+
+// tile list of a step: request r brings tokens [starts[r], starts[r + 1]); tiles hold up to `per_tile` tokens of one request
+__global__ void attn_plan_kernel(const int* __restrict__ starts, int num_seqs, int per_tile, int* __restrict__ tile_info, int max_tiles) {
+    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    int t = 0;
+    for (int r = 0; r < num_seqs; ++r) {
+        for (int a = starts[r]; a < starts[r + 1] && t < max_tiles; a += per_tile, ++t) {
+            tile_info[2 * t] = a;
+            tile_info[2 * t + 1] = min(per_tile, starts[r + 1] - a);
+        }
+    }
+    for (; t < max_tiles; ++t) { tile_info[2 * t] = 0; tile_info[2 * t + 1] = 0; }
+}
+
+template <int D>
+int launch(const Params& p, int num_tiles, int decode_mode, cudaStream_t s) {
+    const dim3 grid(num_tiles, p.nkv, p.num_splits);
+    if (decode_mode) {
+        constexpr int BN = D == 64 ? 64 : 32, STAGES = 3;
+        constexpr size_t ring = (size_t)WARPS * STAGES * 2 * BN * D * sizeof(bf16);
+        constexpr size_t merge = (size_t)(WARPS * 16 * (D + 2) + 16 * (D + 2)) * sizeof(float);
+        constexpr size_t smem = ring > merge ? ring : merge;
+        static bool set = false;
+        if (!set) {
+            cudaError_t e = cudaFuncSetAttribute(attn_mma_decode_kernel<D, BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return (int)e;
+            set = true;
+        }
+        attn_mma_decode_kernel<D, BN, STAGES><<<grid, WARPS * 32, smem, s>>>(p);
+    } else {
+        constexpr size_t tiles = (size_t)(64 * D + 2 * 2 * 64 * D) * sizeof(bf16);
+        constexpr size_t merge = (size_t)(64 * (D + 2)) * sizeof(float);
+        constexpr size_t smem = tiles > merge ? tiles : merge;
+        static bool set = false;
+        if (!set) {
+            cudaError_t e = cudaFuncSetAttribute(attn_mma_prefill_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return (int)e;
+            set = true;
+        }
+        attn_mma_prefill_kernel<D><<<grid, WARPS * 32, smem, s>>>(p);
+    }
+    return launch_status();
+}
+
+}  // namespace
+
+LLMIE_API int llmie_attn_plan(const int* seq_starts, int num_seqs, int tokens_per_tile, int* tile_info, int max_tiles, cudaStream_t s) {
+    if (num_seqs <= 0 || max_tiles <= 0) return 0;
+    if (tokens_per_tile <= 0) return LLMIE_ERR_BAD_ARGUMENT;
+    attn_plan_kernel<<<1, 32, 0, s>>>(seq_starts, num_seqs, tokens_per_tile, tile_info, max_tiles);
+    return launch_status();
+}
+
+// decode_mode 1: every tile has at most 16 rows (tokens * group). 0: at most 64 rows.
+// scratch_o / scratch_ml / counters are needed for num_splits > 1 (counters zeroed once; the kernel leaves them zero).
+LLMIE_API int llmie_paged_attention_mma(const bf16* q, int q_stride, const bf16* k_pool, const bf16* v_pool, const int* block_table,
+                                        int max_blocks, const int* token_seq, const int* positions, const int* tile_info, int num_tiles,
+                                        bf16* out, float* scratch_o, float* scratch_ml, int* counters, int nq, int nkv, int d,
+                                        int page_size, float scale, int window, int num_splits, int decode_mode, cudaStream_t s) {
+    if (num_tiles <= 0) return 0;
+    if ((d != 64 && d != 128) || nkv <= 0 || nq % nkv || page_size <= 0 || num_splits < 1 || q_stride % 8 || nkv > 65535 ||
+        num_splits > 65535 || (num_splits > 1 && (!scratch_o || !scratch_ml || !counters)))
+        return LLMIE_ERR_BAD_ARGUMENT;
+    const int G = nq / nkv;
+    if (G > (decode_mode ? 16 : 64)) return LLMIE_ERR_BAD_ARGUMENT;
+    Params p;
+    p.q = q; p.k_pool = k_pool; p.v_pool = v_pool; p.block_table = block_table; p.token_seq = token_seq; p.positions = positions;
+    p.tile_info = tile_info; p.out = out; p.part_o = scratch_o; p.part_ml = scratch_ml; p.counters = counters;
+    p.q_stride = q_stride; p.max_blocks = max_blocks; p.nq = nq; p.nkv = nkv; p.page_size = page_size; p.window = window;
+    p.num_splits = num_splits; p.scale_log2 = scale * LOG2E;
+    return d == 64 ? launch<64>(p, num_tiles, decode_mode, s) : launch<128>(p, num_tiles, decode_mode, s);
+}

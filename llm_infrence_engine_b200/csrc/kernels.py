@@ -43,9 +43,11 @@ class CudaKernels:
         self.launches = 0
         self.use_cublas = True
         self._attn_scratch: Optional[torch.Tensor] = None
+        self._attn_counters: Optional[torch.Tensor] = None
+        self.use_mma_attention = True
         self.num_sms = torch.cuda.get_device_properties(0).multi_processor_count or NUM_SMS_FALLBACK
         for fn in ("llmie_embed", "llmie_rope_tables", "llmie_add_rmsnorm", "llmie_rope_kv_write", "llmie_silu_mul",
-                   "llmie_gemm_simt", "llmie_paged_attention_f32", "llmie_paged_attention_bf16", "llmie_argmax", "llmie_sample"):
+                   "llmie_gemm_simt", "llmie_attn_plan", "llmie_paged_attention_mma", "llmie_paged_attention_f32", "llmie_paged_attention_bf16", "llmie_argmax", "llmie_sample"):
             getattr(self.lib, fn).restype = ctypes.c_int
 
     # ------------------------------------------------------------------ helpers
@@ -178,7 +180,11 @@ class CudaKernels:
         return self._attn_scratch
 
     def paged_attention(self, qkv, k_pool, v_pool, block_table, token_seq, positions, num_heads, num_kv_heads, head_dim,
-                        page_size, scale, window, max_context, num_splits=None):
+                        page_size, scale, window, max_context, batch=None, num_splits=None):
+        """Attention of every token of the step over its request's pages. ``batch`` (the step's context, or
+        anything with ``seq_lens``, ``seq_starts_dev``, ``max_seq_len`` and a ``_tables`` dict) lets bfloat16
+        inputs with head size 64 or 128 take the tensor-core kernels; without it, or for other types and
+        sizes, the generic kernel runs."""
         self._need(qkv, "qkv", None, 2)
         dt = self._dt(qkv, "qkv")
         N = qkv.shape[0]
@@ -198,8 +204,14 @@ class CudaKernels:
         self._need(positions, "positions", torch.int32, 1)
         if block_table.shape[1] * page_size < max_context:
             raise KernelError(f"paged_attention: block tables of {block_table.shape[1]} pages cannot hold {max_context} tokens")
-        splits = num_splits or self.attention_splits(N, num_kv_heads, min(max_context, window) if window else max_context)
         out = torch.empty((N, num_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
+        group = num_heads // num_kv_heads
+        span = min(max_context, window) if window else max_context
+        if (self.use_mma_attention and batch is not None and dt == 1 and head_dim in (64, 128)
+                and group <= (16 if batch.max_seq_len == 1 else 64)):
+            return self._attention_mma(qkv, k_pool, v_pool, block_table, token_seq, positions, out, num_heads, num_kv_heads,
+                                       head_dim, page_size, scale, window, span, batch, num_splits)
+        splits = num_splits or self.attention_splits(N, num_kv_heads, span)
         scratch = self._scratch(N * num_heads * splits * (head_dim + 2), qkv.device) if splits > 1 else None
         fn = self.lib.llmie_paged_attention_f32 if dt == 0 else self.lib.llmie_paged_attention_bf16
         self._check(fn(_ptr(qkv), qkv.shape[1], _ptr(k_pool), _ptr(v_pool), _ptr(block_table), block_table.shape[1],
@@ -207,6 +219,44 @@ class CudaKernels:
                        ctypes.c_float(scale), int(window), splits, self._stream()), "paged_attention")
         if splits > 1:
             self.launches += 1
+        return out
+
+    def _attention_mma(self, qkv, k_pool, v_pool, block_table, token_seq, positions, out, num_heads, num_kv_heads, head_dim,
+                       page_size, scale, window, span, batch, num_splits):
+        group = num_heads // num_kv_heads
+        decode = batch.max_seq_len == 1
+        N = qkv.shape[0]
+        if decode:
+            tiles, tile_info, rows, chunk = N, None, 16, (64 if head_dim == 64 else 32)
+        else:
+            per_tile = max(1, 64 // group)
+            tiles = sum(-(-n // per_tile) for n in batch.seq_lens)
+            key = ("attention tiles", per_tile)
+            if key not in batch._tables:
+                info = torch.empty((tiles, 2), dtype=torch.int32, device=qkv.device)
+                self._check(self.lib.llmie_attn_plan(_ptr(batch.seq_starts_dev), len(batch.seq_lens), per_tile, _ptr(info), tiles,
+                                                     self._stream()), "attention plan")
+                batch._tables[key] = info
+            tile_info, rows, chunk = batch._tables[key], 64, 64
+        chunks = max(1, -(-span // chunk))
+        if num_splits is None:
+            blocks = max(1, tiles * num_kv_heads)
+            num_splits = max(1, min(self.num_sms // blocks, chunks // (4 if decode else 8), 64))
+        scratch_o = scratch_ml = counters = None
+        if num_splits > 1:
+            cells = tiles * num_kv_heads * num_splits * rows
+            buf = self._scratch(cells * (head_dim + 2), qkv.device)
+            scratch_o, scratch_ml = buf, buf[cells * head_dim:]
+            if tiles * num_kv_heads > (1 << 20):
+                raise KernelError("paged_attention: too many tiles for the split counters")
+            if self._attn_counters is None or self._attn_counters.device != qkv.device:
+                self._attn_counters = torch.zeros(1 << 20, dtype=torch.int32, device=qkv.device)
+            counters = self._attn_counters
+        self._check(self.lib.llmie_paged_attention_mma(
+            _ptr(qkv), qkv.shape[1], _ptr(k_pool), _ptr(v_pool), _ptr(block_table), block_table.shape[1], _ptr(token_seq),
+            _ptr(positions), _ptr(tile_info), tiles, _ptr(out), _ptr(scratch_o), _ptr(scratch_ml), _ptr(counters), num_heads,
+            num_kv_heads, head_dim, page_size, ctypes.c_float(scale), int(window), num_splits, int(decode), self._stream()),
+            "paged_attention (tensor cores)")
         return out
 
     def silu_mul(self, gu):

@@ -52,7 +52,7 @@ class DecodeGraphs:
             all(len(e.tokens) == 1 and e.context_len > 0 and len(e.want) == 1 for e in entries)
 
     def _layout_len(self, B: int) -> int:
-        return B * (5 + len(self.runner.cache.groups))
+        return B * (5 + len(self.runner.cache.groups)) + 1
 
     def _capture(self, B: int) -> _Captured:
         r = self.runner
@@ -64,7 +64,8 @@ class DecodeGraphs:
         ctx.max_context, ctx.max_seq_len = r.max_len, 1
         # padding values, so that warm-up and capture run on harmless inputs
         static_in[2 * B:3 * B] = r.max_seqs
-        static_in[4 * B:5 * B] = torch.arange(B, dtype=torch.int32, device=r.device)
+        static_in[4 * B:5 * B + 1] = torch.arange(B + 1, dtype=torch.int32, device=r.device)
+        static_in[5 * B + 1:6 * B + 1] = torch.arange(B, dtype=torch.int32, device=r.device)
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):

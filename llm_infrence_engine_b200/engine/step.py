@@ -62,6 +62,7 @@ class StepContext:
         self.positions: torch.Tensor = None      # [N] int32, absolute, 0-based
         self.token_seq: torch.Tensor = None      # [N] int32, the token's row in the block tables (= its request's state slot)
         self.seq_slots: torch.Tensor = None      # [R] int32, state slot of each request
+        self.seq_starts_dev: torch.Tensor = None  # [R + 1] int32, first row of each request in the flat batch, then N
         self.block_tables: List[torch.Tensor] = []  # per group [state slots + 1, max_blocks] int32, a row per state slot
         self.slot_mapping: List[torch.Tensor] = []  # per group [N] int32: page * page_size + offset of the token's key
         self.seq_starts: List[int] = []          # host: first row of each request in the flat batch
@@ -152,6 +153,7 @@ class ModelRunner:
         pad = max(0, pad_to - N)
         parts = [ids, np.zeros(pad, np.int64), pos, np.zeros(pad, np.int64), tok_slot, np.full(pad, self.max_seqs, np.int64),
                  np.asarray(slots, dtype=np.int64), np.zeros(pad, np.int64),
+                 starts, np.arange(N, N + pad + 1, dtype=np.int64),
                  np.asarray(rows, dtype=np.int64), np.arange(N, N + pad, dtype=np.int64) if pad_to else np.zeros(0, np.int64)]
         changed = []  # (group, slot, offset of the row in the packed array)
         offset = sum(len(p) for p in parts)
@@ -242,6 +244,7 @@ class ModelRunner:
         ctx.positions = dev[o:o + N]; o += N
         ctx.token_seq = dev[o:o + N]; o += N
         ctx.seq_slots = dev[o:o + R]; o += R
+        ctx.seq_starts_dev = dev[o:o + R + 1]; o += R + 1
         logit_rows = dev[o:o + M]; o += M
         ctx.slot_mapping, ctx.block_tables = [], []
         for g in range(len(self.cache.groups)):

@@ -59,5 +59,5 @@ class PagedAttention(Mixer):
                         self.num_heads, self.num_kv_heads, self.head_dim, ctx.page_size, cache.write)
         attn = K.paged_attention(qkv, cache.k, cache.v, ctx.block_tables[cache.group], ctx.token_seq, ctx.positions,
                                  self.num_heads, self.num_kv_heads, self.head_dim, ctx.page_size, self.scale,
-                                 self.window or 0, ctx.max_context)
+                                 self.window or 0, ctx.max_context, batch=ctx)
         return K.linear(attn, self.w_o)

@@ -230,3 +230,45 @@ def test_sample_frequencies(K):
                    torch.ones(M).cuda(), u.cuda()).cpu()
     freq = torch.bincount(got.long(), minlength=6).double() / M
     assert (freq - plain_logits_to_probs(logits, 0.9).double()).abs().max() < 0.03
+
+
+class _Batch:
+    """What the tensor-core attention needs to know of a step: rows per request, on host and device."""
+
+    def __init__(self, qlens):
+        self.seq_lens = list(qlens)
+        self.max_seq_len = max(qlens)
+        starts = [0]
+        for n in qlens:
+            starts.append(starts[-1] + n)
+        self.seq_starts_dev = torch.tensor(starts, dtype=torch.int32).cuda()
+        self._tables = {}
+
+
+@pytest.mark.parametrize("nq,nkv,d,ps,lens,qlens,window,splits", [
+    (14, 2, 64, 16, [300, 700, 5, 64, 65], [1, 1, 1, 1, 1], 0, None),      # decode, 7 heads per group
+    (14, 2, 64, 16, [8200, 100], [1, 1], 0, 5),                              # decode, long context, slices merged in the kernel
+    (12, 2, 128, 16, [513, 31], [1, 1], 0, 3),                               # head size 128, 6 per group
+    (16, 1, 64, 32, [257, 1], [1, 1], 0, 2),                                 # 16 heads on one key/value head; a request of one token
+    (4, 4, 64, 8, [90], [1], 40, None),                                      # window, no grouping
+    (14, 2, 64, 16, [300, 77, 500], [300, 1, 37], 0, None),                  # prefill rows with a decode token and a late portion between
+    (14, 2, 64, 16, [1000], [1000], 0, None),                                # a long prompt whole
+    (14, 2, 64, 16, [2100], [16], 0, 4),                                     # a short portion far into a long request, sliced
+    (12, 2, 128, 16, [150, 64], [150, 2], 0, None),
+    (6, 3, 64, 16, [200, 130], [200, 5], 48, None),                          # window in prefill
+    (8, 8, 128, 64, [129], [129], 0, 2),
+    (28, 4, 128, 16, [70], [70], 0, None),
+])
+def test_paged_attention_tensor_cores(K, nq, nkv, d, ps, lens, qlens, window, splits):
+    for spike in (False, True):
+        qkv, kp, vp, table, tseq, pos = _attention_case(torch.bfloat16, nq, nkv, d, ps, lens, qlens, window, 11, spike)
+        scale = 1.0 / math.sqrt(d)
+        want = REF.paged_attention(qkv, kp, vp, table, tseq, pos, nq, nkv, d, ps, scale, window, max(lens))
+        before = K.launches
+        got = K.paged_attention(qkv.cuda(), kp.cuda(), vp.cuda(), table.cuda(), tseq.cuda(), pos.cuda(), nq, nkv, d, ps, scale,
+                                window, max(lens), batch=_Batch(qlens), num_splits=splits)
+        close(got, want, 1e-2)
+        # twice in a row: the slice counters must be back at zero
+        got = K.paged_attention(qkv.cuda(), kp.cuda(), vp.cuda(), table.cuda(), tseq.cuda(), pos.cuda(), nq, nkv, d, ps, scale,
+                                window, max(lens), batch=_Batch(qlens), num_splits=splits)
+        close(got, want, 1e-2)

@@ -66,7 +66,7 @@ class TorchKernels:
             v_pool[page, :, off] = v
 
     def paged_attention(self, qkv, k_pool, v_pool, block_table, token_seq, positions, num_heads, num_kv_heads, head_dim,
-                        page_size, scale, window, max_context):
+                        page_size, scale, window, max_context, batch=None, num_splits=None):
         N = qkv.shape[0]
         d = head_dim
         rep = num_heads // num_kv_heads
