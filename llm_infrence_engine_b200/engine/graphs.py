@@ -52,7 +52,8 @@ class DecodeGraphs:
             all(len(e.tokens) == 1 and e.context_len > 0 and len(e.want) == 1 for e in entries)
 
     def _layout_len(self, B: int) -> int:
-        return B * (5 + len(self.runner.cache.groups)) + 1
+        # ids, positions, table rows, state slots, first rows (B + 1), wanted rows, then one cache slot per group
+        return B * (6 + len(self.runner.cache.groups)) + 1
 
     def _capture(self, B: int) -> _Captured:
         r = self.runner
