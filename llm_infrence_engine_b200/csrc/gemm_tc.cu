@@ -1,0 +1,277 @@
+// out[m, n] (+)= sum_k x[m, k] * w[n, k] for FEW rows m (a decode batch): the weights stream through the
+// 5th-generation tensor cores of sm_100a at memory speed.
+//
+// The product is computed transposed ("swap A/B"): a tile of 128 weight rows is the M side of
+// tcgen05.mma (cta_group::1, kind::f16, bfloat16 in, 32-bit accumulate), the TN <= 64 token rows are its
+// N side, so no tensor-core work is wasted on padding tokens up to 128. Operands reach shared memory by
+// TMA (cp.async.bulk.tensor, 128-byte swizzle, no multicast) through a ring of STAGES buffers guarded by
+// mbarriers; the accumulator D[128 x TN] lives in tensor memory and is read back with tcgen05.ld.
+//
+//   warp 0, one lane   producer: waits for a free stage, arms its barrier with the byte count, issues the
+//                      two TMA loads (weight tile 128 x 64, token tile TN x 64; rows or columns outside the
+//                      matrices arrive as zeros)
+//   warp 1, one lane   issues 4 MMAs (K = 16 each) per stage, commits the stage back to the producer,
+//                      and after the last stage commits the accumulator barrier
+//   all 4 warps        epilogue: each thread owns one weight row n (TMEM lane) and TN token columns;
+//                      it stores, or adds with red.global.add.f32 when the K range is split over blocks
+//
+// grid = (ceil(N / 128), ceil(M / TN), k_splits). Splitting K gives small matrices enough blocks to pull
+// the whole memory system; the partial sums meet in the float32 output by atomic addition, which is
+// also how a projection adds itself into the residual stream without a separate kernel.
+//
+// Every wait on an mbarrier is bounded: after SPIN_LIMIT polls the block records an error in
+// `error_flag`, stops issuing work, lets the copies it started land (again bounded), frees its tensor
+// memory and returns. The host reads the flag and raises.
+#include <cuda.h>
+#include <cudaTypedefs.h>
+
+#include <map>
+#include <mutex>
+#include <tuple>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int BM = 128, BK = 64, STAGES = 4, UMMA_K = 16;
+constexpr uint32_t SPIN_LIMIT = 1u << 22;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait. False means: gave up (and said so in *abort_flag / *error_flag) or someone else already had.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* error_flag, int code) {
+    for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (i > 64) __nanosleep(40);
+    }
+    *abort_flag = 1;
+    atomicExch(error_flag, code);
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::"r"(
+                     smem_u32(dst)), "l"(map), "r"(c0), "r"(c1), "r"(smem_u32(bar)) : "memory");
+}
+// Shared-memory operand descriptor: K-major tile whose rows are 128 bytes, 128-byte swizzle, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);  // start address / 16
+    d |= (uint64_t)1 << 16;                        // leading byte offset (not used by this layout)
+    d |= (uint64_t)(1024 >> 4) << 32;              // stride byte offset / 16
+    d |= (uint64_t)1 << 46;                        // descriptor version of sm_100
+    d |= (uint64_t)2 << 61;                        // 128-byte swizzle
+    return d;
+}
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(d_tmem),
+                 "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* v) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]),
+                   "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+                 : "r"(taddr) : "memory");
+}
+
+template <int TN>
+__global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
+                                                      float* __restrict__ out, int ldo, int M, int N, int K, int kb_per_split,
+                                                      int accumulate, int* error_flag) {
+    constexpr int W_BYTES = BM * BK * 2, X_BYTES = TN * BK * 2, STAGE_BYTES = W_BYTES + X_BYTES;
+    constexpr int COLS = TN < 32 ? 32 : TN;  // tensor-memory columns: a power of two, at least 32
+    extern __shared__ unsigned char raw[];
+    unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~(uintptr_t)1023);
+    uint64_t* full = reinterpret_cast<uint64_t*>(tiles + STAGES * STAGE_BYTES);
+    uint64_t* empty = full + STAGES;
+    uint64_t* accum = empty + STAGES;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum + 1);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    volatile int* issued = abort_flag + 1;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n0 = blockIdx.x * BM, m0 = blockIdx.y * TN;
+    const int nkb = (K + BK - 1) / BK;
+    const int kb0 = blockIdx.z * kb_per_split, kb1 = min(nkb, kb0 + kb_per_split);
+    const int iters = kb1 - kb0;
+
+    if (tid == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, 1); }
+        mbar_init(accum, 1);
+        *abort_flag = 0;
+        *issued = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 0) {
+        __syncwarp();  // lane 0 comes back from the initialisation above: the allocation is a warp-wide instruction
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_slot)), "n"(COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 0 && lane == 0) {
+        asm volatile("prefetch.tensormap [%0];\n" ::"l"(&tmap_w) : "memory");
+        asm volatile("prefetch.tensormap [%0];\n" ::"l"(&tmap_x) : "memory");
+        for (int it = 0; it < iters; ++it) {
+            const int s = it % STAGES;
+            if (it >= STAGES && !mbar_wait(empty + s, ((it / STAGES) & 1) ^ 1, abort_flag, error_flag, 1)) break;
+            unsigned char* st = tiles + s * STAGE_BYTES;
+            mbar_expect_tx(full + s, STAGE_BYTES);
+            tma_load_2d(st, &tmap_w, (kb0 + it) * BK, n0, full + s);
+            tma_load_2d(st + W_BYTES, &tmap_x, (kb0 + it) * BK, m0, full + s);
+            *issued = it + 1;
+        }
+    } else if (warp == 1 && lane == 0) {
+        // instruction descriptor: D float32, A and B bfloat16, both K-major, N = TN, M = 128
+        constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+        bool ok = true;
+        for (int it = 0; it < iters && ok; ++it) {
+            const int s = it % STAGES;
+            ok = mbar_wait(full + s, (it / STAGES) & 1, abort_flag, error_flag, 2);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            const uint32_t a_addr = smem_u32(tiles + s * STAGE_BYTES);
+            const uint64_t a_desc = umma_desc(a_addr), b_desc = umma_desc(a_addr + W_BYTES);
+#pragma unroll
+            for (int k = 0; k < BK / UMMA_K; ++k)
+                umma_bf16(tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (it > 0 || k > 0) ? 1u : 0u);  // +32 bytes per K step
+            umma_commit(empty + s);
+        }
+        if (ok) umma_commit(accum);
+    }
+    __syncwarp();
+    const bool done = __all_sync(0xffffffffu, mbar_wait(accum, 0, abort_flag, error_flag, 3));  // uniform per warp: tcgen05.ld is warp-wide
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    if (done) {
+        const int n = n0 + warp * 32 + lane;
+        const int rows = min(TN, M - m0);
+#pragma unroll
+        for (int c = 0; c < TN; c += 16) {
+            uint32_t v[16];
+            tmem_ld16(tmem + ((uint32_t)(warp * 32) << 16) + c, v);
+            asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+            if (n < N) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const int m = c + j;
+                    if (m < rows) {
+                        float* dst = out + (size_t)(m0 + m) * ldo + n;
+                        if (accumulate) atomicAdd(dst, __uint_as_float(v[j]));
+                        else *dst = __uint_as_float(v[j]);
+                    }
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    if (!done && tid == 0) {
+        // gave up somewhere: let the copies that were started land before the block's shared memory goes away
+        const int n_issued = *issued;
+        for (int it = max(0, n_issued - STAGES); it < n_issued; ++it) {
+            for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
+                if (mbar_try_wait(full + it % STAGES, (it / STAGES) & 1)) break;
+                __nanosleep(40);
+            }
+        }
+    }
+    __syncthreads();
+    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "n"(COLS) : "memory");
+}
+
+// ------------------------------------------------------------------------------------------------ host side
+PFN_cuTensorMapEncodeTiled_v12000 g_encode = nullptr;
+std::mutex g_lock;
+std::map<std::tuple<const void*, int, int, int>, CUtensorMap> g_maps;  // (base, rows, K, box rows) -> descriptor
+
+int get_encoder() {
+    if (g_encode) return 0;
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
+    if (e != cudaSuccess) return (int)e;
+    if (q != cudaDriverEntryPointSuccess || !fn) return LLMIE_ERR_BAD_ARGUMENT;
+    g_encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(fn);
+    return 0;
+}
+
+// A [rows, K] row-major bfloat16 matrix, read in boxes of box_rows x 64 elements with 128-byte swizzle; outside: zeros.
+int tensor_map(const void* base, int rows, int K, int box_rows, CUtensorMap* out) {
+    std::lock_guard<std::mutex> hold(g_lock);
+    const auto key = std::make_tuple(base, rows, K, box_rows);
+    auto it = g_maps.find(key);
+    if (it != g_maps.end()) { *out = it->second; return 0; }
+    int rc = get_encoder();
+    if (rc) return rc;
+    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    CUtensorMap m;
+    const CUresult r = g_encode(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return LLMIE_ERR_BAD_ARGUMENT;
+    if (g_maps.size() > 4096) g_maps.clear();
+    g_maps[key] = m;
+    *out = m;
+    return 0;
+}
+
+template <int TN>
+int launch(const CUtensorMap& mw, const CUtensorMap& mx, float* out, int ldo, int M, int N, int K, int k_splits, int accumulate,
+           int* error_flag, cudaStream_t s) {
+    constexpr size_t smem = (size_t)STAGES * (BM * BK * 2 + TN * BK * 2) + 1024 + 256;
+    static bool set = false;
+    if (!set) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<TN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        set = true;
+    }
+    const int nkb = (K + BK - 1) / BK;
+    const int per = (nkb + k_splits - 1) / k_splits;
+    const int splits = (nkb + per - 1) / per;  // no empty split
+    const dim3 grid((N + BM - 1) / BM, (M + TN - 1) / TN, splits);
+    gemm_tc_kernel<TN><<<grid, 128, smem, s>>>(mw, mx, out, ldo, M, N, K, per, accumulate, error_flag);
+    return launch_status();
+}
+
+}  // namespace
+
+// x [M, K] and w [N, K] bfloat16 row-major (K a multiple of 8, bases 16-byte aligned), out float32 with row stride ldo.
+// accumulate = 0 needs k_splits = 1 and stores; accumulate = 1 adds atomically into what `out` holds.
+LLMIE_API int llmie_gemm_tc(const bf16* x, const bf16* w, float* out, int ldo, int M, int N, int K, int k_splits, int accumulate,
+                            int* error_flag, cudaStream_t s) {
+    if (M <= 0 || N <= 0) return 0;
+    if (K <= 0 || K % 8 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15) || k_splits < 1 || (!accumulate && k_splits != 1) || !error_flag ||
+        ldo < N)
+        return LLMIE_ERR_BAD_ARGUMENT;
+    const int TN = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+    CUtensorMap mw, mx;
+    int rc = tensor_map(w, N, K, BM, &mw);
+    if (rc) return rc;
+    rc = tensor_map(x, M, K, TN, &mx);
+    if (rc) return rc;
+    if (TN == 16) return launch<16>(mw, mx, out, ldo, M, N, K, k_splits, accumulate, error_flag, s);
+    if (TN == 32) return launch<32>(mw, mx, out, ldo, M, N, K, k_splits, accumulate, error_flag, s);
+    return launch<64>(mw, mx, out, ldo, M, N, K, k_splits, accumulate, error_flag, s);
+}

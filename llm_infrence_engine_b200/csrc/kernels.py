@@ -45,9 +45,11 @@ class CudaKernels:
         self._attn_scratch: Optional[torch.Tensor] = None
         self._attn_counters: Optional[torch.Tensor] = None
         self.use_mma_attention = True
+        self.use_tc_gemm = True
+        self._error_flag: Optional[torch.Tensor] = None
         self.num_sms = torch.cuda.get_device_properties(0).multi_processor_count or NUM_SMS_FALLBACK
         for fn in ("llmie_embed", "llmie_rope_tables", "llmie_add_rmsnorm", "llmie_rope_kv_write", "llmie_silu_mul",
-                   "llmie_gemm_simt", "llmie_attn_plan", "llmie_paged_attention_mma", "llmie_paged_attention_f32", "llmie_paged_attention_bf16", "llmie_argmax", "llmie_sample"):
+                   "llmie_gemm_simt", "llmie_gemm_tc", "llmie_attn_plan", "llmie_paged_attention_mma", "llmie_paged_attention_f32", "llmie_paged_attention_bf16", "llmie_argmax", "llmie_sample"):
             getattr(self.lib, fn).restype = ctypes.c_int
 
     # ------------------------------------------------------------------ helpers
@@ -140,6 +142,47 @@ class CudaKernels:
         self._check(self.lib.llmie_gemm_simt(_ptr(x), _ptr(w), _ptr(out), M, N, K, self._dt(x, "x"), self._dt(out, "out"),
                                              self._stream()), "linear")
         return out
+
+    def tc_splits(self, M: int, N: int, K: int) -> int:
+        """How many blocks share the K range of a small-batch product: enough blocks to draw on the whole memory
+        system (about two per SM), but no more atomic additions than the weights are worth."""
+        tiles = -(-N // 128) * -(-M // 64)
+        nkb = -(-K // 64)
+        want = max(1, (2 * self.num_sms) // tiles)
+        cap = max(1, (4 << 20) // max(1, M * N))
+        return max(1, min(want, nkb, cap))
+
+    def linear_tc(self, x, w, out=None, accumulate=False, k_splits=None):
+        """``out (+)= x w^T`` in float32 from bfloat16 operands on the tcgen05 tensor cores, for small batches.
+        ``accumulate`` adds into ``out`` (which may be a strided view, e.g. the residual stream) atomically."""
+        self._need(x, "x", torch.bfloat16, 2)
+        self._need(w, "w", torch.bfloat16, 2)
+        M, K, N = x.shape[0], x.shape[1], w.shape[0]
+        if w.shape[1] != K:
+            raise KernelError(f"linear_tc: x has {K} columns, w has {w.shape[1]}")
+        if K % 8:
+            raise KernelError(f"linear_tc: the inner size {K} must be a multiple of 8 (rows are fetched in 16-byte units)")
+        if out is None:
+            if accumulate:
+                raise KernelError("linear_tc: accumulate needs an output to add into")
+            out = torch.empty((M, N), dtype=torch.float32, device=x.device)
+        if out.dtype != torch.float32 or out.dim() != 2 or tuple(out.shape) != (M, N) or out.stride(1) != 1:
+            raise KernelError("linear_tc: out must be float32 [rows of x, rows of w] with unit column stride")
+        if self._error_flag is None:
+            self._error_flag = torch.zeros(1, dtype=torch.int32, device=x.device)
+        if k_splits is None:
+            k_splits = self.tc_splits(M, N, K) if accumulate else 1
+        self._check(self.lib.llmie_gemm_tc(_ptr(x), _ptr(w), _ptr(out), out.stride(0), M, N, K, int(k_splits), int(bool(accumulate)),
+                                           _ptr(self._error_flag), self._stream()), "linear_tc")
+        return out
+
+    def check_device_errors(self) -> None:
+        """Raise if a kernel gave up on a bounded wait since the last check (reads one integer back)."""
+        if self._error_flag is not None:
+            code = int(self._error_flag.item())
+            if code:
+                self._error_flag.zero_()
+                raise KernelError(f"a tensor-core GEMM block gave up waiting on a barrier (stage {code}); its output is not valid")
 
     def rope_kv_write(self, qkv, bias, cos, sin, slot_mapping, k_pool, v_pool, num_heads, num_kv_heads, head_dim, page_size,
                       write_kv=True):

@@ -272,3 +272,38 @@ def test_paged_attention_tensor_cores(K, nq, nkv, d, ps, lens, qlens, window, sp
         got = K.paged_attention(qkv.cuda(), kp.cuda(), vp.cuda(), table.cuda(), tseq.cuda(), pos.cuda(), nq, nkv, d, ps, scale,
                                 window, max(lens), batch=_Batch(qlens), num_splits=splits)
         close(got, want, 1e-2)
+
+
+@pytest.mark.parametrize("M,N,K_,splits,accumulate", [
+    (1, 128, 64, 1, False),
+    (8, 1152, 896, 1, False),
+    (8, 9728, 896, 3, True),
+    (8, 896, 4864, 19, True),        # many blocks add into the same rows
+    (64, 896, 896, 14, True),
+    (40, 200, 72, 2, True),          # ragged: N and K are no multiples of the tile
+    (17, 3000, 896, 1, False),
+    (100, 384, 256, None, True),     # more rows than one token tile
+    (5, 151936, 896, 1, False),      # the output head
+])
+def test_linear_tc(K, M, N, K_, splits, accumulate):
+    g = torch.Generator().manual_seed(8)
+    x = torch.randn(M, K_, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K_, generator=g) * 0.1).to(torch.bfloat16)
+    base = torch.randn(M, N, generator=g)
+    want = x.double() @ w.double().T + (base.double() if accumulate else 0)
+    for _ in range(2):
+        out = base.clone().cuda() if accumulate else None
+        got = K.linear_tc(x.cuda(), w.cuda(), out=out, accumulate=accumulate, k_splits=splits)
+        K.check_device_errors()
+        close(got, want, 2e-5)
+
+
+def test_linear_tc_into_a_strided_view(K):
+    g = torch.Generator().manual_seed(9)
+    x = torch.randn(6, 128, generator=g).to(torch.bfloat16)
+    w = torch.randn(130, 128, generator=g).to(torch.bfloat16)
+    big = torch.zeros(6, 300, device="cuda")
+    K.linear_tc(x.cuda(), w.cuda(), out=big[:, 20:150], accumulate=True, k_splits=2)
+    K.check_device_errors()
+    close(big[:, 20:150], x.double() @ w.double().T, 2e-5)
+    assert big[:, :20].abs().sum() == 0 and big[:, 150:].abs().sum() == 0
