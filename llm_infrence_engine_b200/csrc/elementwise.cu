@@ -85,17 +85,21 @@ LLMIE_API int llmie_add_rmsnorm(float* residual, const void* delta, const float*
 }
 
 // ------------------------------------------------------------------------------------------------
-// qkv[n] is [num_heads + 2 num_kv_heads][d]. Adds the bias, rotates the query and key heads by the
-// token's angle (pairs (j, j + d/2)), writes everything back in place and, if asked, copies the key
-// and value heads into the token's cache slot: pool[page][kv head][offset][d], slot = page * page_size + offset.
-template <typename T>
-__global__ void rope_kv_write_kernel(T* __restrict__ qkv, const float* __restrict__ bias, const float* __restrict__ cos_t,
-                                     const float* __restrict__ sin_t, const int* __restrict__ slots, T* __restrict__ k_pool,
-                                     T* __restrict__ v_pool, int nq, int nkv, int d, int page_size, int write_kv) {
+// in[n] is [num_heads + 2 num_kv_heads][d]. Adds the bias, rotates the query and key heads by the
+// token's angle (pairs (j, j + d/2)), writes everything to out[n] (which may be `in` itself) and, if asked,
+// copies the key and value heads into the token's cache slot: pool[page][kv head][offset][d],
+// slot = page * page_size + offset. With `clear_in` the input is set to zero after it was read: it is
+// then a float32 accumulation buffer that the next split-K product adds into.
+template <typename TI, typename TO>
+__global__ void rope_kv_write_kernel(TI* __restrict__ in, TO* __restrict__ out, const float* __restrict__ bias,
+                                     const float* __restrict__ cos_t, const float* __restrict__ sin_t, const int* __restrict__ slots,
+                                     TO* __restrict__ k_pool, TO* __restrict__ v_pool, int nq, int nkv, int d, int page_size, int write_kv,
+                                     int clear_in) {
     const int n = blockIdx.x;
     const int half = d >> 1;
     const int heads = nq + 2 * nkv;
-    T* row = qkv + (size_t)n * heads * d;
+    TI* src = in + (size_t)n * heads * d;
+    TO* row = out + (size_t)n * heads * d;
     const float* c = cos_t + (size_t)n * half;
     const float* sn = sin_t + (size_t)n * half;
     const int slot = write_kv ? slots[n] : -1;
@@ -103,58 +107,84 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const float* __restric
     for (int i = threadIdx.x; i < heads * half; i += blockDim.x) {
         const int h = i / half, j = i % half;
         const int a = h * d + j, b = a + half;
-        float x1 = to_f32(row[a]), x2 = to_f32(row[b]);
+        float x1 = to_f32(src[a]), x2 = to_f32(src[b]);
+        if (clear_in) { src[a] = from_f32<TI>(0.f); src[b] = from_f32<TI>(0.f); }
         if (bias) { x1 += bias[a]; x2 += bias[b]; }
         float y1 = x1, y2 = x2;
         if (h < nq + nkv) {
             y1 = x1 * c[j] - x2 * sn[j];
             y2 = x2 * c[j] + x1 * sn[j];
         }
-        const T o1 = from_f32<T>(y1), o2 = from_f32<T>(y2);
+        const TO o1 = from_f32<TO>(y1), o2 = from_f32<TO>(y2);
         row[a] = o1;
         row[b] = o2;
         if (slot >= 0 && h >= nq) {
             const int kvh = h < nq + nkv ? h - nq : h - nq - nkv;
-            T* pool = h < nq + nkv ? k_pool : v_pool;
-            T* dst = pool + (((size_t)page * nkv + kvh) * page_size + off) * d;
+            TO* pool = h < nq + nkv ? k_pool : v_pool;
+            TO* dst = pool + (((size_t)page * nkv + kvh) * page_size + off) * d;
             dst[j] = o1;
             dst[j + half] = o2;
         }
     }
 }
 
-LLMIE_API int llmie_rope_kv_write(void* qkv, const float* bias, const float* cos_t, const float* sin_t, const int* slots,
+// in_dtype / out_dtype: 0 float32, 1 bfloat16; allowed pairs: equal types (out may alias in), or float32 in and bfloat16 out.
+LLMIE_API int llmie_rope_kv_write(void* in, void* out, const float* bias, const float* cos_t, const float* sin_t, const int* slots,
                                   void* k_pool, void* v_pool, int N, int nq, int nkv, int d, int page_size, int write_kv,
-                                  int dtype, cudaStream_t s) {
+                                  int clear_in, int in_dtype, int out_dtype, cudaStream_t s) {
     if (N <= 0) return 0;
-    if (d <= 0 || (d & 1) || page_size <= 0) return LLMIE_ERR_BAD_ARGUMENT;
+    if (d <= 0 || (d & 1) || page_size <= 0 || (clear_in && in == out)) return LLMIE_ERR_BAD_ARGUMENT;
     const int work = (nq + 2 * nkv) * (d / 2);
     const int threads = work >= 512 ? 256 : 128;
-    if (dtype == DT_F32)
-        rope_kv_write_kernel<float><<<N, threads, 0, s>>>((float*)qkv, bias, cos_t, sin_t, slots, (float*)k_pool, (float*)v_pool,
-                                                          nq, nkv, d, page_size, write_kv);
+    if (in_dtype == DT_F32 && out_dtype == DT_F32)
+        rope_kv_write_kernel<float, float><<<N, threads, 0, s>>>((float*)in, (float*)out, bias, cos_t, sin_t, slots, (float*)k_pool,
+                                                                 (float*)v_pool, nq, nkv, d, page_size, write_kv, clear_in);
+    else if (in_dtype == DT_BF16 && out_dtype == DT_BF16)
+        rope_kv_write_kernel<bf16, bf16><<<N, threads, 0, s>>>((bf16*)in, (bf16*)out, bias, cos_t, sin_t, slots, (bf16*)k_pool,
+                                                               (bf16*)v_pool, nq, nkv, d, page_size, write_kv, clear_in);
+    else if (in_dtype == DT_F32 && out_dtype == DT_BF16)
+        rope_kv_write_kernel<float, bf16><<<N, threads, 0, s>>>((float*)in, (bf16*)out, bias, cos_t, sin_t, slots, (bf16*)k_pool,
+                                                                (bf16*)v_pool, nq, nkv, d, page_size, write_kv, clear_in);
     else
-        rope_kv_write_kernel<bf16><<<N, threads, 0, s>>>((bf16*)qkv, bias, cos_t, sin_t, slots, (bf16*)k_pool, (bf16*)v_pool, nq,
-                                                         nkv, d, page_size, write_kv);
+        return LLMIE_ERR_BAD_ARGUMENT;
     return launch_status();
 }
 
 // ------------------------------------------------------------------------------------------------
-// out[n, i] = silu(gu[n, i]) * gu[n, I + i], silu(z) = z / (1 + exp(-z)) in 32-bit
-template <typename T>
-__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int N, int I) {
+// out[n, i] = silu(gu[n, i]) * gu[n, I + i], silu(z) = z / (1 + exp(-z)) in 32-bit; `clear_in` zeroes what was read
+template <typename TI, typename TO>
+__global__ void silu_mul_kernel(TI* __restrict__ gu, TO* __restrict__ out, int N, int I, int clear_in) {
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= (size_t)N * I) return;
     const size_t n = idx / I, i = idx % I;
     const float g = to_f32(gu[n * 2 * I + i]), u = to_f32(gu[n * 2 * I + I + i]);
-    out[idx] = from_f32<T>(g / (1.0f + expf(-g)) * u);
+    if (clear_in) { gu[n * 2 * I + i] = from_f32<TI>(0.f); gu[n * 2 * I + I + i] = from_f32<TI>(0.f); }
+    out[idx] = from_f32<TO>(g / (1.0f + expf(-g)) * u);
 }
 
-LLMIE_API int llmie_silu_mul(const void* gu, void* out, int N, int I, int dtype, cudaStream_t s) {
+LLMIE_API int llmie_silu_mul(void* gu, void* out, int N, int I, int clear_in, int in_dtype, int out_dtype, cudaStream_t s) {
     if (N <= 0) return 0;
     const size_t total = (size_t)N * I;
     const int blocks = (int)((total + 255) / 256);
-    if (dtype == DT_F32) silu_mul_kernel<float><<<blocks, 256, 0, s>>>((const float*)gu, (float*)out, N, I);
-    else silu_mul_kernel<bf16><<<blocks, 256, 0, s>>>((const bf16*)gu, (bf16*)out, N, I);
+    if (in_dtype == DT_F32 && out_dtype == DT_F32) silu_mul_kernel<float, float><<<blocks, 256, 0, s>>>((float*)gu, (float*)out, N, I, clear_in);
+    else if (in_dtype == DT_BF16 && out_dtype == DT_BF16) silu_mul_kernel<bf16, bf16><<<blocks, 256, 0, s>>>((bf16*)gu, (bf16*)out, N, I, clear_in);
+    else if (in_dtype == DT_F32 && out_dtype == DT_BF16) silu_mul_kernel<float, bf16><<<blocks, 256, 0, s>>>((float*)gu, (bf16*)out, N, I, clear_in);
+    else return LLMIE_ERR_BAD_ARGUMENT;
+    return launch_status();
+}
+
+// ------------------------------------------------------------------------------------------------
+// residual[i] += delta[i] (the residual stream is float32)
+template <typename T>
+__global__ void add_into_kernel(float* __restrict__ residual, const T* __restrict__ delta, size_t total) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx < total) residual[idx] += to_f32(delta[idx]);
+}
+
+LLMIE_API int llmie_add_into(float* residual, const void* delta, long long total, int dtype, cudaStream_t s) {
+    if (total <= 0) return 0;
+    const int blocks = (int)((total + 255) / 256);
+    if (dtype == DT_F32) add_into_kernel<float><<<blocks, 256, 0, s>>>(residual, (const float*)delta, (size_t)total);
+    else add_into_kernel<bf16><<<blocks, 256, 0, s>>>(residual, (const bf16*)delta, (size_t)total);
     return launch_status();
 }

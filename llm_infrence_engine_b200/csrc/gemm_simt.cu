@@ -33,7 +33,7 @@ __device__ __forceinline__ void load4(const T* __restrict__ base, int row, int r
 
 template <typename TI, typename TO>
 __global__ void __launch_bounds__(256) gemm_simt_kernel(const TI* __restrict__ A, const TI* __restrict__ W, TO* __restrict__ C,
-                                                       int M, int N, int K, int vec) {
+                                                       int M, int N, int K, int vec, int accumulate) {
     __shared__ float As[BK][BM + 4];
     __shared__ float Ws[BK][BN + 4];
     const int tid = threadIdx.x;
@@ -77,7 +77,10 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const TI* __restrict__ A
 #pragma unroll
         for (int j = 0; j < TN; ++j) {
             const int n = n0 + tx * TN + j;
-            if (n < N) C[(size_t)m * N + n] = from_f32<TO>(acc[i][j]);
+            if (n < N) {
+                TO* dst = C + (size_t)m * N + n;  // with `accumulate` the product is added to what C holds (its only writer is this thread)
+                *dst = from_f32<TO>(accumulate ? to_f32(*dst) + acc[i][j] : acc[i][j]);
+            }
         }
     }
 }
@@ -86,17 +89,17 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const TI* __restrict__ A
 
 // in_dtype / out_dtype: 0 float32, 1 bfloat16. Beyond K the tiles are padded with zeros, which add nothing.
 LLMIE_API int llmie_gemm_simt(const void* A, const void* W, void* C, int M, int N, int K, int in_dtype, int out_dtype,
-                              cudaStream_t s) {
+                              int accumulate, cudaStream_t s) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0) return LLMIE_ERR_BAD_ARGUMENT;
     const dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
     const int vec = (K % 4 == 0) && ((uintptr_t)A % 16 == 0) && ((uintptr_t)W % 16 == 0);
     if (in_dtype == DT_F32 && out_dtype == DT_F32)
-        gemm_simt_kernel<float, float><<<grid, 256, 0, s>>>((const float*)A, (const float*)W, (float*)C, M, N, K, vec);
+        gemm_simt_kernel<float, float><<<grid, 256, 0, s>>>((const float*)A, (const float*)W, (float*)C, M, N, K, vec, accumulate);
     else if (in_dtype == DT_BF16 && out_dtype == DT_F32)
-        gemm_simt_kernel<bf16, float><<<grid, 256, 0, s>>>((const bf16*)A, (const bf16*)W, (float*)C, M, N, K, vec);
+        gemm_simt_kernel<bf16, float><<<grid, 256, 0, s>>>((const bf16*)A, (const bf16*)W, (float*)C, M, N, K, vec, accumulate);
     else if (in_dtype == DT_BF16 && out_dtype == DT_BF16)
-        gemm_simt_kernel<bf16, bf16><<<grid, 256, 0, s>>>((const bf16*)A, (const bf16*)W, (bf16*)C, M, N, K, vec);
+        gemm_simt_kernel<bf16, bf16><<<grid, 256, 0, s>>>((const bf16*)A, (const bf16*)W, (bf16*)C, M, N, K, vec, accumulate);
     else
         return LLMIE_ERR_BAD_ARGUMENT;
     return launch_status();

@@ -46,10 +46,12 @@ class CudaKernels:
         self._attn_counters: Optional[torch.Tensor] = None
         self.use_mma_attention = True
         self.use_tc_gemm = True
+        self.tc_max_rows = 128        # batches up to this many rows take the small-batch tensor-core product
+        self._acc: Optional[torch.Tensor] = None  # float32 zeros: split-K products add into it, their consumer clears it again
         self._error_flag: Optional[torch.Tensor] = None
         self.num_sms = torch.cuda.get_device_properties(0).multi_processor_count or NUM_SMS_FALLBACK
         for fn in ("llmie_embed", "llmie_rope_tables", "llmie_add_rmsnorm", "llmie_rope_kv_write", "llmie_silu_mul",
-                   "llmie_gemm_simt", "llmie_gemm_tc", "llmie_attn_plan", "llmie_paged_attention_mma", "llmie_paged_attention_f32", "llmie_paged_attention_bf16", "llmie_argmax", "llmie_sample"):
+                   "llmie_gemm_simt", "llmie_gemm_tc", "llmie_add_into", "llmie_attn_plan", "llmie_paged_attention_mma", "llmie_paged_attention_f32", "llmie_paged_attention_bf16", "llmie_argmax", "llmie_sample"):
             getattr(self.lib, fn).restype = ctypes.c_int
 
     # ------------------------------------------------------------------ helpers
@@ -128,20 +130,54 @@ class CudaKernels:
     def rmsnorm_rows(self, residual, delta, weight, eps, rows, out_dtype):
         return self._norm(residual, delta, weight, eps, rows, out_dtype, "rmsnorm_rows")
 
-    def linear(self, x, w, out_dtype=None):
+    def _transient(self, M: int, N: int, device) -> torch.Tensor:
+        if self._acc is None or self._acc.numel() < M * N or self._acc.device != device:
+            self._acc = torch.zeros(max(M * N, 1 << 20), dtype=torch.float32, device=device)
+        return self._acc[: M * N].view(M, N)
+
+    def linear(self, x, w, out_dtype=None, add_to=None, transient=False):
+        """``x w^T`` for ``x [rows, K]`` and ``w [outputs, K]``.
+
+        ``add_to``: a float32 ``[rows, outputs]`` tensor (the residual stream) that the product is added into;
+        nothing is returned. ``transient``: the caller hands the result straight to ``rope_kv_write`` or
+        ``silu_mul`` and nowhere else; for small bfloat16 batches it is then a float32 view of the library's
+        accumulation buffer, which those kernels read and set back to zero."""
         self._need(x, "x", None, 2)
         self._need(w, "w", x.dtype, 2)
         if x.shape[1] != w.shape[1]:
             raise KernelError(f"linear: x has {x.shape[1]} columns, w has {w.shape[1]}")
-        out_dtype = out_dtype or x.dtype
         M, K, N = x.shape[0], x.shape[1], w.shape[0]
-        if self.use_cublas and x.dtype == torch.bfloat16 and out_dtype == torch.bfloat16:
+        bf16 = x.dtype == torch.bfloat16
+        small = bf16 and self.use_tc_gemm and M <= self.tc_max_rows and K % 8 == 0
+        if add_to is not None:
+            self._need(add_to, "add_to", torch.float32, 2)
+            if tuple(add_to.shape) != (M, N):
+                raise KernelError(f"linear: add_to is {list(add_to.shape)}, the product is [{M}, {N}]")
+            if small:
+                self.linear_tc(x, w, out=add_to, accumulate=True)
+            elif bf16 and self.use_cublas:
+                self.launches += 1
+                y = torch.matmul(x, w.t())
+                self._check(self.lib.llmie_add_into(_ptr(add_to), _ptr(y), M * N, 1, self._stream()), "add_into")
+            else:
+                self._check(self.lib.llmie_gemm_simt(_ptr(x), _ptr(w), _ptr(add_to), M, N, K, self._dt(x, "x"), 0, 1, self._stream()),
+                            "linear (accumulate)")
+            return None
+        out_dtype = out_dtype or x.dtype
+        if small and transient and self.tc_splits(M, N, K) > 1:
+            return self.linear_tc(x, w, out=self._transient(M, N, x.device), accumulate=True)
+        if small and out_dtype == torch.float32:
+            return self.linear_tc(x, w)
+        if self.use_cublas and bf16 and out_dtype == torch.bfloat16:
             self.launches += 1
             return torch.matmul(x, w.t())
         out = torch.empty((M, N), dtype=out_dtype, device=x.device)
-        self._check(self.lib.llmie_gemm_simt(_ptr(x), _ptr(w), _ptr(out), M, N, K, self._dt(x, "x"), self._dt(out, "out"),
+        self._check(self.lib.llmie_gemm_simt(_ptr(x), _ptr(w), _ptr(out), M, N, K, self._dt(x, "x"), self._dt(out, "out"), 0,
                                              self._stream()), "linear")
         return out
+
+    def _is_transient(self, t: torch.Tensor) -> bool:
+        return self._acc is not None and t.dtype == torch.float32 and t.untyped_storage().data_ptr() == self._acc.untyped_storage().data_ptr()
 
     def tc_splits(self, M: int, N: int, K: int) -> int:
         """How many blocks share the K range of a small-batch product: enough blocks to draw on the whole memory
@@ -185,7 +221,9 @@ class CudaKernels:
                 raise KernelError(f"a tensor-core GEMM block gave up waiting on a barrier (stage {code}); its output is not valid")
 
     def rope_kv_write(self, qkv, bias, cos, sin, slot_mapping, k_pool, v_pool, num_heads, num_kv_heads, head_dim, page_size,
-                      write_kv=True):
+                      write_kv=True, out_dtype=None):
+        """Bias, rotation and cache write of a fused q/k/v projection; returns the rotated rows in ``out_dtype``
+        (the input itself when the types agree). A transient float32 input is consumed and cleared."""
         self._need(qkv, "qkv", None, 2)
         N = qkv.shape[0]
         heads = num_heads + 2 * num_kv_heads
@@ -201,15 +239,19 @@ class CudaKernels:
             self._need(bias, "bias", torch.float32, 1)
             if bias.shape[0] != heads * head_dim:
                 raise KernelError("rope_kv_write: bias does not match the projection's width")
+        out_dtype = out_dtype or qkv.dtype
+        clear = self._is_transient(qkv)
+        out = qkv if (out_dtype == qkv.dtype and not clear) else torch.empty(qkv.shape, dtype=out_dtype, device=qkv.device)
         if write_kv:
             self._need(slot_mapping, "slot_mapping", torch.int32, 1)
             for name, pool in (("k_pool", k_pool), ("v_pool", v_pool)):
-                self._need(pool, name, qkv.dtype, 4)
+                self._need(pool, name, out_dtype, 4)
                 if tuple(pool.shape[1:]) != (num_kv_heads, page_size, head_dim):
                     raise KernelError(f"rope_kv_write: {name} is {list(pool.shape)}, expected [pages, {num_kv_heads}, {page_size}, {head_dim}]")
-        self._check(self.lib.llmie_rope_kv_write(_ptr(qkv), _ptr(bias), _ptr(cos), _ptr(sin), _ptr(slot_mapping), _ptr(k_pool),
+        self._check(self.lib.llmie_rope_kv_write(_ptr(qkv), _ptr(out), _ptr(bias), _ptr(cos), _ptr(sin), _ptr(slot_mapping), _ptr(k_pool),
                                                  _ptr(v_pool), N, num_heads, num_kv_heads, head_dim, page_size, int(bool(write_kv)),
-                                                 self._dt(qkv, "qkv"), self._stream()), "rope_kv_write")
+                                                 int(clear), self._dt(qkv, "qkv"), self._dt(out, "out"), self._stream()), "rope_kv_write")
+        return out
 
     def attention_splits(self, num_tokens: int, num_kv_heads: int, max_context: int) -> int:
         """Slices of the keys per token: enough blocks to fill the device, at least 256 keys each."""
@@ -302,13 +344,15 @@ class CudaKernels:
             "paged_attention (tensor cores)")
         return out
 
-    def silu_mul(self, gu):
+    def silu_mul(self, gu, out_dtype=None):
+        """``silu(gate) * up`` of a fused gate/up projection ``[rows, 2 I]`` (gate first); a transient float32 input is consumed and cleared."""
         self._need(gu, "gate_up", None, 2)
         if gu.shape[1] % 2:
             raise KernelError("silu_mul: the row must hold gate and up halves of equal width")
         N, I = gu.shape[0], gu.shape[1] // 2
-        out = torch.empty((N, I), dtype=gu.dtype, device=gu.device)
-        self._check(self.lib.llmie_silu_mul(_ptr(gu), _ptr(out), N, I, self._dt(gu, "gate_up"), self._stream()), "silu_mul")
+        out = torch.empty((N, I), dtype=out_dtype or gu.dtype, device=gu.device)
+        self._check(self.lib.llmie_silu_mul(_ptr(gu), _ptr(out), N, I, int(self._is_transient(gu)), self._dt(gu, "gate_up"),
+                                            self._dt(out, "out"), self._stream()), "silu_mul")
         return out
 
     def argmax(self, logits):

@@ -272,15 +272,14 @@ class ModelRunner:
     def forward(self, ctx: StepContext, logit_rows: torch.Tensor) -> Optional[torch.Tensor]:
         spec = self.spec
         residual = spec.embedding.forward(ctx)
-        delta = None
         for call in spec.schedule:
             b = self.bindings[call.cache]
             if b is not None and b.write != call.write:
                 b = type(b)(**{**b.__dict__, "write": call.write})
-            delta = spec.layers[call.layer].forward(ctx, residual, delta, b)
+            spec.layers[call.layer].forward(ctx, residual, b)
         if logit_rows.numel() == 0:
             return None
-        h = spec.final_norm.norm_rows(ctx, residual, delta, logit_rows)
+        h = spec.final_norm.norm_rows(ctx, residual, logit_rows)
         return spec.head.forward(ctx, h)
 
     # ------------------------------------------------------------------ accounting

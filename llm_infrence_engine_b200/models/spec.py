@@ -26,7 +26,7 @@ class LayerCall:
 class ModelSpec:
     config: Any
     embedding: TokenEmbedding
-    layers: List[Part]              # each has forward(ctx, residual, delta, cache) and cache_spec()
+    layers: List[Part]              # each has forward(ctx, residual, cache) and cache_spec()
     schedule: List[LayerCall]
     final_norm: Norm
     head: OutputHead

@@ -6,14 +6,14 @@ the running step reaches it through a ``StepContext``.
 
 Kinds of part and what each must provide:
 
-``Norm``              ``add_norm(ctx, residual, delta) -> h``: add ``delta`` (or nothing) into the
-                      32-bit residual stream in place and return the normalised rows in the compute dtype.
+``Norm``              ``norm(ctx, residual) -> h``: the rows of the 32-bit residual stream, normalised, in the
+                      compute dtype; ``norm_rows(ctx, residual, rows)`` the same for chosen rows only.
 ``PositionEncoding``  ``tables(ctx) -> object``: whatever its mixers need for the step's positions;
                       the context computes it once per step and shares it between layers.
-``Mixer``             ``cache_spec()`` (pages, fixed state or None) and
-                      ``forward(ctx, h, cache) -> [N, hidden]``: reads and writes only its ``cache``.
-``FeedForward``       ``forward(ctx, h) -> [N, hidden]``.
-``Block``             the arrangement of the above in one layer: ``forward(ctx, residual, delta, cache) -> delta``.
+``Mixer``             ``cache_spec()`` (pages, fixed state or None) and ``forward(ctx, h, cache, residual)``:
+                      reads and writes only its ``cache`` and ADDS its ``[N, hidden]`` result into ``residual``.
+``FeedForward``       ``forward(ctx, h, residual)``: adds its result into ``residual``.
+``Block``             the arrangement of the above in one layer: ``forward(ctx, residual, cache)``.
 
 Every part lists its tensors with ``params()``; the loader fills them and calls ``bind``.
 """
@@ -85,11 +85,11 @@ class Part:
 
 
 class Norm(Part):
-    def add_norm(self, ctx, residual: torch.Tensor, delta: Optional[torch.Tensor]) -> torch.Tensor:
+    def norm(self, ctx, residual: torch.Tensor) -> torch.Tensor:
         raise NotImplementedError
 
-    def norm_rows(self, ctx, residual: torch.Tensor, delta: Optional[torch.Tensor], rows: torch.Tensor) -> torch.Tensor:
-        """Normalise only ``residual[rows] (+ delta[rows])``; the residual stream is left as it is."""
+    def norm_rows(self, ctx, residual: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
+        """Normalise only ``residual[rows]``."""
         raise NotImplementedError
 
 
@@ -106,12 +106,12 @@ class Mixer(Part):
     def cache_spec(self):
         return None
 
-    def forward(self, ctx, h: torch.Tensor, cache) -> torch.Tensor:
+    def forward(self, ctx, h: torch.Tensor, cache, residual: torch.Tensor) -> None:
         raise NotImplementedError
 
 
 class FeedForward(Part):
-    def forward(self, ctx, h: torch.Tensor) -> torch.Tensor:
+    def forward(self, ctx, h: torch.Tensor, residual: torch.Tensor) -> None:
         raise NotImplementedError
 
 

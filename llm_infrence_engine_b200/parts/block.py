@@ -11,9 +11,9 @@ from .base import FeedForward, Mixer, Norm, Part
 class PreNormBlock(Part):
     """``x += mixer(norm1(x)); x += ff(norm2(x))`` (src/miniserve/model.py:184-185).
 
-    The residual stream ``x`` is 32-bit and is updated in place. The second addition is left to
-    whoever normalises next (the following block, or the model's last norm), which does it in the
-    same kernel as its norm: ``forward`` takes the addend still owed to ``x`` and returns the new one.
+    The residual stream ``x`` is 32-bit and is updated in place: the mixer and the feed-forward are handed
+    ``x`` and add their result into it themselves, which lets their last matrix product do the addition
+    in its own epilogue instead of a kernel of its own.
     """
 
     graph_safe = True
@@ -27,8 +27,6 @@ class PreNormBlock(Part):
     def cache_spec(self):
         return self.mixer.cache_spec()
 
-    def forward(self, ctx, residual: torch.Tensor, delta: Optional[torch.Tensor], cache) -> torch.Tensor:
-        h = self.norm1.add_norm(ctx, residual, delta)
-        a = self.mixer.forward(ctx, h, cache)
-        h = self.norm2.add_norm(ctx, residual, a)
-        return self.ff.forward(ctx, h)
+    def forward(self, ctx, residual: torch.Tensor, cache) -> None:
+        self.mixer.forward(ctx, self.norm1.norm(ctx, residual), cache, residual)
+        self.ff.forward(ctx, self.norm2.norm(ctx, residual), residual)

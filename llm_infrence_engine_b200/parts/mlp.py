@@ -33,8 +33,8 @@ class GatedMLP(FeedForward):
             "w_down": ParamSpec((Source(f"{p}.down_proj.weight", (h, i)),), MATRIX),
         }
 
-    def forward(self, ctx, h):
+    def forward(self, ctx, h, residual):
         K = ctx.K
-        gu = K.linear(h, self.w_gate_up)
-        a = K.silu_mul(gu)
-        return K.linear(a, self.w_down)
+        gu = K.linear(h, self.w_gate_up, transient=True)
+        a = K.silu_mul(gu, out_dtype=ctx.dtype)
+        K.linear(a, self.w_down, add_to=residual)

@@ -1,4 +1,4 @@
-"""RMS normalisation, fused with the addition into the residual stream that precedes it."""
+"""RMS normalisation of rows of the 32-bit residual stream."""
 from __future__ import annotations
 
 from typing import Dict, Optional
@@ -26,8 +26,8 @@ class RMSNorm(Norm):
     def params(self) -> Dict[str, ParamSpec]:
         return {"weight": ParamSpec((Source(self.weight_name, (self.dim,), INIT_NORM),), VECTOR)}
 
-    def add_norm(self, ctx, residual, delta):
-        return ctx.K.add_rmsnorm(residual, delta, self.weight, self.eps, ctx.dtype)
+    def norm(self, ctx, residual):
+        return ctx.K.add_rmsnorm(residual, None, self.weight, self.eps, ctx.dtype)
 
-    def norm_rows(self, ctx, residual, delta, rows):
-        return ctx.K.rmsnorm_rows(residual, delta, self.weight, self.eps, rows, ctx.dtype)
+    def norm_rows(self, ctx, residual, rows):
+        return ctx.K.rmsnorm_rows(residual, None, self.weight, self.eps, rows, ctx.dtype)

@@ -116,7 +116,8 @@ def test_rope_kv_write(K, dtype, nq, nkv, d, ps, bias):
     q_ref, kp_ref, vp_ref = qkv.clone(), kp.clone(), vp.clone()
     REF.rope_kv_write(q_ref, b, cos, sin, slots, kp_ref, vp_ref, nq, nkv, d, ps, True)
     q_gpu, kp_gpu, vp_gpu = qkv.clone().cuda(), kp.cuda(), vp.cuda()
-    K.rope_kv_write(q_gpu, None if b is None else b.cuda(), cos.cuda(), sin.cuda(), slots.cuda(), kp_gpu, vp_gpu, nq, nkv, d, ps, True)
+    out = K.rope_kv_write(q_gpu, None if b is None else b.cuda(), cos.cuda(), sin.cuda(), slots.cuda(), kp_gpu, vp_gpu, nq, nkv, d, ps, True)
+    assert out.data_ptr() == q_gpu.data_ptr()   # same types: in place
     close(q_gpu, q_ref, tol(dtype, 1e-6, 8e-3))
     close(kp_gpu, kp_ref, tol(dtype, 1e-6, 8e-3))
     close(vp_gpu, vp_ref, tol(dtype, 1e-6, 8e-3))
@@ -307,3 +308,43 @@ def test_linear_tc_into_a_strided_view(K):
     K.check_device_errors()
     close(big[:, 20:150], x.double() @ w.double().T, 2e-5)
     assert big[:, :20].abs().sum() == 0 and big[:, 150:].abs().sum() == 0
+
+
+def test_transient_products_are_consumed_and_cleared(K):
+    """Small bfloat16 batches: the q/k/v and gate/up products are float32 sums of split-K blocks in the library's
+    accumulation buffer; the kernels that read them leave the buffer zero for the next product."""
+    g = torch.Generator().manual_seed(12)
+    nq, nkv, d, ps, N, H, I = 14, 2, 64, 16, 8, 896, 4864
+    x = torch.randn(N, H, generator=g).to(torch.bfloat16)
+    wqkv = (torch.randn((nq + 2 * nkv) * d, H, generator=g) * 0.05).to(torch.bfloat16)
+    bias = torch.randn((nq + 2 * nkv) * d, generator=g)
+    pos = torch.arange(100, 100 + N, dtype=torch.int32)
+    inv = 1.0 / (1e6 ** (torch.arange(0, d, 2).float() / d))
+    cos, sin = REF.rope_tables(pos, inv)
+    slots = torch.arange(N, dtype=torch.int32) + 16
+    kp, vp = torch.zeros(4, nkv, ps, d, dtype=torch.bfloat16), torch.zeros(4, nkv, ps, d, dtype=torch.bfloat16)
+    ref_q = (x.float() @ wqkv.float().T)
+    kp_ref, vp_ref = kp.clone().float(), vp.clone().float()
+    REF.rope_kv_write(ref_q, bias, cos, sin, slots, kp_ref, vp_ref, nq, nkv, d, ps, True)
+    for _ in range(2):
+        acc = K.linear(x.cuda(), wqkv.cuda(), transient=True)
+        assert acc.dtype == torch.float32 and K._is_transient(acc)
+        kp_gpu, vp_gpu = kp.cuda(), vp.cuda()
+        out = K.rope_kv_write(acc, bias.cuda(), cos.cuda(), sin.cuda(), slots.cuda(), kp_gpu, vp_gpu, nq, nkv, d, ps, True,
+                              out_dtype=torch.bfloat16)
+        assert out.dtype == torch.bfloat16 and K._acc.abs().sum().item() == 0
+        close(out, ref_q, 8e-3)
+        close(kp_gpu, kp_ref, 8e-3)
+        close(vp_gpu, vp_ref, 8e-3)
+    wgu = (torch.randn(2 * I, H, generator=g) * 0.05).to(torch.bfloat16)
+    gu = K.linear(x.cuda(), wgu.cuda(), transient=True)
+    assert K._is_transient(gu)
+    a = K.silu_mul(gu, out_dtype=torch.bfloat16)
+    assert K._acc.abs().sum().item() == 0
+    close(a, REF.silu_mul(x.float() @ wgu.float().T), 8e-3)
+    res = torch.randn(N, H, generator=g)
+    wd = (torch.randn(H, I, generator=g) * 0.02).to(torch.bfloat16)
+    r = res.clone().cuda()
+    assert K.linear(a, wd.cuda(), add_to=r) is None
+    close(r, res.double() + a.double().cpu() @ wd.double().T, 2e-5)
+    K.check_device_errors()

@@ -50,14 +50,13 @@ def test_each_part_alone(tmp_path, name, dtype, tol):
     x = spec.embedding.forward(ctx)
     assert torch.equal(x.cpu(), w["model.embed_tokens.weight"][torch.tensor(prompt)].float())
 
-    # norm (with and without the pending addition), also on chosen rows only
+    # norm of all rows, and of chosen rows only; the residual stream itself is not touched
     res = torch.randn(T, H, generator=g)
-    delta = torch.randn(T, H, generator=g).to(td)
     norm = spec.layers[0].norm1
     r = res.clone().cuda()
-    close(norm.add_norm(ctx, r, delta.cuda()), plain_rmsnorm(res + delta.float(), w["model.layers.0.input_layernorm.weight"], c["eps"]), tol)
-    close(r, res + delta.float(), 1e-7)
-    close(norm.norm_rows(ctx, res.clone().cuda(), None, rows[3:9]), plain_rmsnorm(res[3:9], w["model.layers.0.input_layernorm.weight"], c["eps"]), tol)
+    close(norm.norm(ctx, r), plain_rmsnorm(res, w["model.layers.0.input_layernorm.weight"], c["eps"]), tol)
+    assert torch.equal(r.cpu(), res)
+    close(norm.norm_rows(ctx, r, rows[3:9]), plain_rmsnorm(res[3:9], w["model.layers.0.input_layernorm.weight"], c["eps"]), tol)
 
     # position encoding
     cos, sin = ctx.position_tables(spec.layers[0].mixer.position)
@@ -65,23 +64,25 @@ def test_each_part_alone(tmp_path, name, dtype, tol):
     close(cos, pc[:, : c["head_dim"] // 2], 2e-6)
     close(sin, ps[:, : c["head_dim"] // 2], 2e-6)
 
-    # mixer: every layer's attention alone (different windows in C), on random normalised input
+    # mixer: every layer's attention alone (different windows in C), on random normalised input; it adds into the residual
     h = (torch.randn(T, H, generator=g) * 0.5).to(td)
     for i, layer in enumerate(spec.layers):
         b = runner.bindings[i]
-        got = layer.mixer.forward(ctx, h.cuda(), b)
+        r = res.clone().cuda()
+        layer.mixer.forward(ctx, h.cuda(), b, r)
         want = plain_attention(h.float(), w, f"model.layers.{i}.self_attn", c, pc, ps, c["window"][i])
-        close(got, want, tol)
+        close(r.cpu() - res, want, tol)
 
     # feed-forward
-    got = spec.layers[1].ff.forward(ctx, h.cuda())
-    close(got, plain_mlp(h.float(), w, "model.layers.1.mlp"), tol)
+    r = res.clone().cuda()
+    spec.layers[1].ff.forward(ctx, h.cuda(), r)
+    close(r.cpu() - res, plain_mlp(h.float(), w, "model.layers.1.mlp"), tol)
 
-    # block: residual in, residual + owed addend out
+    # block: residual in, residual out
     res2 = torch.randn(T, H, generator=g) * 0.3
     r = res2.clone().cuda()
-    owed = spec.layers[1].forward(ctx, r, None, runner.bindings[1])
-    close(r + owed.float(), plain_block(res2, w, 1, c, pc, ps), tol)
+    spec.layers[1].forward(ctx, r, runner.bindings[1])
+    close(r, plain_block(res2, w, 1, c, pc, ps), tol)
 
     # head
     hn = torch.randn(5, H, generator=g).to(td)
@@ -112,7 +113,7 @@ def _toy_parts():
         def cache_spec(self):
             return FixedStateSpec((self.hidden + 1,))
 
-        def forward(self, ctx, h, cache):
+        def forward(self, ctx, h, cache, residual):
             out = torch.empty_like(h)
             for start, n, slot in zip(ctx.seq_starts, ctx.seq_lens, ctx.seq_slot_list):
                 x = h[start:start + n].float()
@@ -122,7 +123,7 @@ def _toy_parts():
                 out[start:start + n] = (x + sums / counts[:, None]).to(h.dtype)
                 st[: self.hidden] = sums[-1]
                 st[self.hidden] = counts[-1]
-            return ctx.K.linear(out, self.w)
+            ctx.K.linear(out, self.w, add_to=residual)
 
     @dataclass(frozen=True)
     class ToyConfig:

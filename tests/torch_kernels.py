@@ -40,11 +40,15 @@ class TorchKernels:
         h = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps)
         return (weight.float() * h.to(out_dtype).float()).to(out_dtype)
 
-    def linear(self, x, w, out_dtype=None):
-        return (x.float() @ w.float().T).to(out_dtype or x.dtype)
+    def linear(self, x, w, out_dtype=None, add_to=None, transient=False):
+        y = x.float() @ w.float().T
+        if add_to is not None:
+            add_to += y
+            return None
+        return y.to(out_dtype or x.dtype)
 
     def rope_kv_write(self, qkv, bias, cos, sin, slot_mapping, k_pool, v_pool, num_heads, num_kv_heads, head_dim,
-                      page_size, write_kv=True):
+                      page_size, write_kv=True, out_dtype=None):
         N = qkv.shape[0]
         d, half = head_dim, head_dim // 2
         x = qkv.float()
@@ -64,6 +68,7 @@ class TorchKernels:
             v = qkv.view(N, -1, d)[:, num_heads + num_kv_heads:]
             k_pool[page, :, off] = k
             v_pool[page, :, off] = v
+        return qkv
 
     def paged_attention(self, qkv, k_pool, v_pool, block_table, token_seq, positions, num_heads, num_kv_heads, head_dim,
                         page_size, scale, window, max_context, batch=None, num_splits=None):
@@ -86,7 +91,7 @@ class TorchKernels:
                 out[t, h] = pr @ v[:, h // rep]
         return out.reshape(N, num_heads * d).to(qkv.dtype)
 
-    def silu_mul(self, gu):
+    def silu_mul(self, gu, out_dtype=None):
         i = gu.shape[1] // 2
         g, u = gu[:, :i].float(), gu[:, i:].float()
         return (g * torch.sigmoid(g) * u).to(gu.dtype)
