@@ -71,19 +71,30 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 // permuted by the row's low bits so that the 8 rows one ldmatrix phase reads fall on different banks.
 template <int D> __device__ __forceinline__ int swz(int row, int col) { return row * D + ((((col >> 3) ^ (row & 7)) << 3) | (col & 7)); }
 
-// Copy `keys` cache rows starting at absolute key `key0` (clamped to `last_key`) into a swizzled tile.
-template <int D, int THREADS>
-__device__ __forceinline__ void load_kv_tile(const Params& p, const int* table, int kvh, int key0, int last_key, int keys, bf16* ks,
-                                             bf16* vs, int tid) {
-    constexpr int CH = D / 8;
-    for (int idx = tid; idx < keys * CH; idx += THREADS) {
-        const int key = idx / CH, ch = idx % CH;
-        const int ka = min(key0 + key, last_key);
+// One warp copies NKEYS consecutive cache rows (keys key_abs0 .., clamped to last_key) into rows tile_row0 .. of a
+// swizzled K tile and V tile. Every lane looks up the page of at most two keys; the row numbers then travel by
+// shuffle to the lanes that copy that row's 16-byte pieces, 8 (or 16) neighbouring lanes per row.
+template <int D, int NKEYS>
+__device__ __forceinline__ void load_rows_warp(const Params& p, const int* table, int kvh, int key_abs0, int last_key, int tile_row0,
+                                               bf16* ks, bf16* vs, int lane) {
+    constexpr int CH = D / 8, KPI = 32 / CH, NH = (NKEYS + 31) / 32;
+    int rowidx[NH];
+#pragma unroll
+    for (int h = 0; h < NH; ++h) {
+        const int ka = min(key_abs0 + h * 32 + lane, last_key);
         const int page = table[ka / p.page_size];
-        const size_t row = ((size_t)page * p.nkv + kvh) * p.page_size + ka % p.page_size;
-        const int dst = key * D + ((ch ^ (key & 7)) << 3);
-        cp_async16(ks + dst, p.k_pool + row * D + ch * 8);
-        cp_async16(vs + dst, p.v_pool + row * D + ch * 8);
+        rowidx[h] = (page * p.nkv + kvh) * p.page_size + ka % p.page_size;
+    }
+    const int ch = lane % CH, sub = lane / CH;
+#pragma unroll
+    for (int i = 0; i < NKEYS / KPI; ++i) {
+        const int key = i * KPI + sub;
+        const int r = __shfl_sync(0xffffffffu, rowidx[(i * KPI) >> 5], key & 31);
+        const int trow = tile_row0 + key;
+        const int dst = trow * D + ((ch ^ (trow & 7)) << 3);
+        const size_t src = (size_t)r * D + ch * 8;
+        cp_async16(ks + dst, p.k_pool + src);
+        cp_async16(vs + dst, p.v_pool + src);
     }
 }
 
@@ -255,14 +266,14 @@ __global__ void __launch_bounds__(WARPS * 32) attn_mma_decode_kernel(const Param
     const int mine = first < c_end ? (c_end - first + WARPS - 1) / WARPS : 0;
 #pragma unroll
     for (int s = 0; s < STAGES - 1; ++s) {
-        if (s < mine) load_kv_tile<D, 32>(p, table, kvh, lo + (first + s * WARPS) * BN, hi - 1, BN, my + s * 2 * TILE, my + s * 2 * TILE + TILE, lane);
+        if (s < mine) load_rows_warp<D, BN>(p, table, kvh, lo + (first + s * WARPS) * BN, hi - 1, 0, my + s * 2 * TILE, my + s * 2 * TILE + TILE, lane);
         cp_async_commit();
     }
     for (int it = 0; it < mine; ++it) {
         const int nxt = it + STAGES - 1;
         if (nxt < mine) {
             bf16* dst = my + (nxt % STAGES) * 2 * TILE;
-            load_kv_tile<D, 32>(p, table, kvh, lo + (first + nxt * WARPS) * BN, hi - 1, BN, dst, dst + TILE, lane);
+            load_rows_warp<D, BN>(p, table, kvh, lo + (first + nxt * WARPS) * BN, hi - 1, 0, dst, dst + TILE, lane);
         }
         cp_async_commit();
         cp_async_wait<STAGES - 1>();
@@ -326,7 +337,8 @@ __global__ void __launch_bounds__(WARPS * 32) attn_mma_prefill_kernel(const Para
     bf16* kv = qs + BM * D;                         // [2 stages][K, V][BN][D]
     __shared__ int flag;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int tile = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+    const int tile = gridDim.x - 1 - blockIdx.x;  // later tiles of a prompt see more keys: start them first
+    const int kvh = blockIdx.y, split = blockIdx.z;
     const int n0 = p.tile_info ? p.tile_info[2 * tile] : tile;
     const int ntok = p.tile_info ? p.tile_info[2 * tile + 1] : 1;
     const int G = p.nq / p.nkv;
@@ -347,7 +359,7 @@ __global__ void __launch_bounds__(WARPS * 32) attn_mma_prefill_kernel(const Para
         if (row < nrows) cp_async16(dst, p.q + (size_t)(n0 + row / G) * p.q_stride + (size_t)(kvh * G + row % G) * D + ch * 8);
         else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
     }
-    if (c_begin < c_end) load_kv_tile<D, WARPS * 32>(p, table, kvh, lo + c_begin * BN, hi - 1, BN, kv, kv + TILE, tid);
+    if (c_begin < c_end) load_rows_warp<D, BN / WARPS>(p, table, kvh, lo + c_begin * BN + warp * (BN / WARPS), hi - 1, warp * (BN / WARPS), kv, kv + TILE, lane);
     cp_async_commit();
 
     int row_pos[2];
@@ -372,7 +384,7 @@ __global__ void __launch_bounds__(WARPS * 32) attn_mma_prefill_kernel(const Para
         const int stage = (c - c_begin) & 1;
         if (c + 1 < c_end) {
             bf16* dst = kv + (stage ^ 1) * 2 * TILE;
-            load_kv_tile<D, WARPS * 32>(p, table, kvh, lo + (c + 1) * BN, hi - 1, BN, dst, dst + TILE, tid);
+            load_rows_warp<D, BN / WARPS>(p, table, kvh, lo + (c + 1) * BN + warp * (BN / WARPS), hi - 1, warp * (BN / WARPS), dst, dst + TILE, lane);
         }
         cp_async_commit();
         cp_async_wait<1>();

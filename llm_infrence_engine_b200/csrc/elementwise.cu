@@ -46,42 +46,66 @@ LLMIE_API int llmie_rope_tables(const int* pos, const float* inv_freq, float* co
 //   rows == nullptr: r = blockIdx.x; residual[r] += delta[r] (stored); out[r] = norm(residual[r])
 //   rows != nullptr: r = rows[blockIdx.x]; out[blockIdx.x] = norm(residual[r] + delta[r]); residual untouched
 // norm(x) = weight * T(x / sqrt(mean(x^2) + eps)), the mean and the scaling in 32-bit.
-template <typename T>
+// The row is kept in shared memory between the two passes; VEC = 4 moves four elements per access when H allows.
+template <typename T, int VEC>
 __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __restrict__ delta, const float* __restrict__ weight,
                                    T* __restrict__ out, const int* __restrict__ rows, int H, float eps) {
-    extern __shared__ float row_buf[];  // H floats, then 33 for the reduction
+    extern __shared__ __align__(16) float row_buf[];  // H floats, then 33 for the reduction
     float* scratch = row_buf + H;
     const int r = rows ? rows[blockIdx.x] : blockIdx.x;
     float* x = residual + (size_t)r * H;
     const T* d = delta ? delta + (size_t)r * H : nullptr;
     float ss = 0.f;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) {
-        float v = x[i];
-        if (d) v += to_f32(d[i]);
-        row_buf[i] = v;
-        if (d && !rows) x[i] = v;
-        ss += v * v;
+    for (int i = threadIdx.x * VEC; i < H; i += blockDim.x * VEC) {
+        float v[VEC];
+        if constexpr (VEC == 4) load4(x + i, v); else v[0] = x[i];
+        if (d) {
+            float dv[VEC];
+            if constexpr (VEC == 4) load4(d + i, dv); else dv[0] = to_f32(d[i]);
+#pragma unroll
+            for (int j = 0; j < VEC; ++j) v[j] += dv[j];
+            if (!rows) { if constexpr (VEC == 4) store4(x + i, v); else x[i] = v[0]; }
+        }
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) { row_buf[i + j] = v[j]; ss += v[j] * v[j]; }
     }
     ss = block_sum(ss, scratch);
     const float rstd = 1.0f / sqrtf(ss / (float)H + eps);
     T* o = out + (size_t)blockIdx.x * H;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = from_f32<T>(weight[i] * round_through<T>(row_buf[i] * rstd));
+    for (int i = threadIdx.x * VEC; i < H; i += blockDim.x * VEC) {
+        float w[VEC], y[VEC];
+        if constexpr (VEC == 4) load4(weight + i, w); else w[0] = weight[i];
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) y[j] = w[j] * round_through<T>(row_buf[i + j] * rstd);
+        if constexpr (VEC == 4) store4(o + i, y); else o[i] = from_f32<T>(y[0]);
+    }
+}
+
+template <typename T>
+static int launch_add_rmsnorm(float* residual, const T* delta, const float* weight, T* out, const int* rows, int n_out, int H, float eps,
+                              cudaStream_t s) {
+    const size_t smem = (size_t)(H + 33) * sizeof(float);
+    const bool vec = H % 4 == 0 && ((uintptr_t)residual % 16 == 0) && ((uintptr_t)out % 8 == 0) && ((uintptr_t)delta % 8 == 0) &&
+                     ((uintptr_t)weight % 16 == 0);
+    const int per = vec ? 4 : 1;
+    int threads = 32;
+    while (threads < 512 && threads * per * 2 <= H) threads *= 2;
+    if (vec) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(add_rmsnorm_kernel<T, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        add_rmsnorm_kernel<T, 4><<<n_out, threads, smem, s>>>(residual, delta, weight, out, rows, H, eps);
+    } else {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(add_rmsnorm_kernel<T, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        add_rmsnorm_kernel<T, 1><<<n_out, threads, smem, s>>>(residual, delta, weight, out, rows, H, eps);
+    }
+    return launch_status();
 }
 
 LLMIE_API int llmie_add_rmsnorm(float* residual, const void* delta, const float* weight, void* out, const int* rows,
                                 int n_out, int H, float eps, int dtype, cudaStream_t s) {
     if (n_out <= 0) return 0;
-    const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
-    const size_t smem = (size_t)(H + 33) * sizeof(float);
-    if (smem > 200 * 1024) return LLMIE_ERR_BAD_ARGUMENT;
-    if (dtype == DT_F32) {
-        if (smem > 48 * 1024) cudaFuncSetAttribute(add_rmsnorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        add_rmsnorm_kernel<float><<<n_out, threads, smem, s>>>(residual, (const float*)delta, weight, (float*)out, rows, H, eps);
-    } else {
-        if (smem > 48 * 1024) cudaFuncSetAttribute(add_rmsnorm_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        add_rmsnorm_kernel<bf16><<<n_out, threads, smem, s>>>(residual, (const bf16*)delta, weight, (bf16*)out, rows, H, eps);
-    }
-    return launch_status();
+    if ((size_t)(H + 33) * sizeof(float) > 200 * 1024) return LLMIE_ERR_BAD_ARGUMENT;
+    if (dtype == DT_F32) return launch_add_rmsnorm<float>(residual, (const float*)delta, weight, (float*)out, rows, n_out, H, eps, s);
+    return launch_add_rmsnorm<bf16>(residual, (const bf16*)delta, weight, (bf16*)out, rows, n_out, H, eps, s);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -151,40 +175,78 @@ LLMIE_API int llmie_rope_kv_write(void* in, void* out, const float* bias, const 
 }
 
 // ------------------------------------------------------------------------------------------------
-// out[n, i] = silu(gu[n, i]) * gu[n, I + i], silu(z) = z / (1 + exp(-z)) in 32-bit; `clear_in` zeroes what was read
+// out[n, i] = silu(gu[n, i]) * gu[n, I + i], silu(z) = z / (1 + exp(-z)) in 32-bit; `clear_in` zeroes what was read.
+// grid = (column blocks, rows); VEC = 4 moves four columns per thread.
+template <typename TI, typename TO, int VEC>
+__global__ void silu_mul_kernel(TI* __restrict__ gu, TO* __restrict__ out, int I, int clear_in) {
+    const int i = (blockIdx.x * blockDim.x + threadIdx.x) * VEC;
+    if (i >= I) return;
+    TI* g_ptr = gu + (size_t)blockIdx.y * 2 * I + i;
+    TI* u_ptr = g_ptr + I;
+    float g[VEC], u[VEC], y[VEC];
+    if constexpr (VEC == 4) { load4(g_ptr, g); load4(u_ptr, u); } else { g[0] = to_f32(*g_ptr); u[0] = to_f32(*u_ptr); }
+    if (clear_in) {
+        const float zero[4] = {0.f, 0.f, 0.f, 0.f};
+        if constexpr (VEC == 4) { store4(g_ptr, zero); store4(u_ptr, zero); } else { *g_ptr = from_f32<TI>(0.f); *u_ptr = from_f32<TI>(0.f); }
+    }
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) y[j] = g[j] / (1.0f + expf(-g[j])) * u[j];
+    TO* o = out + (size_t)blockIdx.y * I + i;
+    if constexpr (VEC == 4) store4(o, y); else *o = from_f32<TO>(y[0]);
+}
+
 template <typename TI, typename TO>
-__global__ void silu_mul_kernel(TI* __restrict__ gu, TO* __restrict__ out, int N, int I, int clear_in) {
-    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx >= (size_t)N * I) return;
-    const size_t n = idx / I, i = idx % I;
-    const float g = to_f32(gu[n * 2 * I + i]), u = to_f32(gu[n * 2 * I + I + i]);
-    if (clear_in) { gu[n * 2 * I + i] = from_f32<TI>(0.f); gu[n * 2 * I + I + i] = from_f32<TI>(0.f); }
-    out[idx] = from_f32<TO>(g / (1.0f + expf(-g)) * u);
+static int launch_silu_mul(TI* gu, TO* out, int N, int I, int clear_in, cudaStream_t s) {
+    if (N > 65535) {  // rows ride in grid.y; more rows than that go in slabs
+        for (int n0 = 0; n0 < N; n0 += 65535) {
+            const int rc = launch_silu_mul<TI, TO>(gu + (size_t)n0 * 2 * I, out + (size_t)n0 * I, min(65535, N - n0), I, clear_in, s);
+            if (rc) return rc;
+        }
+        return 0;
+    }
+    const bool vec = I % 4 == 0 && ((uintptr_t)gu % 16 == 0) && ((uintptr_t)out % 16 == 0);
+    if (vec) silu_mul_kernel<TI, TO, 4><<<dim3((I / 4 + 127) / 128, N), 128, 0, s>>>(gu, out, I, clear_in);
+    else silu_mul_kernel<TI, TO, 1><<<dim3((I + 127) / 128, N), 128, 0, s>>>(gu, out, I, clear_in);
+    return launch_status();
 }
 
 LLMIE_API int llmie_silu_mul(void* gu, void* out, int N, int I, int clear_in, int in_dtype, int out_dtype, cudaStream_t s) {
     if (N <= 0) return 0;
-    const size_t total = (size_t)N * I;
-    const int blocks = (int)((total + 255) / 256);
-    if (in_dtype == DT_F32 && out_dtype == DT_F32) silu_mul_kernel<float, float><<<blocks, 256, 0, s>>>((float*)gu, (float*)out, N, I, clear_in);
-    else if (in_dtype == DT_BF16 && out_dtype == DT_BF16) silu_mul_kernel<bf16, bf16><<<blocks, 256, 0, s>>>((bf16*)gu, (bf16*)out, N, I, clear_in);
-    else if (in_dtype == DT_F32 && out_dtype == DT_BF16) silu_mul_kernel<float, bf16><<<blocks, 256, 0, s>>>((float*)gu, (bf16*)out, N, I, clear_in);
-    else return LLMIE_ERR_BAD_ARGUMENT;
-    return launch_status();
+    if (in_dtype == DT_F32 && out_dtype == DT_F32) return launch_silu_mul<float, float>((float*)gu, (float*)out, N, I, clear_in, s);
+    if (in_dtype == DT_BF16 && out_dtype == DT_BF16) return launch_silu_mul<bf16, bf16>((bf16*)gu, (bf16*)out, N, I, clear_in, s);
+    if (in_dtype == DT_F32 && out_dtype == DT_BF16) return launch_silu_mul<float, bf16>((float*)gu, (bf16*)out, N, I, clear_in, s);
+    return LLMIE_ERR_BAD_ARGUMENT;
 }
 
 // ------------------------------------------------------------------------------------------------
 // residual[i] += delta[i] (the residual stream is float32)
-template <typename T>
+template <typename T, int VEC>
 __global__ void add_into_kernel(float* __restrict__ residual, const T* __restrict__ delta, size_t total) {
-    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx < total) residual[idx] += to_f32(delta[idx]);
+    const size_t idx = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * VEC;
+    if (idx >= total) return;
+    if constexpr (VEC == 4) {
+        float r[4], d[4];
+        load4(residual + idx, r);
+        load4(delta + idx, d);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) r[j] += d[j];
+        store4(residual + idx, r);
+    } else {
+        residual[idx] += to_f32(delta[idx]);
+    }
 }
 
 LLMIE_API int llmie_add_into(float* residual, const void* delta, long long total, int dtype, cudaStream_t s) {
     if (total <= 0) return 0;
-    const int blocks = (int)((total + 255) / 256);
-    if (dtype == DT_F32) add_into_kernel<float><<<blocks, 256, 0, s>>>(residual, (const float*)delta, (size_t)total);
-    else add_into_kernel<bf16><<<blocks, 256, 0, s>>>(residual, (const bf16*)delta, (size_t)total);
+    const bool vec = total % 4 == 0 && ((uintptr_t)residual % 16 == 0) && ((uintptr_t)delta % 16 == 0);
+    const long long work = vec ? total / 4 : total;
+    const int blocks = (int)((work + 255) / 256);
+    if (dtype == DT_F32) {
+        if (vec) add_into_kernel<float, 4><<<blocks, 256, 0, s>>>(residual, (const float*)delta, (size_t)total);
+        else add_into_kernel<float, 1><<<blocks, 256, 0, s>>>(residual, (const float*)delta, (size_t)total);
+    } else {
+        if (vec) add_into_kernel<bf16, 4><<<blocks, 256, 0, s>>>(residual, (const bf16*)delta, (size_t)total);
+        else add_into_kernel<bf16, 1><<<blocks, 256, 0, s>>>(residual, (const bf16*)delta, (size_t)total);
+    }
     return launch_status();
 }

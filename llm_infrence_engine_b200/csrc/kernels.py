@@ -359,7 +359,10 @@ class CudaKernels:
         self._need(logits, "logits", torch.float32, 2)
         M, V = logits.shape
         out = torch.empty((M,), dtype=torch.int32, device=logits.device)
-        self._check(self.lib.llmie_argmax(_ptr(logits), _ptr(out), M, V, self._stream()), "argmax")
+        part_v = torch.empty((M * 64,), dtype=torch.float32, device=logits.device)
+        part_i = torch.empty((M * 64,), dtype=torch.int32, device=logits.device)
+        self._check(self.lib.llmie_argmax(_ptr(logits), _ptr(out), _ptr(part_v), _ptr(part_i), M, V, self._stream()), "argmax")
+        self.launches += 1
         return out
 
     def sample(self, logits, temperature, top_k, top_p, uniform):

@@ -39,37 +39,48 @@ __device__ __forceinline__ double block_sum_f64(double v, double* scratch) {
     return scratch[32];
 }
 
-// Lowest index among the largest values.
-__global__ void __launch_bounds__(THREADS) argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int V) {
-    __shared__ float bv[32];
-    __shared__ int bi[32];
-    const float* x = logits + (size_t)blockIdx.x * V;
-    float best = -INFINITY;
-    int idx = 0x7fffffff;
-    for (int i = threadIdx.x; i < V; i += THREADS) {
-        const float v = x[i];
-        if (v > best || (v == best && i < idx) || idx == 0x7fffffff) { best = v; idx = i; }
-    }
+// Lowest index among the largest values. Stage 1: grid (parts, rows), each block scans one slice of a row and
+// writes its best (value, index) to `part`; stage 2: one block per row picks among the parts.
+constexpr int ARG_THREADS = 256;
+
+__device__ __forceinline__ void arg_better(float& best, int& idx, float ov, int oi) {
+    if (oi >= 0 && (idx < 0 || ov > best || (ov == best && oi < idx))) { best = ov; idx = oi; }
+}
+
+__device__ __forceinline__ void arg_block_reduce(float& best, int& idx) {
+    __shared__ float bv[ARG_THREADS / 32];
+    __shared__ int bi[ARG_THREADS / 32];
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-        const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
-        if (oi != 0x7fffffff && (idx == 0x7fffffff || ov > best || (ov == best && oi < idx))) { best = ov; idx = oi; }
-    }
+    for (int o = 16; o > 0; o >>= 1) arg_better(best, idx, __shfl_xor_sync(0xffffffffu, best, o), __shfl_xor_sync(0xffffffffu, idx, o));
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     if (lane == 0) { bv[warp] = best; bi[warp] = idx; }
     __syncthreads();
     if (warp == 0) {
-        best = bv[lane];
-        idx = bi[lane];
+        best = lane < ARG_THREADS / 32 ? bv[lane] : 0.f;
+        idx = lane < ARG_THREADS / 32 ? bi[lane] : -1;
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-            const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
-            if (oi != 0x7fffffff && (idx == 0x7fffffff || ov > best || (ov == best && oi < idx))) { best = ov; idx = oi; }
-        }
-        if (lane == 0) out[blockIdx.x] = idx == 0x7fffffff ? 0 : idx;
+        for (int o = 16; o > 0; o >>= 1) arg_better(best, idx, __shfl_xor_sync(0xffffffffu, best, o), __shfl_xor_sync(0xffffffffu, idx, o));
     }
+}
+
+__global__ void __launch_bounds__(ARG_THREADS) argmax_part_kernel(const float* __restrict__ logits, float* __restrict__ part_v,
+                                                                 int* __restrict__ part_i, int V, int per) {
+    const float* x = logits + (size_t)blockIdx.y * V;
+    const int lo = blockIdx.x * per, hi = min(V, lo + per);
+    float best = 0.f;
+    int idx = -1;
+    for (int i = lo + threadIdx.x; i < hi; i += ARG_THREADS) arg_better(best, idx, x[i], i);
+    arg_block_reduce(best, idx);
+    if (threadIdx.x == 0) { part_v[blockIdx.y * gridDim.x + blockIdx.x] = best; part_i[blockIdx.y * gridDim.x + blockIdx.x] = idx; }
+}
+
+__global__ void __launch_bounds__(ARG_THREADS) argmax_final_kernel(const float* __restrict__ part_v, const int* __restrict__ part_i,
+                                                                  int* __restrict__ out, int parts) {
+    float best = 0.f;
+    int idx = -1;
+    for (int i = threadIdx.x; i < parts; i += ARG_THREADS) arg_better(best, idx, part_v[blockIdx.x * parts + i], part_i[blockIdx.x * parts + i]);
+    arg_block_reduce(best, idx);
+    if (threadIdx.x == 0) out[blockIdx.x] = idx < 0 ? 0 : idx;
 }
 
 __global__ void __launch_bounds__(THREADS) sample_kernel(const float* __restrict__ logits, const float* __restrict__ temperature,
@@ -236,10 +247,16 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(const float* __restrict
 
 }  // namespace
 
-LLMIE_API int llmie_argmax(const float* logits, int* out, int M, int V, cudaStream_t s) {
+// `part_v` / `part_i`: scratch of M * ARGMAX_PARTS floats / ints.
+LLMIE_API int llmie_argmax(const float* logits, int* out, float* part_v, int* part_i, int M, int V, cudaStream_t s) {
     if (M <= 0) return 0;
-    if (V <= 0) return LLMIE_ERR_BAD_ARGUMENT;
-    argmax_kernel<<<M, THREADS, 0, s>>>(logits, out, V);
+    if (V <= 0 || M > 65535) return LLMIE_ERR_BAD_ARGUMENT;
+    const int parts = 64;
+    const int per = (V + parts - 1) / parts;
+    argmax_part_kernel<<<dim3(parts, M), ARG_THREADS, 0, s>>>(logits, part_v, part_i, V, per);
+    int rc = launch_status();
+    if (rc) return rc;
+    argmax_final_kernel<<<M, ARG_THREADS, 0, s>>>(part_v, part_i, out, parts);
     return launch_status();
 }
 
