@@ -228,6 +228,8 @@ __global__ void __launch_bounds__(WARPS * 32) attn_mma_decode_kernel(const Param
     __shared__ int flag;
 
     const int tile = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+    pdl_trigger();
+    pdl_wait();
     const int n0 = p.tile_info ? p.tile_info[2 * tile] : tile;
     const int ntok = p.tile_info ? p.tile_info[2 * tile + 1] : 1;
     const int G = p.nq / p.nkv;
@@ -339,6 +341,8 @@ __global__ void __launch_bounds__(WARPS * 32) attn_mma_prefill_kernel(const Para
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int tile = gridDim.x - 1 - blockIdx.x;  // later tiles of a prompt see more keys: start them first
     const int kvh = blockIdx.y, split = blockIdx.z;
+    pdl_trigger();
+    pdl_wait();
     const int n0 = p.tile_info ? p.tile_info[2 * tile] : tile;
     const int ntok = p.tile_info ? p.tile_info[2 * tile + 1] : 1;
     const int G = p.nq / p.nkv;
@@ -432,6 +436,8 @@ __global__ void __launch_bounds__(WARPS * 32) attn_mma_prefill_kernel(const Para
 
 // tile list of a step: request r brings tokens [starts[r], starts[r + 1]); tiles hold up to `per_tile` tokens of one request
 __global__ void attn_plan_kernel(const int* __restrict__ starts, int num_seqs, int per_tile, int* __restrict__ tile_info, int max_tiles) {
+    pdl_trigger();
+    pdl_wait();
     if (threadIdx.x != 0 || blockIdx.x != 0) return;
     int t = 0;
     for (int r = 0; r < num_seqs; ++r) {
@@ -457,7 +463,7 @@ int launch(const Params& p, int num_tiles, int decode_mode, cudaStream_t s) {
             if (e != cudaSuccess) return (int)e;
             set = true;
         }
-        attn_mma_decode_kernel<D, BN, STAGES><<<grid, WARPS * 32, smem, s>>>(p);
+        return launch_kernel(attn_mma_decode_kernel<D, BN, STAGES>, grid, dim3(WARPS * 32), smem, s, p);
     } else {
         constexpr size_t tiles = (size_t)(64 * D + 2 * 2 * 64 * D) * sizeof(bf16);
         constexpr size_t merge = (size_t)(64 * (D + 2)) * sizeof(float);
@@ -468,9 +474,8 @@ int launch(const Params& p, int num_tiles, int decode_mode, cudaStream_t s) {
             if (e != cudaSuccess) return (int)e;
             set = true;
         }
-        attn_mma_prefill_kernel<D><<<grid, WARPS * 32, smem, s>>>(p);
+        return launch_kernel(attn_mma_prefill_kernel<D>, grid, dim3(WARPS * 32), smem, s, p);
     }
-    return launch_status();
 }
 
 }  // namespace
@@ -478,8 +483,7 @@ int launch(const Params& p, int num_tiles, int decode_mode, cudaStream_t s) {
 LLMIE_API int llmie_attn_plan(const int* seq_starts, int num_seqs, int tokens_per_tile, int* tile_info, int max_tiles, cudaStream_t s) {
     if (num_seqs <= 0 || max_tiles <= 0) return 0;
     if (tokens_per_tile <= 0) return LLMIE_ERR_BAD_ARGUMENT;
-    attn_plan_kernel<<<1, 32, 0, s>>>(seq_starts, num_seqs, tokens_per_tile, tile_info, max_tiles);
-    return launch_status();
+    return launch_kernel(attn_plan_kernel, dim3(1), dim3(32), 0, s, seq_starts, num_seqs, tokens_per_tile, tile_info, max_tiles);
 }
 
 // decode_mode 1: every tile has at most 16 rows (tokens * group). 0: at most 64 rows.

@@ -95,3 +95,31 @@ __device__ __forceinline__ void store4(bf16* p, const float* v) {
 static inline int launch_status() {
     return (int)cudaGetLastError();
 }
+
+// ------------------------------------------------------------------------------------------------
+// Programmatic dependent launch. A kernel launched through `launch_kernel` may start while the kernel
+// before it on the stream is still running; it does whatever does not depend on that kernel (set-up,
+// fetching weights), then calls pdl_wait(), which returns once the earlier kernel has finished and its
+// writes are visible. Every kernel launched this way calls pdl_wait() exactly where its first access to
+// anything an earlier kernel wrote (or still reads) would be, and ALWAYS calls it, so that completion
+// stays ordered along the stream. pdl_trigger() lets the next kernel's blocks be scheduled from now on.
+// Without the launch attribute both are no-ops.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+
+extern "C" int llmie_pdl_flag;  // 1: launch with the programmatic-serialization attribute (set by llmie_set_pdl)
+
+template <typename... KArgs, typename... Args>
+static inline int launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = llmie_pdl_flag ? 1 : 0;
+    return (int)cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}

@@ -3,10 +3,20 @@
 // residual stream, the norms' reductions, the rotation angles and the activation are 32-bit.
 #include "common.cuh"
 
+int llmie_pdl_flag = 0;
+
+// 1: kernels of a step overlap their set-up with the tail of the kernel before them (see common.cuh); 0: plain launches.
+LLMIE_API int llmie_set_pdl(int on) {
+    llmie_pdl_flag = on ? 1 : 0;
+    return 0;
+}
+
 // ------------------------------------------------------------------------------------------------
 // x[n, :] = table[ids[n], :]  widened to float (the residual stream)
 template <typename T>
 __global__ void embed_kernel(const int* __restrict__ ids, const T* __restrict__ table, float* __restrict__ out, int H) {
+    pdl_trigger();
+    pdl_wait();
     const int n = blockIdx.x;
     const T* row = table + (size_t)ids[n] * H;
     float* o = out + (size_t)n * H;
@@ -16,15 +26,16 @@ __global__ void embed_kernel(const int* __restrict__ ids, const T* __restrict__ 
 LLMIE_API int llmie_embed(const int* ids, const void* table, float* out, int N, int H, int dtype, cudaStream_t s) {
     if (N <= 0) return 0;
     const int threads = H >= 1024 ? 256 : 128;
-    if (dtype == DT_F32) embed_kernel<float><<<N, threads, 0, s>>>(ids, (const float*)table, out, H);
-    else embed_kernel<bf16><<<N, threads, 0, s>>>(ids, (const bf16*)table, out, H);
-    return launch_status();
+    if (dtype == DT_F32) return launch_kernel(embed_kernel<float>, dim3(N), dim3(threads), 0, s, ids, (const float*)table, out, H);
+    return launch_kernel(embed_kernel<bf16>, dim3(N), dim3(threads), 0, s, ids, (const bf16*)table, out, H);
 }
 
 // ------------------------------------------------------------------------------------------------
 // cos/sin[n, j] of the angle float(position[n]) * inv_freq[j], all in 32-bit
 __global__ void rope_tables_kernel(const int* __restrict__ pos, const float* __restrict__ inv_freq, float* __restrict__ cos_out,
                                    float* __restrict__ sin_out, int N, int half) {
+    pdl_trigger();
+    pdl_wait();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= N * half) return;
     const int n = i / half, j = i % half;
@@ -37,8 +48,7 @@ LLMIE_API int llmie_rope_tables(const int* pos, const float* inv_freq, float* co
                                 cudaStream_t s) {
     if (N <= 0) return 0;
     const int total = N * half;
-    rope_tables_kernel<<<(total + 127) / 128, 128, 0, s>>>(pos, inv_freq, cos_out, sin_out, N, half);
-    return launch_status();
+    return launch_kernel(rope_tables_kernel, dim3((total + 127) / 128), dim3(128), 0, s, pos, inv_freq, cos_out, sin_out, N, half);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -52,6 +62,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __rest
                                    T* __restrict__ out, const int* __restrict__ rows, int H, float eps) {
     extern __shared__ __align__(16) float row_buf[];  // H floats, then 33 for the reduction
     float* scratch = row_buf + H;
+    pdl_trigger();
+    pdl_wait();
     const int r = rows ? rows[blockIdx.x] : blockIdx.x;
     float* x = residual + (size_t)r * H;
     const T* d = delta ? delta + (size_t)r * H : nullptr;
@@ -92,12 +104,11 @@ static int launch_add_rmsnorm(float* residual, const T* delta, const float* weig
     while (threads < 512 && threads * per * 2 <= H) threads *= 2;
     if (vec) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(add_rmsnorm_kernel<T, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        add_rmsnorm_kernel<T, 4><<<n_out, threads, smem, s>>>(residual, delta, weight, out, rows, H, eps);
+        return launch_kernel(add_rmsnorm_kernel<T, 4>, dim3(n_out), dim3(threads), smem, s, residual, delta, weight, out, rows, H, eps);
     } else {
         if (smem > 48 * 1024) cudaFuncSetAttribute(add_rmsnorm_kernel<T, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        add_rmsnorm_kernel<T, 1><<<n_out, threads, smem, s>>>(residual, delta, weight, out, rows, H, eps);
+        return launch_kernel(add_rmsnorm_kernel<T, 1>, dim3(n_out), dim3(threads), smem, s, residual, delta, weight, out, rows, H, eps);
     }
-    return launch_status();
 }
 
 LLMIE_API int llmie_add_rmsnorm(float* residual, const void* delta, const float* weight, void* out, const int* rows,
@@ -119,6 +130,8 @@ __global__ void rope_kv_write_kernel(TI* __restrict__ in, TO* __restrict__ out, 
                                      const float* __restrict__ cos_t, const float* __restrict__ sin_t, const int* __restrict__ slots,
                                      TO* __restrict__ k_pool, TO* __restrict__ v_pool, int nq, int nkv, int d, int page_size, int write_kv,
                                      int clear_in) {
+    pdl_trigger();
+    pdl_wait();
     const int n = blockIdx.x;
     const int half = d >> 1;
     const int heads = nq + 2 * nkv;
@@ -161,17 +174,15 @@ LLMIE_API int llmie_rope_kv_write(void* in, void* out, const float* bias, const 
     const int work = (nq + 2 * nkv) * (d / 2);
     const int threads = work >= 512 ? 256 : 128;
     if (in_dtype == DT_F32 && out_dtype == DT_F32)
-        rope_kv_write_kernel<float, float><<<N, threads, 0, s>>>((float*)in, (float*)out, bias, cos_t, sin_t, slots, (float*)k_pool,
-                                                                 (float*)v_pool, nq, nkv, d, page_size, write_kv, clear_in);
+        return launch_kernel(rope_kv_write_kernel<float, float>, dim3(N), dim3(threads), 0, s, (float*)in, (float*)out, bias, cos_t, sin_t,
+                             slots, (float*)k_pool, (float*)v_pool, nq, nkv, d, page_size, write_kv, clear_in);
     else if (in_dtype == DT_BF16 && out_dtype == DT_BF16)
-        rope_kv_write_kernel<bf16, bf16><<<N, threads, 0, s>>>((bf16*)in, (bf16*)out, bias, cos_t, sin_t, slots, (bf16*)k_pool,
-                                                               (bf16*)v_pool, nq, nkv, d, page_size, write_kv, clear_in);
+        return launch_kernel(rope_kv_write_kernel<bf16, bf16>, dim3(N), dim3(threads), 0, s, (bf16*)in, (bf16*)out, bias, cos_t, sin_t,
+                             slots, (bf16*)k_pool, (bf16*)v_pool, nq, nkv, d, page_size, write_kv, clear_in);
     else if (in_dtype == DT_F32 && out_dtype == DT_BF16)
-        rope_kv_write_kernel<float, bf16><<<N, threads, 0, s>>>((float*)in, (bf16*)out, bias, cos_t, sin_t, slots, (bf16*)k_pool,
-                                                                (bf16*)v_pool, nq, nkv, d, page_size, write_kv, clear_in);
-    else
-        return LLMIE_ERR_BAD_ARGUMENT;
-    return launch_status();
+        return launch_kernel(rope_kv_write_kernel<float, bf16>, dim3(N), dim3(threads), 0, s, (float*)in, (bf16*)out, bias, cos_t, sin_t,
+                             slots, (bf16*)k_pool, (bf16*)v_pool, nq, nkv, d, page_size, write_kv, clear_in);
+    return LLMIE_ERR_BAD_ARGUMENT;
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -179,6 +190,8 @@ LLMIE_API int llmie_rope_kv_write(void* in, void* out, const float* bias, const 
 // grid = (column blocks, rows); VEC = 4 moves four columns per thread.
 template <typename TI, typename TO, int VEC>
 __global__ void silu_mul_kernel(TI* __restrict__ gu, TO* __restrict__ out, int I, int clear_in) {
+    pdl_trigger();
+    pdl_wait();
     const int i = (blockIdx.x * blockDim.x + threadIdx.x) * VEC;
     if (i >= I) return;
     TI* g_ptr = gu + (size_t)blockIdx.y * 2 * I + i;
@@ -205,9 +218,8 @@ static int launch_silu_mul(TI* gu, TO* out, int N, int I, int clear_in, cudaStre
         return 0;
     }
     const bool vec = I % 4 == 0 && ((uintptr_t)gu % 16 == 0) && ((uintptr_t)out % 16 == 0);
-    if (vec) silu_mul_kernel<TI, TO, 4><<<dim3((I / 4 + 127) / 128, N), 128, 0, s>>>(gu, out, I, clear_in);
-    else silu_mul_kernel<TI, TO, 1><<<dim3((I + 127) / 128, N), 128, 0, s>>>(gu, out, I, clear_in);
-    return launch_status();
+    if (vec) return launch_kernel(silu_mul_kernel<TI, TO, 4>, dim3((I / 4 + 127) / 128, N), dim3(128), 0, s, gu, out, I, clear_in);
+    return launch_kernel(silu_mul_kernel<TI, TO, 1>, dim3((I + 127) / 128, N), dim3(128), 0, s, gu, out, I, clear_in);
 }
 
 LLMIE_API int llmie_silu_mul(void* gu, void* out, int N, int I, int clear_in, int in_dtype, int out_dtype, cudaStream_t s) {

@@ -128,12 +128,23 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
     const uint32_t tmem = *tmem_slot;
 
+    pdl_trigger();
     if (warp == 0 && lane == 0) {
         asm volatile("prefetch.tensormap [%0];\n" ::"l"(&tmap_w) : "memory");
         asm volatile("prefetch.tensormap [%0];\n" ::"l"(&tmap_x) : "memory");
-        for (int it = 0; it < iters; ++it) {
+        // The weights do not depend on the kernel before this one: the first stages' weight tiles are on their way
+        // before the wait; the token tiles, which that kernel wrote, follow after it.
+        const int early = min(iters, STAGES);
+        for (int it = 0; it < early; ++it) {
+            mbar_expect_tx(full + it, STAGE_BYTES);
+            tma_load_2d(tiles + it * STAGE_BYTES, &tmap_w, (kb0 + it) * BK, n0, full + it);
+            *issued = it + 1;
+        }
+        pdl_wait();
+        for (int it = 0; it < early; ++it) tma_load_2d(tiles + it * STAGE_BYTES + W_BYTES, &tmap_x, (kb0 + it) * BK, m0, full + it);
+        for (int it = early; it < iters; ++it) {
             const int s = it % STAGES;
-            if (it >= STAGES && !mbar_wait(empty + s, ((it / STAGES) & 1) ^ 1, abort_flag, error_flag, 1)) break;
+            if (!mbar_wait(empty + s, ((it / STAGES) & 1) ^ 1, abort_flag, error_flag, 1)) break;
             unsigned char* st = tiles + s * STAGE_BYTES;
             mbar_expect_tx(full + s, STAGE_BYTES);
             tma_load_2d(st, &tmap_w, (kb0 + it) * BK, n0, full + s);
@@ -159,6 +170,7 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
         if (ok) umma_commit(accum);
     }
     __syncwarp();
+    pdl_wait();  // every thread: the epilogue writes where the kernel before may still read or write
     const bool done = __all_sync(0xffffffffu, mbar_wait(accum, 0, abort_flag, error_flag, 3));  // uniform per warp: tcgen05.ld is warp-wide
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
     if (done) {
@@ -251,8 +263,7 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, float* out, int ldo, in
     const int per = (nkb + k_splits - 1) / k_splits;
     const int splits = (nkb + per - 1) / per;  // no empty split
     const dim3 grid((N + BM - 1) / BM, (M + TN - 1) / TN, splits);
-    gemm_tc_kernel<TN><<<grid, 128, smem, s>>>(mw, mx, out, ldo, M, N, K, per, accumulate, error_flag);
-    return launch_status();
+    return launch_kernel(gemm_tc_kernel<TN>, grid, dim3(128), smem, s, mw, mx, out, ldo, M, N, K, per, accumulate, error_flag);
 }
 
 }  // namespace

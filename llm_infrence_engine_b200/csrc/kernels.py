@@ -14,6 +14,7 @@ produces from bfloat16 inputs with a 32-bit accumulator.
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
@@ -53,6 +54,8 @@ class CudaKernels:
         for fn in ("llmie_embed", "llmie_rope_tables", "llmie_add_rmsnorm", "llmie_rope_kv_write", "llmie_silu_mul",
                    "llmie_gemm_simt", "llmie_gemm_tc", "llmie_add_into", "llmie_attn_plan", "llmie_paged_attention_mma", "llmie_paged_attention_f32", "llmie_paged_attention_bf16", "llmie_argmax", "llmie_sample"):
             getattr(self.lib, fn).restype = ctypes.c_int
+        # kernels of a step overlap their set-up with the tail of the kernel before (programmatic dependent launch)
+        self.lib.llmie_set_pdl(0 if os.environ.get("LLMIE_PDL", "1") == "0" else 1)
 
     # ------------------------------------------------------------------ helpers
     @staticmethod

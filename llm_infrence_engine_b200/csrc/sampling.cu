@@ -65,6 +65,8 @@ __device__ __forceinline__ void arg_block_reduce(float& best, int& idx) {
 
 __global__ void __launch_bounds__(ARG_THREADS) argmax_part_kernel(const float* __restrict__ logits, float* __restrict__ part_v,
                                                                  int* __restrict__ part_i, int V, int per) {
+    pdl_trigger();
+    pdl_wait();
     const float* x = logits + (size_t)blockIdx.y * V;
     const int lo = blockIdx.x * per, hi = min(V, lo + per);
     float best = 0.f;
@@ -76,6 +78,8 @@ __global__ void __launch_bounds__(ARG_THREADS) argmax_part_kernel(const float* _
 
 __global__ void __launch_bounds__(ARG_THREADS) argmax_final_kernel(const float* __restrict__ part_v, const int* __restrict__ part_i,
                                                                   int* __restrict__ out, int parts) {
+    pdl_trigger();
+    pdl_wait();
     float best = 0.f;
     int idx = -1;
     for (int i = threadIdx.x; i < parts; i += ARG_THREADS) arg_better(best, idx, part_v[blockIdx.x * parts + i], part_i[blockIdx.x * parts + i]);
@@ -253,11 +257,9 @@ LLMIE_API int llmie_argmax(const float* logits, int* out, float* part_v, int* pa
     if (V <= 0 || M > 65535) return LLMIE_ERR_BAD_ARGUMENT;
     const int parts = 64;
     const int per = (V + parts - 1) / parts;
-    argmax_part_kernel<<<dim3(parts, M), ARG_THREADS, 0, s>>>(logits, part_v, part_i, V, per);
-    int rc = launch_status();
+    int rc = launch_kernel(argmax_part_kernel, dim3(parts, M), dim3(ARG_THREADS), 0, s, logits, part_v, part_i, V, per);
     if (rc) return rc;
-    argmax_final_kernel<<<M, ARG_THREADS, 0, s>>>(part_v, part_i, out, parts);
-    return launch_status();
+    return launch_kernel(argmax_final_kernel, dim3(M), dim3(ARG_THREADS), 0, s, (const float*)part_v, (const int*)part_i, out, parts);
 }
 
 LLMIE_API int llmie_sample(const float* logits, const float* temperature, const int* top_k, const float* top_p,
