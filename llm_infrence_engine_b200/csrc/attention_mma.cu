@@ -201,19 +201,43 @@ __device__ __forceinline__ void finish_tile(const Params& p, const float* row_m,
     __syncthreads();
     if (!*flag_smem) return;
     __threadfence();
-    for (int i = tid; i < nrows * D; i += THREADS) {
-        const int r = i / D, dim = i % D;
+    // Last block of the tile: first the slices' (max, sum) pairs become per-row weights in shared memory (the
+    // block's own row_m / row_l / row_o are not needed any more), then every output element is one weighted sum
+    // whose loads do not depend on each other.
+    float* wgt = const_cast<float*>(row_o);                 // [num_splits][nrows] weights e^(m_s - M) / L
+    float* mx = const_cast<float*>(row_m);                  // [nrows] overall maximum
+    for (int r = tid; r < nrows; r += THREADS) {
         float M = -INFINITY;
         for (int s = 0; s < p.num_splits; ++s) M = fmaxf(M, __ldcg(p.part_ml + (base + s) * ROWS * 2 + 2 * r));
-        float L = 0.f, O = 0.f;
-        if (M > -INFINITY) {
-            for (int s = 0; s < p.num_splits; ++s) {
-                const float f = exp2f(__ldcg(p.part_ml + (base + s) * ROWS * 2 + 2 * r) - M);
-                L = fmaf(__ldcg(p.part_ml + (base + s) * ROWS * 2 + 2 * r + 1), f, L);
-                O = fmaf(__ldcg(p.part_o + (base + s) * ROWS * D + i), f, O);
-            }
+        mx[r] = M;
+    }
+    __syncthreads();
+    for (int i = tid; i < nrows * p.num_splits; i += THREADS) {
+        const int s = i / nrows, r = i % nrows;
+        const float M = mx[r];
+        wgt[i] = M > -INFINITY ? exp2f(__ldcg(p.part_ml + (base + s) * ROWS * 2 + 2 * r) - M) : 0.f;
+    }
+    __syncthreads();
+    for (int r = tid; r < nrows; r += THREADS) {
+        float L = 0.f;
+        for (int s = 0; s < p.num_splits; ++s) L = fmaf(__ldcg(p.part_ml + (base + s) * ROWS * 2 + 2 * r + 1), wgt[s * nrows + r], L);
+        const_cast<float*>(row_l)[r] = L > 0.f ? 1.f / L : 0.f;
+    }
+    __syncthreads();
+    for (int i = tid; i < nrows * D; i += THREADS) {
+        const int r = i / D, dim = i % D;
+        float O = 0.f;
+        int s = 0;
+        for (; s + 4 <= p.num_splits; s += 4) {
+            const float a0 = __ldcg(p.part_o + (base + s) * ROWS * D + i), a1 = __ldcg(p.part_o + (base + s + 1) * ROWS * D + i);
+            const float a2 = __ldcg(p.part_o + (base + s + 2) * ROWS * D + i), a3 = __ldcg(p.part_o + (base + s + 3) * ROWS * D + i);
+            O = fmaf(a0, wgt[s * nrows + r], O);
+            O = fmaf(a1, wgt[(s + 1) * nrows + r], O);
+            O = fmaf(a2, wgt[(s + 2) * nrows + r], O);
+            O = fmaf(a3, wgt[(s + 3) * nrows + r], O);
         }
-        p.out[(size_t)(n0 + r / G) * p.nq * D + (size_t)(kvh * G + r % G) * D + dim] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+        for (; s < p.num_splits; ++s) O = fmaf(__ldcg(p.part_o + (base + s) * ROWS * D + i), wgt[s * nrows + r], O);
+        p.out[(size_t)(n0 + r / G) * p.nq * D + (size_t)(kvh * G + r % G) * D + dim] = __float2bfloat16_rn(O * row_l[r]);
     }
     if (tid == 0) p.counters[tile * p.nkv + kvh] = 0;  // ready for the next launch
 }
@@ -494,7 +518,7 @@ LLMIE_API int llmie_paged_attention_mma(const bf16* q, int q_stride, const bf16*
                                         int page_size, float scale, int window, int num_splits, int decode_mode, cudaStream_t s) {
     if (num_tiles <= 0) return 0;
     if ((d != 64 && d != 128) || nkv <= 0 || nq % nkv || page_size <= 0 || num_splits < 1 || q_stride % 8 || nkv > 65535 ||
-        num_splits > 65535 || (num_splits > 1 && (!scratch_o || !scratch_ml || !counters)))
+        num_splits > 64 || (num_splits > 1 && (!scratch_o || !scratch_ml || !counters)))
         return LLMIE_ERR_BAD_ARGUMENT;
     const int G = nq / nkv;
     if (G > (decode_mode ? 16 : 64)) return LLMIE_ERR_BAD_ARGUMENT;

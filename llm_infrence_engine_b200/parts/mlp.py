@@ -18,6 +18,7 @@ class GatedMLP(FeedForward):
     """
 
     graph_safe = True
+    takes_deferred_input = True
 
     def __init__(self, hidden: int, intermediate: int, prefix: str, activation: str = "silu"):
         if activation not in ACTIVATIONS:
@@ -36,5 +37,4 @@ class GatedMLP(FeedForward):
     def forward(self, ctx, h, residual):
         K = ctx.K
         gu = K.linear(h, self.w_gate_up, transient=True)
-        a = K.silu_mul(gu, out_dtype=ctx.dtype)
-        K.linear(a, self.w_down, add_to=residual)
+        K.linear(K.gated(gu, ctx.dtype), self.w_down, add_to=residual)
