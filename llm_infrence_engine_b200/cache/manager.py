@@ -69,13 +69,14 @@ class PagePool:
 class _Held:
     """What one live request holds."""
 
-    __slots__ = ("slot", "tables", "length", "versions")
+    __slots__ = ("slot", "tables", "length", "versions", "released")
 
     def __init__(self, slot: int, num_groups: int, version: int):
         self.slot = slot
         self.tables: List[List[int]] = [[] for _ in range(num_groups)]
         self.length = 0  # positions covered so far
         self.versions = [version] * num_groups  # changes whenever the group's table changes; never repeats
+        self.released = [0] * num_groups        # pages below this index were given back (windowed groups)
 
 
 class CacheManager:
@@ -142,18 +143,25 @@ class CacheManager:
             return 0
         return max(0, context_len - w + 1) // self.page_size
 
+    def _missing(self, held: "_Held", g: int, context_len: int, new_len: int) -> int:
+        """Pages ``reserve`` would take from group ``g``'s pool, not counting those it gives back first. Pages from the
+        first needed one up to the end of the table are always held, so only the table's growth counts."""
+        want = -(-new_len // self.page_size)
+        first = self._first_needed_page(g, context_len)
+        return max(0, want - max(len(held.tables[g]), first))
+
+    def _passed(self, held: "_Held", g: int, context_len: int) -> int:
+        """Pages of group ``g`` that ``release_passed`` would give back."""
+        if self.groups[g].window is None:
+            return 0
+        first = min(self._first_needed_page(g, context_len), len(held.tables[g]))
+        return max(0, first - held.released[g])
+
     def pages_missing(self, req: Hashable, context_len: int, new_len: int) -> List[int]:
-        """Per group, how many pages ``reserve`` would have to take from the pool beyond those it frees first."""
+        """Per group, how many pages ``reserve`` would have to find in the pool beyond those it frees first."""
         held = self._held[req]
-        out = []
-        for g in range(len(self.groups)):
-            table = held.tables[g]
-            first = self._first_needed_page(g, context_len)
-            want = -(-new_len // self.page_size)
-            have = sum(1 for i in range(first, min(len(table), want)) if table[i] != NULL_PAGE)
-            freed = sum(1 for i in range(0, min(first, len(table))) if table[i] != NULL_PAGE)
-            out.append(max(0, (want - first) - have - freed))
-        return out
+        return [max(0, self._missing(held, g, context_len, new_len) - self._passed(held, g, context_len))
+                for g in range(len(self.groups))]
 
     def can_reserve(self, req: Hashable, context_len: int, new_len: int, spare: int = 0) -> bool:
         missing = self.pages_missing(req, context_len, new_len)
@@ -169,26 +177,21 @@ class CacheManager:
             raise ValueError("new_len is less than context_len")
         held = self._held[req]
         self.release_passed(req, context_len)
-        for g in range(len(self.groups)):
-            table = held.tables[g]
-            want = -(-new_len // self.page_size)
-            first = self._first_needed_page(g, context_len)
-            missing = sum(1 for i in range(first, want) if i >= len(table) or table[i] == NULL_PAGE)
+        groups = range(len(self.groups))
+        for g in groups:
+            missing = self._missing(held, g, context_len, new_len)
             if self.pools[g].num_free < missing:
                 raise OutOfPages(f"group {g}: {missing} pages wanted, {self.pools[g].num_free} free")
-        for g in range(len(self.groups)):
+        for g in groups:
             table = held.tables[g]
             want = -(-new_len // self.page_size)
+            if len(table) >= want:
+                continue
             first = self._first_needed_page(g, context_len)
-            changed = len(table) < want
             while len(table) < want:
-                table.append(NULL_PAGE)
-            for i in range(first, want):
-                if table[i] == NULL_PAGE:
-                    table[i] = self.pools[g].allocate(req)
-                    changed = True
-            if changed:
-                self._bump(held, g)
+                table.append(self.pools[g].allocate(req) if len(table) >= first else NULL_PAGE)
+            held.released[g] = max(held.released[g], min(first, len(table)))
+            self._bump(held, g)
             self.max_blocks_per_seq = max(self.max_blocks_per_seq, len(table))
         held.length = max(held.length, new_len)
 
@@ -200,14 +203,16 @@ class CacheManager:
             if self.groups[g].window is None:
                 continue
             table = held.tables[g]
-            before = n
-            for i in range(min(self._first_needed_page(g, context_len), len(table))):
+            upto = min(self._first_needed_page(g, context_len), len(table))
+            if upto <= held.released[g]:
+                continue
+            for i in range(held.released[g], upto):
                 if table[i] != NULL_PAGE:
                     self.pools[g].free(table[i], req)
                     table[i] = NULL_PAGE
                     n += 1
-            if n != before:
-                self._bump(held, g)
+            held.released[g] = upto
+            self._bump(held, g)
         return n
 
     def free(self, req: Hashable) -> None:

@@ -114,7 +114,7 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     return *reinterpret_cast<const uint32_t*>(&v);
 }
 
-template <int TN>
+template <int TN, int XMODE>
 __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                                                       float* __restrict__ out, int ldo, int M, int N, int K, int kb_per_split,
                                                       int accumulate, int* error_flag, const XSource xs) {
@@ -137,7 +137,7 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
     const int iters = kb1 - kb0;
 
     if (tid == 0) {
-        for (int s = 0; s < STAGES; ++s) { mbar_init(full + s, xs.mode == 0 ? 1 : 3); mbar_init(empty + s, 1); }
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full + s, XMODE == 0 ? 1 : 3); mbar_init(empty + s, 1); }
         mbar_init(accum, 1);
         *abort_flag = 0;
         *issued = 0;
@@ -160,14 +160,14 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
         // The weights do not depend on the kernel before this one: the first stages' weight tiles are on their way
         // before the wait; the token tiles, which that kernel wrote, follow after it.
         const int early = min(iters, STAGES);
-        const uint32_t tx = xs.mode == 0 ? STAGE_BYTES : W_BYTES;
+        constexpr uint32_t tx = XMODE == 0 ? STAGE_BYTES : W_BYTES;
         for (int it = 0; it < early; ++it) {
             mbar_expect_tx(full + it, tx);
             tma_load_2d(tiles + it * STAGE_BYTES, &tmap_w, (kb0 + it) * BK, n0, full + it);
             *issued = it + 1;
         }
         pdl_wait();
-        if (xs.mode == 0)
+        if constexpr (XMODE == 0)
             for (int it = 0; it < early; ++it) tma_load_2d(tiles + it * STAGE_BYTES + W_BYTES, &tmap_x, (kb0 + it) * BK, m0, full + it);
         for (int it = early; it < iters; ++it) {
             const int s = it % STAGES;
@@ -175,7 +175,7 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
             unsigned char* st = tiles + s * STAGE_BYTES;
             mbar_expect_tx(full + s, tx);
             tma_load_2d(st, &tmap_w, (kb0 + it) * BK, n0, full + s);
-            if (xs.mode == 0) tma_load_2d(st + W_BYTES, &tmap_x, (kb0 + it) * BK, m0, full + s);
+            if constexpr (XMODE == 0) tma_load_2d(st + W_BYTES, &tmap_x, (kb0 + it) * BK, m0, full + s);
             *issued = it + 1;
         }
     } else if (warp == 1 && lane == 0) {
@@ -195,43 +195,53 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
             umma_commit(empty + s);
         }
         if (ok) umma_commit(accum);
-    } else if (warp >= 2 && xs.mode != 0) {
+    } else if (XMODE != 0 && warp >= 2) {
         // The two token-tile warps: 64 threads turn float32 rows into the bfloat16 tile of every stage.
         const int t = tid - 64;
         const int rows = min(TN, M - m0);
         pdl_wait();
-        if (xs.mode == 1) {
-            for (int r = 0; r < rows; ++r) {  // 1 / rms of each of the block's rows, over the whole row
-                const float* x = xs.src + (size_t)(m0 + r) * xs.ld;
-                float ss = 0.f;
-                for (int k = t * 4; k < K; k += 64 * 4) {
-                    float v[4];
-                    load4(x + k, v);
-                    ss += v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
+        if constexpr (XMODE == 1) {
+            // Sum of squares of each of the block's rows over the whole row: a warp takes two rows at a time, so the
+            // loads of one row do not wait for the reduction of the other.
+            for (int r = (warp - 2) * 2; r < rows; r += 4) {
+                const bool two = r + 1 < rows;
+                const float* x0 = xs.src + (size_t)(m0 + r) * xs.ld;
+                const float* x1 = xs.src + (size_t)(m0 + (two ? r + 1 : r)) * xs.ld;
+                float s0 = 0.f, s1 = 0.f;
+                for (int k = lane * 4; k < K; k += 32 * 4) {
+                    float a[4], b[4];
+                    load4(x0 + k, a);
+                    load4(x1 + k, b);
+                    s0 += a[0] * a[0] + a[1] * a[1] + a[2] * a[2] + a[3] * a[3];
+                    s1 += b[0] * b[0] + b[1] * b[1] + b[2] * b[2] + b[3] * b[3];
                 }
-                ss = warp_sum(ss);
-                if (lane == 0) rstd[TN + (warp - 2) * TN + r] = ss;  // two partial sums per row, one per warp
+                s0 = warp_sum(s0);
+                s1 = warp_sum(s1);
+                if (lane == 0) { rstd[TN + r] = s0; if (two) rstd[TN + r + 1] = s1; }
             }
             named_sync_64();
-            for (int r = t; r < rows; r += 64) rstd[r] = 1.0f / sqrtf((rstd[TN + r] + rstd[2 * TN + r]) / (float)K + xs.eps);
+            for (int r = t; r < rows; r += 64) rstd[r] = 1.0f / sqrtf(rstd[TN + r] / (float)K + xs.eps);
             named_sync_64();
         }
+        // Tiles are made for a whole round of the ring at once (up to STAGES k-blocks): the loads of all of them are
+        // independent, so a round costs one trip to memory instead of one per stage.
         bool ok = true;
-        for (int it = 0; it < iters && ok; ++it) {
-            const int s = it % STAGES;
-            if (it >= STAGES) {
-                if (lane == 0) ok = mbar_wait(empty + s, ((it / STAGES) & 1) ^ 1, abort_flag, error_flag, 4);
+        for (int g0 = 0; g0 < iters && ok; g0 += STAGES) {
+            const int gn = min(STAGES, iters - g0);
+            if (g0 > 0) {
+                if (lane == 0)
+                    for (int st = 0; st < gn && ok; ++st) ok = mbar_wait(empty + st, (((g0 + st) / STAGES) & 1) ^ 1, abort_flag, error_flag, 4);
                 ok = __shfl_sync(0xffffffffu, ok, 0);
                 if (!ok) break;
             }
-            unsigned char* xt = tiles + s * STAGE_BYTES + W_BYTES;
-            const int k0 = (kb0 + it) * BK;
-            for (int c = t; c < TN * 8; c += 64) {
-                const int r = c >> 3, ch = c & 7, k = k0 + ch * 8;
+#pragma unroll 4
+            for (int c = t; c < gn * TN * 8; c += 64) {
+                const int st = c / (TN * 8), rem = c % (TN * 8);
+                const int r = rem >> 3, ch = rem & 7, k = (kb0 + g0 + st) * BK + ch * 8;
                 uint4 packed = make_uint4(0, 0, 0, 0);
                 if (r < rows && k < K) {
                     float a[8], y[8];
-                    if (xs.mode == 1) {
+                    if constexpr (XMODE == 1) {
                         const float* x = xs.src + (size_t)(m0 + r) * xs.ld + k;
                         float w[8];
                         load4(x, a); load4(x + 4, a + 4);
@@ -249,13 +259,14 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
                     }
                     packed.x = pack2(y[0], y[1]); packed.y = pack2(y[2], y[3]); packed.z = pack2(y[4], y[5]); packed.w = pack2(y[6], y[7]);
                 }
-                *reinterpret_cast<uint4*>(xt + r * 128 + ((ch ^ (r & 7)) << 4)) = packed;
+                *reinterpret_cast<uint4*>(tiles + st * STAGE_BYTES + W_BYTES + r * 128 + ((ch ^ (r & 7)) << 4)) = packed;
             }
             asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // the tensor core reads shared memory through the async proxy
             __syncwarp();
-            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(full + s)) : "memory");
+            if (lane == 0)
+                for (int st = 0; st < gn; ++st) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(full + st)) : "memory");
         }
-        if (xs.mode == 2 && ok) {
+        if (XMODE == 2 && ok) {
             // Whichever warp (two per block, over all blocks of the slice) finishes reading this (row tile, K slice)
             // last sets it back to zero. Warp-level only: no barrier that a warp which gave up could leave hanging.
             __threadfence();
@@ -357,13 +368,13 @@ int tensor_map(const void* base, int rows, int K, int box_rows, CUtensorMap* out
     return 0;
 }
 
-template <int TN>
+template <int TN, int XMODE>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, float* out, int ldo, int M, int N, int K, int k_splits, int accumulate,
            int* error_flag, const XSource& xs, cudaStream_t s) {
     constexpr size_t smem = (size_t)STAGES * (BM * BK * 2 + TN * BK * 2) + 1024 + 256 + 3 * TN * sizeof(float);
     static bool set = false;
     if (!set) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<TN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<TN, XMODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         set = true;
     }
@@ -371,7 +382,7 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, float* out, int ldo, in
     const int per = (nkb + k_splits - 1) / k_splits;
     const int splits = (nkb + per - 1) / per;  // no empty split
     const dim3 grid((N + BM - 1) / BM, (M + TN - 1) / TN, splits);
-    return launch_kernel(gemm_tc_kernel<TN>, grid, dim3(128), smem, s, mw, mx, out, ldo, M, N, K, per, accumulate, error_flag, xs);
+    return launch_kernel(gemm_tc_kernel<TN, XMODE>, grid, dim3(128), smem, s, mw, mx, out, ldo, M, N, K, per, accumulate, error_flag, xs);
 }
 
 
@@ -395,9 +406,16 @@ static int run(const bf16* x, const bf16* w, float* out, int ldo, int M, int N, 
             return LLMIE_ERR_BAD_ARGUMENT;
         mx = mw;  // not read
     }
-    if (TN == 16) return launch<16>(mw, mx, out, ldo, M, N, K, k_splits, accumulate, error_flag, xs, s);
-    if (TN == 32) return launch<32>(mw, mx, out, ldo, M, N, K, k_splits, accumulate, error_flag, xs, s);
-    return launch<64>(mw, mx, out, ldo, M, N, K, k_splits, accumulate, error_flag, xs, s);
+#define LLMIE_TC_LAUNCH(MODE)                                                                                        \
+    do {                                                                                                            \
+        if (TN == 16) return launch<16, MODE>(mw, mx, out, ldo, M, N, K, k_splits, accumulate, error_flag, xs, s); \
+        if (TN == 32) return launch<32, MODE>(mw, mx, out, ldo, M, N, K, k_splits, accumulate, error_flag, xs, s); \
+        return launch<64, MODE>(mw, mx, out, ldo, M, N, K, k_splits, accumulate, error_flag, xs, s);               \
+    } while (0)
+    if (xs.mode == 0) LLMIE_TC_LAUNCH(0);
+    if (xs.mode == 1) LLMIE_TC_LAUNCH(1);
+    LLMIE_TC_LAUNCH(2);
+#undef LLMIE_TC_LAUNCH
 }
 
 }  // namespace

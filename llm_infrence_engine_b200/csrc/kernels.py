@@ -70,7 +70,11 @@ class CudaKernels:
         self.tc_max_rows = 128        # batches up to this many rows take the small-batch tensor-core product
         self._acc: Optional[torch.Tensor] = None  # float32 zeros: split-K products add into it, their consumer clears it again
         self._slice_counters: Optional[torch.Tensor] = None
-        self.fuse_into_gemm = True    # fold the norm before a product, and silu(gate) * up, into the tensor-core product
+        # Fold the norm before a product, and silu(gate) * up, into the tensor-core product. Off: measured on a B200 the
+        # separate kernels (whose launch overlaps the product's weight fetch) are faster at every batch size, because a
+        # block that makes its own token tiles adds a trip to memory between the wait and the first MMA.
+        self.fuse_into_gemm = False
+        self.fuse_max_rows = 16       # ... for batches up to this many rows: every block redoes the row work, which must stay small
         self._error_flag: Optional[torch.Tensor] = None
         self.num_sms = torch.cuda.get_device_properties(0).multi_processor_count or NUM_SMS_FALLBACK
         for fn in ("llmie_embed", "llmie_rope_tables", "llmie_add_rmsnorm", "llmie_rope_kv_write", "llmie_silu_mul",
@@ -171,7 +175,7 @@ class CudaKernels:
     def gated(self, gu, out_dtype):
         """``silu(gate) * up`` of a fused gate/up projection, for ``linear``: deferred when ``gu`` is a transient float32
         accumulation (the product applies it and clears the accumulation), computed right away otherwise."""
-        if self.fuse_into_gemm and self._is_transient(gu) and gu.shape[0] <= self.tc_max_rows and (gu.shape[1] // 2) % 8 == 0:
+        if self.fuse_into_gemm and self._is_transient(gu) and gu.shape[0] <= self.fuse_max_rows and (gu.shape[1] // 2) % 8 == 0:
             return DeferredGate(gu, out_dtype)
         return self.silu_mul(gu, out_dtype)
 
@@ -195,7 +199,8 @@ class CudaKernels:
         N = w.shape[0]
         if deferred:
             fusable = (self.fuse_into_gemm and self.use_tc_gemm and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
-                       and M <= self.tc_max_rows and K % 8 == 0 and (add_to is not None or transient or out_dtype == torch.float32))
+                       and (M <= self.fuse_max_rows or isinstance(x, DeferredGate)) and K % 8 == 0
+                       and (add_to is not None or transient or out_dtype == torch.float32))
             if not fusable:
                 x = self.materialize(x)
                 deferred = False

@@ -118,7 +118,7 @@ class Engine:
         if plan.items:
             entries = []
             for s in plan.items:
-                ids = s.req.all_ids[s.start:s.start + s.count]
+                ids = s.req.tokens(s.start, s.start + s.count)
                 if s.req.admitted_time is None:
                     s.req.admitted_time = now
                 entries.append(StepEntry(s.req.id, ids, s.start, (s.count - 1,) if s.samples else ()))

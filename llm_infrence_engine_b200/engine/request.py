@@ -36,6 +36,20 @@ class Request:
         return self.prompt_ids + self.output_ids
 
     @property
+    def num_tokens(self) -> int:
+        """Tokens known so far: prompt plus output."""
+        return len(self.prompt_ids) + len(self.output_ids)
+
+    def tokens(self, start: int, stop: int) -> List[int]:
+        """``all_ids[start:stop]`` without joining the two lists."""
+        p = len(self.prompt_ids)
+        if stop <= p:
+            return self.prompt_ids[start:stop]
+        if start >= p:
+            return self.output_ids[start - p:stop - p]
+        return self.prompt_ids[start:] + self.output_ids[:stop - p]
+
+    @property
     def ttft(self) -> Optional[float]:
         return None if self.first_token_time is None else self.first_token_time - self.arrival_time
 

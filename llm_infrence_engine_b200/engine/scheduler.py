@@ -107,11 +107,11 @@ class Scheduler:
         budget = self.budget
         before = self.preemptions
         # running requests: those that decode first, then prompts in progress, each group oldest first
-        order = sorted(self.running, key=lambda r: (len(r.all_ids) - r.num_computed > 1, r.admit_seq))
+        order = sorted(self.running, key=lambda r: (r.num_tokens - r.num_computed > 1, r.admit_seq))
         for r in order:
             if r.state != "running" or budget <= 0:
                 continue
-            pending = len(r.all_ids) - r.num_computed
+            pending = r.num_tokens - r.num_computed
             count = min(pending, budget)
             while True:
                 try:
@@ -134,7 +134,7 @@ class Scheduler:
         while self.waiting and not plan.preempted and budget > 0 and len(self.running) < self.max_seqs \
                 and self.cache.num_free_slots() > 0:
             r = self.waiting[0]
-            pending = len(r.all_ids)
+            pending = r.num_tokens
             count = min(pending, budget)
             self.cache.admit(r.id)
             if not self.cache.can_reserve(r.id, 0, count, spare=len(self.running)):

@@ -136,6 +136,8 @@ class ModelRunner:
                 raise ValueError(f"request {e.req!r} brings no tokens to the step")
             if e.context_len + n > self.max_len:
                 raise ValueError(f"request {e.req!r} would reach {e.context_len + n} tokens, more than max_len {self.max_len}")
+        if max(lens) == 1:
+            return self._build_single_tokens(entries, ctxs, slots, pad_to)
         ids = np.concatenate([np.asarray(e.tokens, dtype=np.int64) for e in entries])
         if ids.min() < 0 or ids.max() >= vocab:
             bad = int(ids[(ids < 0) | (ids >= vocab)][0])
@@ -163,8 +165,13 @@ class ModelRunner:
                 t = cache.block_table(e.req, g)
                 if len(t) * ps < c + n:
                     raise ValueError(f"request {e.req!r} has {len(t)} pages in group {g} but the step needs {-(-(c + n) // ps)}")
-                p = np.arange(c, c + n, dtype=np.int64)
-                pages = np.asarray(t, dtype=np.int64)[p // ps]
+                if n == 1:
+                    pages = np.asarray([t[c // ps]], dtype=np.int64)
+                    p = np.asarray([c], dtype=np.int64)
+                else:
+                    p = np.arange(c, c + n, dtype=np.int64)
+                    first = c // ps
+                    pages = np.asarray(t[first:(c + n - 1) // ps + 1], dtype=np.int64)[p // ps - first]
                 if (pages == NULL_PAGE).any():
                     raise ValueError(f"request {e.req!r}: a position of the step has no page in group {g}")
                 maps.append(pages * ps + p % ps)
@@ -184,6 +191,55 @@ class ModelRunner:
                     offset += self.max_blocks
         packed = np.concatenate(parts).astype(np.int32)
         return packed, N + pad, R + pad, M + (pad if pad_to else 0), changed, [int(x) for x in starts], lens, ctxs, slots
+
+    def _build_single_tokens(self, entries, ctxs, slots, pad_to: int):
+        """``_build`` for steps in which every request brings one token (decoding): plain lists, one array at the end."""
+        cache, ps = self.cache, self.page_size
+        groups = len(cache.groups)
+        vocab = self.spec.embedding.vocab
+        R = len(entries)
+        ids = [int(e.tokens[0]) for e in entries]
+        for t in ids:
+            if not 0 <= t < vocab:
+                raise ValueError(f"token {t} is outside the vocabulary of {vocab}")
+        rows = []
+        for i, e in enumerate(entries):
+            for w in e.want:
+                if int(w) != 0:
+                    raise ValueError(f"request {e.req!r}: wanted place {w} is outside its 1 tokens")
+                rows.append(i)
+        pad = max(0, pad_to - R)
+        zeros = [0] * pad
+        packed = (ids + zeros + ctxs + zeros + slots + [self.max_seqs] * pad + slots + zeros + list(range(R + pad + 1)) + rows
+                  + (list(range(R, R + pad)) if pad_to else []))
+        for g in range(groups):
+            for e, c in zip(entries, ctxs):
+                t = cache.block_table(e.req, g)
+                page = t[c // ps] if c // ps < len(t) else NULL_PAGE
+                if page == NULL_PAGE:
+                    raise ValueError(f"request {e.req!r}: position {c} has no page in group {g}")
+                packed.append(page * ps + c % ps)
+            packed += zeros
+        changed = []
+        tables = []
+        offset = len(packed)
+        for g in range(groups):
+            for e, slot in zip(entries, slots):
+                v = cache.table_version(e.req, g)
+                if self._synced[g][slot] != v:
+                    t = cache.block_table(e.req, g)
+                    if len(t) > self.max_blocks:
+                        raise ValueError(f"request {e.req!r} holds {len(t)} pages, more than max_len allows")
+                    row = np.zeros(self.max_blocks, np.int32)
+                    row[:len(t)] = t
+                    tables.append(row)
+                    changed.append((g, slot, offset, v))
+                    offset += self.max_blocks
+        arr = np.asarray(packed, dtype=np.int32)
+        if tables:
+            arr = np.concatenate([arr] + tables)
+        M = len(rows) + (pad if pad_to else 0)
+        return arr, R + pad, R + pad, M, changed, list(range(R)), [1] * R, ctxs, slots
 
     def _stage(self, packed: "np.ndarray") -> torch.Tensor:
         """The pinned buffer that holds ``packed`` for one asynchronous copy. The buffers form a ring: one is

@@ -367,7 +367,7 @@ def test_linear_tc_with_the_norm_folded_in(K, M, H, N, splits):
         assert torch.equal(r.cpu(), res)
 
 
-@pytest.mark.parametrize("M,I,N,splits", [(8, 4864, 896, 38), (1, 64, 128, 1), (33, 200, 72, 2), (128, 512, 256, 4)])
+@pytest.mark.parametrize("M,I,N,splits", [(8, 4864, 896, 38), (1, 64, 128, 1), (16, 200, 72, 2), (13, 512, 256, 4)])
 def test_linear_tc_with_the_gate_folded_in(K, M, I, N, splits):
     from llm_infrence_engine_b200.csrc.kernels import DeferredGate
 
@@ -380,8 +380,7 @@ def test_linear_tc_with_the_gate_folded_in(K, M, I, N, splits):
     want = res.double() + REF.silu_mul(gu_ref).to(torch.bfloat16).double() @ wd.double().T
     for _ in range(2):
         gu = K.linear(x.cuda(), wgu.cuda(), transient=True)
-        gated = K.gated(gu, torch.bfloat16)
-        assert isinstance(gated, DeferredGate)
+        gated = DeferredGate(gu, torch.bfloat16)
         r = res.clone().cuda()
         K.linear_tc(gated, wd.cuda(), out=r, accumulate=True, k_splits=splits)
         K.check_device_errors()
