@@ -65,7 +65,7 @@ def peaks() -> dict:
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons of GPU 0 every 200 ms while running."""
+    """nvidia-smi clocks and throttle reasons of GPU 0 every 100 ms while running."""
 
     Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
@@ -75,7 +75,7 @@ class ClockSampler:
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200"],
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
@@ -112,15 +112,16 @@ def flops_prefill(T: int) -> float:
 
 
 def reference_arm() -> int:
-    why = "the reference is a pure-Python package that downloads Qwen2.5-0.5B-Instruct from the network at start; not installed here"
-    ref = ROOT / "baseline" / "_ref" / "miniserve"
-    if ref.is_dir():
-        why = "the reference needs the downloaded Qwen2.5-0.5B-Instruct checkpoint and tokenizer; there is no network"
+    """The reference cannot be installed offline: its build backend (hatchling) is not in the wheelhouse, so
+    ``pip install --no-index --no-build-isolation --find-links /opt/wheelhouse --target baseline/_ref`` stops with
+    "No module named 'hatchling'"; and its public entry (``load_model``) downloads its checkpoint and tokenizer."""
+    why = ("pip install of the reference fails offline: its build backend hatchling is not in the wheelhouse "
+           "(ModuleNotFoundError: No module named 'hatchling'); its load_model() also needs a network download")
     print(json.dumps({"impl": "reference", "unavailable": why}))
     return 0
 
 
-def decode_point(folder: Path, batch: int, steps: int, warmup: int, torch, graphs: bool = True) -> dict:
+def decode_point(folder: Path, batch: int, steps: int, warmup: int, torch, graphs: bool = True, sampler=None) -> dict:
     """Device time of ``steps`` decode steps of ``batch`` requests at CONTEXT tokens: the step function
     (replayed from its CUDA graph unless ``graphs`` is off) plus the argmax over its logits."""
     from llm_infrence_engine_b200.config import EngineConfig
@@ -161,6 +162,12 @@ def decode_point(folder: Path, batch: int, steps: int, warmup: int, torch, graph
     for _ in range(warmup):
         one()
     torch.cuda.synchronize()
+    if sampler is not None:
+        sampler.start()
+        for _ in range(min(steps, 200)):  # bring the clocks up before the samples count
+            one()
+        torch.cuda.synchronize()
+        sampler.rows.clear()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record()
     for _ in range(steps):
@@ -168,6 +175,8 @@ def decode_point(folder: Path, batch: int, steps: int, warmup: int, torch, graph
     stop.record()
     torch.cuda.synchronize()
     ms = start.elapsed_time(stop) / steps
+    if sampler is not None:
+        sampler.clocks = sampler.stop()
     out = {"ms": ms, "tok_s": batch / ms * 1e3, "launches": per_step * steps,
            "bytes": runner.weight_bytes_per_step() + batch * CONTEXT * runner.kv_bytes_per_token}
     del runner, spec, cache
@@ -238,7 +247,7 @@ def e2e_point(folder: Path, batch: int, steps: int, warmup: int, torch, graphs: 
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--steps", type=int, default=1024)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
@@ -265,13 +274,12 @@ def main() -> int:
     with tempfile.TemporaryDirectory() as tmp:
         folder = write_random_model(model, Path(tmp) / "model", seed=0, store_dtype="bfloat16")
         sampler = ClockSampler()
-        sampler.start()
-        main_pt = decode_point(folder, a.batch, a.steps if a.only != "prefill" else 3, a.warmup, torch, graphs)
-        clocks = sampler.stop()
-        b1 = decode_point(folder, 1, a.steps, a.warmup, torch, graphs) if a.only == "all" else None
-        b64 = decode_point(folder, 64, max(8, a.steps // 4), a.warmup, torch, graphs) if a.only == "all" else None
+        main_pt = decode_point(folder, a.batch, a.steps if a.only != "prefill" else 3, a.warmup, torch, graphs, sampler)
+        clocks = sampler.clocks
+        b1 = decode_point(folder, 1, min(a.steps, 256), a.warmup, torch, graphs) if a.only == "all" else None
+        b64 = decode_point(folder, 64, min(a.steps, 128), a.warmup, torch, graphs) if a.only == "all" else None
         pre = prefill_point(folder, torch) if a.only in ("all", "prefill") else None
-        e2e = None if (a.skip_e2e or a.only != "all") else e2e_point(folder, a.batch, a.steps, a.warmup, torch, graphs)
+        e2e = None if (a.skip_e2e or a.only != "all") else e2e_point(folder, a.batch, min(a.steps, 512), a.warmup, torch, graphs)
 
     fl = flops_prefill(PREFILL_TOKENS) * a.layers / MODEL["num_hidden_layers"]
     achieved = main_pt["bytes"] / (main_pt["ms"] * 1e-3) / 1e9
