@@ -245,3 +245,62 @@ def test_decode_from_cuda_graphs_matches_eager(models, dtype):
     assert torch.equal(out[True], out[False])
     ref = torch.stack([want[k][i] for i in range(33, 60) for k in ("a", "b", "c")] + [want[k][i] for i in range(60, 64) for k in ("a", "c")])
     check(out[True], ref, dtype, "graph decode vs plain")
+
+
+HALF_B = dict(CONFIGS["A"], vocab_size=151936, hidden_size=896, intermediate_size=4864, num_hidden_layers=2, num_attention_heads=14,
+              num_key_value_heads=2, rms_norm_eps=1e-6, rope_theta=1e6, tie_word_embeddings=True, max_position_embeddings=32768)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_layer_sizes_of_the_half_billion_model(tmp_path, dtype):
+    """Two layers with the real widths (hidden 896, 14 / 2 heads of 64, intermediate 4864, vocabulary 151936): the sizes
+    at which serving runs the tensor-core kernels. Whole, cut into portions, decoded, mixed, and from CUDA graphs."""
+    from llm_infrence_engine_b200.config import EngineConfig
+    from llm_infrence_engine_b200.engine import StepEntry, build_runner
+    from llm_infrence_engine_b200.weights import write_random_model
+
+    folder = write_random_model(HALF_B, tmp_path / "half_b", 4, dtype)
+    cfg, w = plain_load(folder)
+    pa, pb = random_prompt(151936, 150, 1), random_prompt(151936, 70, 2)
+    want_a, want_b = plain_forward(cfg, w, pa), plain_forward(cfg, w, pb)
+    from llm_infrence_engine_b200.engine import TraceReplayer
+
+    rp = TraceReplayer(str(folder), dtype, 320)
+    got = rp.step({"step": 0, "entries": [{"id": "a", "tokens": pa, "want": list(range(150))}], "end": ["a"]})
+    assert first_bad(got, want_a, dtype) is None, f"whole: first wrong position {first_bad(got, want_a, dtype)}"
+    # a in portions (one of two tokens) while b decodes token by token beside it, then a decodes too
+    outs = {"a": [], "b": []}
+    cuts_a = [(0, 64), (64, 66), (66, 130)] + [(i, i + 1) for i in range(130, 150)]
+    for step in range(max(len(cuts_a), 70)):
+        entries = []
+        if step < len(cuts_a):
+            lo, hi = cuts_a[step]
+            entries.append({"id": "a", "tokens": pa[lo:hi], "want": list(range(hi - lo))})
+        if step < 70:
+            entries.append({"id": "b", "tokens": [pb[step]], "want": [0]})
+        out = rp.step({"step": step, "entries": entries, "end": []})
+        o = 0
+        for e in entries:
+            outs[e["id"]].append(out[o:o + len(e["tokens"])])
+            o += len(e["tokens"])
+    for k, want in (("a", want_a), ("b", want_b)):
+        got = torch.cat(outs[k])
+        assert first_bad(got, want, dtype) is None, f"{k}: first wrong position {first_bad(got, want, dtype)}"
+    rp.runner.K.check_device_errors()
+    # the same decoding through captured graphs
+    ec = EngineConfig(dtype=dtype, block_size=16, num_blocks=40, max_seqs=4, max_len=160, max_num_batched_tokens=256, cuda_graphs=True)
+    spec, cache, runner = build_runner(folder, ec)
+    for k in ("a", "b"):
+        cache.admit(k)
+        cache.reserve(k, 0, 40)
+    runner.step([StepEntry("a", pa[:40], 0, ()), StepEntry("b", pb[:40], 0, ())])
+    got_a, got_b = [], []
+    for i in range(40, 70):
+        for k in ("a", "b"):
+            cache.reserve(k, i, i + 1)
+        out = runner.step([StepEntry("a", [pa[i]], i, (0,)), StepEntry("b", [pb[i]], i, (0,))]).float().cpu()
+        got_a.append(out[0]); got_b.append(out[1])
+    assert runner.graphs.replays == 30
+    check(torch.stack(got_a), want_a[40:70], dtype, "graphs, request a")
+    check(torch.stack(got_b), want_b[40:70], dtype, "graphs, request b")
+    runner.K.check_device_errors()
