@@ -5,8 +5,8 @@
 // row r is token n0 + r / G, head kvh * G + r % G (G = query heads per key/value head). All rows of
 // a tile read the same keys and values, so a page is fetched once for the whole group.
 //
-//   decode kernel   one tile = up to 16 rows (one token of up to 16 heads, or a few tokens). The four
-//                   warps of a block split the KEYS: each warp streams its own 64-key (or 32-key)
+//   decode kernel   one tile = up to 16 rows (one token of up to 16 heads, or a few tokens). The eight
+//                   warps of a block split the KEYS: each warp streams its own 32-key (or 16-key)
 //                   chunks through a private cp.async ring, keeps its own running (max, sum, output)
 //                   and the warps are merged in shared memory at the end.
 //   prefill kernel  one tile = up to 64 rows (64 / G consecutive tokens of one request). The four warps
@@ -39,6 +39,7 @@ struct Params {
     float* part_ml;         // [tiles][nkv][splits][ROWS][2]
     int* counters;          // [tiles * nkv], zero between launches
     int q_stride, max_blocks, nq, nkv, page_size, window, num_splits;
+    int cluster;            // 1: the slices of a tile are one thread-block cluster and merge through distributed shared memory
     float scale_log2;       // softmax scale * log2(e)
 };
 
@@ -65,6 +66,18 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], 
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ float ld_cluster(const float* local, int rank) {  // the same shared-memory word in block `rank` of the cluster
+    uint32_t remote;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(remote) : "r"((uint32_t)__cvta_generic_to_shared(local)), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];\n" : "=f"(v) : "r"(remote));  // no memory clobber: loads may be in flight together
+    return v;
 }
 
 // Element (row, col) of a [rows][D] bfloat16 tile in shared memory; 16-byte chunks of a row are
@@ -243,8 +256,8 @@ __device__ __forceinline__ void finish_tile(const Params& p, const float* row_m,
 }
 
 // ---------------------------------------------------------------------------------------------- decode
-template <int D, int BN, int STAGES>
-__global__ void __launch_bounds__(WARPS * 32) attn_mma_decode_kernel(const Params p) {
+template <int D, int BN, int STAGES, int DW>
+__global__ void __launch_bounds__(DW * 32) attn_mma_decode_kernel(const Params p) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     constexpr int TILE = BN * D;                       // elements of one K or V chunk
@@ -287,25 +300,25 @@ __global__ void __launch_bounds__(WARPS * 32) attn_mma_decode_kernel(const Param
     for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
 
-    // this warp's chunks: c_begin + warp, + WARPS, ...
+    // this warp's chunks: c_begin + warp, + DW, ...
     const int first = c_begin + warp;
-    const int mine = first < c_end ? (c_end - first + WARPS - 1) / WARPS : 0;
+    const int mine = first < c_end ? (c_end - first + DW - 1) / DW : 0;
 #pragma unroll
     for (int s = 0; s < STAGES - 1; ++s) {
-        if (s < mine) load_rows_warp<D, BN>(p, table, kvh, lo + (first + s * WARPS) * BN, hi - 1, 0, my + s * 2 * TILE, my + s * 2 * TILE + TILE, lane);
+        if (s < mine) load_rows_warp<D, BN>(p, table, kvh, lo + (first + s * DW) * BN, hi - 1, 0, my + s * 2 * TILE, my + s * 2 * TILE + TILE, lane);
         cp_async_commit();
     }
     for (int it = 0; it < mine; ++it) {
         const int nxt = it + STAGES - 1;
         if (nxt < mine) {
             bf16* dst = my + (nxt % STAGES) * 2 * TILE;
-            load_rows_warp<D, BN>(p, table, kvh, lo + (first + nxt * WARPS) * BN, hi - 1, 0, dst, dst + TILE, lane);
+            load_rows_warp<D, BN>(p, table, kvh, lo + (first + nxt * DW) * BN, hi - 1, 0, dst, dst + TILE, lane);
         }
         cp_async_commit();
         cp_async_wait<STAGES - 1>();
         __syncwarp();
         const bf16* cur = my + (it % STAGES) * 2 * TILE;
-        attend_chunk<D, BN>(qa, cur, cur + TILE, o, m, l, lo + (first + it * WARPS) * BN, row_pos, row_ok, p.window, p.scale_log2, lane);
+        attend_chunk<D, BN>(qa, cur, cur + TILE, o, m, l, lo + (first + it * DW) * BN, row_pos, row_ok, p.window, p.scale_log2, lane);
         __syncwarp();
     }
     cp_async_wait<0>();
@@ -315,10 +328,10 @@ __global__ void __launch_bounds__(WARPS * 32) attn_mma_decode_kernel(const Param
         l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
     }
     __syncthreads();  // every warp is done with its ring; the space is reused for the merge
-    float* wm = reinterpret_cast<float*>(smem_raw);        // [WARPS][16]
-    float* wl = wm + WARPS * 16;                           // [WARPS][16]
-    float* wo = wl + WARPS * 16;                           // [WARPS][16][D]
-    float* fm = wo + WARPS * 16 * D;                       // merged [16], [16], [16][D]
+    float* wm = reinterpret_cast<float*>(smem_raw);        // [DW][16]
+    float* wl = wm + DW * 16;                           // [DW][16]
+    float* wo = wl + DW * 16;                           // [DW][16][D]
+    float* fm = wo + DW * 16 * D;                       // merged [16], [16], [16][D]
     float* fl = fm + 16;
     float* fo = fl + 16;
 #pragma unroll
@@ -333,15 +346,15 @@ __global__ void __launch_bounds__(WARPS * 32) attn_mma_decode_kernel(const Param
         }
     }
     __syncthreads();
-    for (int i = tid; i < 16 * D; i += WARPS * 32) {
+    for (int i = tid; i < 16 * D; i += DW * 32) {
         const int r = i / D, dim = i % D;
         float M = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < WARPS; ++w) M = fmaxf(M, wm[w * 16 + r]);
+        for (int w = 0; w < DW; ++w) M = fmaxf(M, wm[w * 16 + r]);
         float L = 0.f, O = 0.f;
         if (M > -INFINITY) {
 #pragma unroll
-            for (int w = 0; w < WARPS; ++w) {
+            for (int w = 0; w < DW; ++w) {
                 const float f = exp2f(wm[w * 16 + r] - M);
                 L = fmaf(wl[w * 16 + r], f, L);
                 O = fmaf(wo[(w * 16 + r) * D + dim], f, O);
@@ -351,7 +364,44 @@ __global__ void __launch_bounds__(WARPS * 32) attn_mma_decode_kernel(const Param
         if (dim == 0) { fm[r] = M; fl[r] = L; }
     }
     __syncthreads();
-    finish_tile<D, 16, WARPS * 32>(p, fm, fl, fo, tile, kvh, split, n0, nrows, G, &flag);
+    if (p.cluster && p.num_splits > 1) {
+        // The slices of this tile are the blocks of one cluster: block 0 reads every block's (max, sum, output) out of
+        // its shared memory and writes the rows. Nothing goes through global memory and nobody waits on a counter.
+        cluster_sync_all();
+        if (split == 0) {
+            // (max[16], sum[16], output[16][D]) of every block lie in one run of shared memory starting at fm: bring all of
+            // them here with loads that do not wait for each other, then merge locally.
+            constexpr int RUN = 32 + 16 * D;
+            float* stage = fo + 16 * D;  // behind the block's own run; the rings' space is free now
+            const int total = p.num_splits * RUN;
+#pragma unroll 8
+            for (int idx = tid; idx < total; idx += DW * 32) stage[idx] = ld_cluster(fm + idx % RUN, idx / RUN);
+            __syncthreads();
+            float* wgt = wm;      // [splits][16] weights, reusing the warps' merge space
+            float* linv = wl;     // [16]
+            for (int r = tid; r < nrows; r += DW * 32) {
+                float M = -INFINITY;
+                for (int s2 = 0; s2 < p.num_splits; ++s2) M = fmaxf(M, stage[s2 * RUN + r]);
+                float L = 0.f;
+                for (int s2 = 0; s2 < p.num_splits; ++s2) {
+                    const float f = M > -INFINITY ? exp2f(stage[s2 * RUN + r] - M) : 0.f;
+                    wgt[s2 * 16 + r] = f;
+                    L = fmaf(stage[s2 * RUN + 16 + r], f, L);
+                }
+                linv[r] = L > 0.f ? 1.f / L : 0.f;
+            }
+            __syncthreads();
+            for (int i = tid; i < nrows * D; i += DW * 32) {
+                const int r = i / D, dim = i % D;
+                float O = 0.f;
+                for (int s2 = 0; s2 < p.num_splits; ++s2) O = fmaf(stage[s2 * RUN + 32 + i], wgt[s2 * 16 + r], O);
+                p.out[(size_t)(n0 + r / G) * p.nq * D + (size_t)(kvh * G + r % G) * D + dim] = __float2bfloat16_rn(O * linv[r]);
+            }
+        }
+        cluster_sync_all();  // the other blocks' shared memory stays until block 0 has read it
+        return;
+    }
+    finish_tile<D, 16, DW * 32>(p, fm, fl, fo, tile, kvh, split, n0, nrows, G, &flag);
 }
 
 // ---------------------------------------------------------------------------------------------- prefill
@@ -477,17 +527,34 @@ template <int D>
 int launch(const Params& p, int num_tiles, int decode_mode, cudaStream_t s) {
     const dim3 grid(num_tiles, p.nkv, p.num_splits);
     if (decode_mode) {
-        constexpr int BN = D == 64 ? 64 : 32, STAGES = 3;
-        constexpr size_t ring = (size_t)WARPS * STAGES * 2 * BN * D * sizeof(bf16);
-        constexpr size_t merge = (size_t)(WARPS * 16 * (D + 2) + 16 * (D + 2)) * sizeof(float);
+        constexpr int BN = D == 64 ? 32 : 16, STAGES = 3, DW = 8;  // eight warps, each with its own ring of 4 KB + 4 KB chunks
+        constexpr size_t ring = (size_t)DW * STAGES * 2 * BN * D * sizeof(bf16);
+        constexpr size_t merge = (size_t)(DW * 16 * (D + 2) + 16 * (D + 2)) * sizeof(float);
         constexpr size_t smem = ring > merge ? ring : merge;
         static bool set = false;
         if (!set) {
-            cudaError_t e = cudaFuncSetAttribute(attn_mma_decode_kernel<D, BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            cudaError_t e = cudaFuncSetAttribute(attn_mma_decode_kernel<D, BN, STAGES, DW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             if (e != cudaSuccess) return (int)e;
             set = true;
         }
-        return launch_kernel(attn_mma_decode_kernel<D, BN, STAGES>, grid, dim3(WARPS * 32), smem, s, p);
+        if (p.cluster && p.num_splits > 1) {
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = grid;
+            cfg.blockDim = dim3(DW * 32);
+            cfg.dynamicSmemBytes = smem;
+            cfg.stream = s;
+            cudaLaunchAttribute attr[2];
+            attr[0].id = cudaLaunchAttributeClusterDimension;
+            attr[0].val.clusterDim.x = 1;
+            attr[0].val.clusterDim.y = 1;
+            attr[0].val.clusterDim.z = p.num_splits;
+            attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attr[1].val.programmaticStreamSerializationAllowed = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = llmie_pdl_flag ? 2 : 1;
+            return (int)cudaLaunchKernelEx(&cfg, attn_mma_decode_kernel<D, BN, STAGES, DW>, p);
+        }
+        return launch_kernel(attn_mma_decode_kernel<D, BN, STAGES, DW>, grid, dim3(DW * 32), smem, s, p);
     } else {
         constexpr size_t tiles = (size_t)(64 * D + 2 * 2 * 64 * D) * sizeof(bf16);
         constexpr size_t merge = (size_t)(64 * (D + 2)) * sizeof(float);
@@ -511,14 +578,16 @@ LLMIE_API int llmie_attn_plan(const int* seq_starts, int num_seqs, int tokens_pe
 }
 
 // decode_mode 1: every tile has at most 16 rows (tokens * group). 0: at most 64 rows.
-// scratch_o / scratch_ml / counters are needed for num_splits > 1 (counters zeroed once; the kernel leaves them zero).
+// scratch_o / scratch_ml / counters are needed for num_splits > 1 (counters zeroed once; the kernel leaves them zero), unless
+// `cluster` is set (decode mode, at most 8 slices): the slices then form one thread-block cluster and merge in shared memory.
 LLMIE_API int llmie_paged_attention_mma(const bf16* q, int q_stride, const bf16* k_pool, const bf16* v_pool, const int* block_table,
                                         int max_blocks, const int* token_seq, const int* positions, const int* tile_info, int num_tiles,
                                         bf16* out, float* scratch_o, float* scratch_ml, int* counters, int nq, int nkv, int d,
-                                        int page_size, float scale, int window, int num_splits, int decode_mode, cudaStream_t s) {
+                                        int page_size, float scale, int window, int num_splits, int decode_mode, int cluster, cudaStream_t s) {
     if (num_tiles <= 0) return 0;
+    if (cluster && (!decode_mode || num_splits > 8)) return LLMIE_ERR_BAD_ARGUMENT;
     if ((d != 64 && d != 128) || nkv <= 0 || nq % nkv || page_size <= 0 || num_splits < 1 || q_stride % 8 || nkv > 65535 ||
-        num_splits > 64 || (num_splits > 1 && (!scratch_o || !scratch_ml || !counters)))
+        num_splits > 64 || (num_splits > 1 && !cluster && (!scratch_o || !scratch_ml || !counters)))
         return LLMIE_ERR_BAD_ARGUMENT;
     const int G = nq / nkv;
     if (G > (decode_mode ? 16 : 64)) return LLMIE_ERR_BAD_ARGUMENT;
@@ -526,6 +595,6 @@ LLMIE_API int llmie_paged_attention_mma(const bf16* q, int q_stride, const bf16*
     p.q = q; p.k_pool = k_pool; p.v_pool = v_pool; p.block_table = block_table; p.token_seq = token_seq; p.positions = positions;
     p.tile_info = tile_info; p.out = out; p.part_o = scratch_o; p.part_ml = scratch_ml; p.counters = counters;
     p.q_stride = q_stride; p.max_blocks = max_blocks; p.nq = nq; p.nkv = nkv; p.page_size = page_size; p.window = window;
-    p.num_splits = num_splits; p.scale_log2 = scale * LOG2E;
+    p.num_splits = num_splits; p.scale_log2 = scale * LOG2E; p.cluster = cluster;
     return d == 64 ? launch<64>(p, num_tiles, decode_mode, s) : launch<128>(p, num_tiles, decode_mode, s);
 }

@@ -66,6 +66,7 @@ class CudaKernels:
         self._attn_scratch: Optional[torch.Tensor] = None
         self._attn_counters: Optional[torch.Tensor] = None
         self.use_mma_attention = True
+        self.cluster_merge = True      # decode attention: the key slices of a token form a cluster and merge in shared memory
         self.use_tc_gemm = True
         self.tc_max_rows = 128        # batches up to this many rows take the small-batch tensor-core product
         self._acc: Optional[torch.Tensor] = None  # float32 zeros: split-K products add into it, their consumer clears it again
@@ -386,7 +387,7 @@ class CudaKernels:
         decode = batch.max_seq_len == 1
         N = qkv.shape[0]
         if decode:
-            tiles, tile_info, rows, chunk = N, None, 16, (64 if head_dim == 64 else 32)
+            tiles, tile_info, rows, chunk = N, None, 16, (32 if head_dim == 64 else 16)
         else:
             per_tile = max(1, 64 // group)
             tiles = sum(-(-n // per_tile) for n in batch.seq_lens)
@@ -398,11 +399,16 @@ class CudaKernels:
                 batch._tables[key] = info
             tile_info, rows, chunk = batch._tables[key], 64, 64
         chunks = max(1, -(-span // chunk))
+        explicit = num_splits
         if num_splits is None:
             blocks = max(1, tiles * num_kv_heads)
-            num_splits = max(1, min(self.num_sms // blocks, chunks // (4 if decode else 8), 64))
+            num_splits = max(1, min(self.num_sms // blocks, chunks // (16 if decode else 8), 64))
         scratch_o = scratch_ml = counters = None
-        if num_splits > 1:
+        # Up to four slices of a token merge as one thread-block cluster through shared memory (no trip through global
+        # memory); more slices than that go through scratch and a counter: clusters of eight blocks of this size do not
+        # all fit on the device at once and were measured slower.
+        cluster = int(decode and self.cluster_merge and 1 < num_splits <= (4 if explicit is None else 8))
+        if num_splits > 1 and not cluster:
             cells = tiles * num_kv_heads * num_splits * rows
             buf = self._scratch(cells * (head_dim + 2), qkv.device)
             scratch_o, scratch_ml = buf, buf[cells * head_dim:]
@@ -414,7 +420,7 @@ class CudaKernels:
         self._check(self.lib.llmie_paged_attention_mma(
             _ptr(qkv), qkv.shape[1], _ptr(k_pool), _ptr(v_pool), _ptr(block_table), block_table.shape[1], _ptr(token_seq),
             _ptr(positions), _ptr(tile_info), tiles, _ptr(out), _ptr(scratch_o), _ptr(scratch_ml), _ptr(counters), num_heads,
-            num_kv_heads, head_dim, page_size, ctypes.c_float(scale), int(window), num_splits, int(decode), self._stream()),
+            num_kv_heads, head_dim, page_size, ctypes.c_float(scale), int(window), num_splits, int(decode), cluster, self._stream()),
             "paged_attention (tensor cores)")
         return out
 
