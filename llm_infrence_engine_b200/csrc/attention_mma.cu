@@ -80,6 +80,13 @@ __device__ __forceinline__ float ld_cluster(const float* local, int rank) {  // 
     return v;
 }
 
+// 2^x by the hardware's approximation unit (about two units in the last place; -inf gives 0): the softmax stays 32-bit.
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
+
 // Element (row, col) of a [rows][D] bfloat16 tile in shared memory; 16-byte chunks of a row are
 // permuted by the row's low bits so that the 8 rows one ldmatrix phase reads fall on different banks.
 template <int D> __device__ __forceinline__ int swz(int row, int col) { return row * D + ((((col >> 3) ^ (row & 7)) << 3) | (col & 7)); }
@@ -112,7 +119,7 @@ __device__ __forceinline__ void load_rows_warp(const Params& p, const int* table
 }
 
 // One chunk of BN keys for one warp's 16 rows: S = Q K^T, masked online softmax, O += P V.
-template <int D, int BN>
+template <int D, int BN, bool MASKED = true>
 __device__ __forceinline__ void attend_chunk(const uint32_t (&qa)[D / 16][4], const bf16* ks, const bf16* vs, float (&o)[D / 8][4],
                                              float (&m)[2], float (&l)[2], int key0, const int (&row_pos)[2], const bool (&row_ok)[2],
                                              int window, float scale_log2, int lane) {
@@ -139,7 +146,7 @@ __device__ __forceinline__ void attend_chunk(const uint32_t (&qa)[D / 16][4], co
         for (int e = 0; e < 4; ++e) {
             const int r = e >> 1;
             const int key = key0 + nt * 8 + ((lane & 3) << 1) + (e & 1);
-            const bool ok = row_ok[r] && key <= row_pos[r] && (window <= 0 || key > row_pos[r] - window);
+            const bool ok = !MASKED || (row_ok[r] && key <= row_pos[r] && (window <= 0 || key > row_pos[r] - window));
             const float x = ok ? s[nt][e] * scale_log2 : -INFINITY;
             s[nt][e] = x;
             mx[r] = fmaxf(mx[r], x);
@@ -152,7 +159,7 @@ __device__ __forceinline__ void attend_chunk(const uint32_t (&qa)[D / 16][4], co
         mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
         const float m_new = fmaxf(m[r], mx[r]);
         use[r] = m_new == -INFINITY ? 0.f : m_new;
-        corr[r] = exp2f(m[r] - use[r]);
+        corr[r] = fast_exp2(m[r] - use[r]);
         m[r] = m_new;
         l[r] *= corr[r];
     }
@@ -164,8 +171,8 @@ __device__ __forceinline__ void attend_chunk(const uint32_t (&qa)[D / 16][4], co
     uint32_t pa[BN / 16][4];
 #pragma unroll
     for (int nt = 0; nt < BN / 8; ++nt) {
-        const float p0 = exp2f(s[nt][0] - use[0]), p1 = exp2f(s[nt][1] - use[0]);
-        const float p2 = exp2f(s[nt][2] - use[1]), p3 = exp2f(s[nt][3] - use[1]);
+        const float p0 = fast_exp2(s[nt][0] - use[0]), p1 = fast_exp2(s[nt][1] - use[0]);
+        const float p2 = fast_exp2(s[nt][2] - use[1]), p3 = fast_exp2(s[nt][3] - use[1]);
         l[0] += p0 + p1;
         l[1] += p2 + p3;
         pa[nt >> 1][(nt & 1) * 2] = pack_bf16(p0, p1);
@@ -318,7 +325,13 @@ __global__ void __launch_bounds__(DW * 32) attn_mma_decode_kernel(const Params p
         cp_async_wait<STAGES - 1>();
         __syncwarp();
         const bf16* cur = my + (it % STAGES) * 2 * TILE;
-        attend_chunk<D, BN>(qa, cur, cur + TILE, o, m, l, lo + (first + it * DW) * BN, row_pos, row_ok, p.window, p.scale_log2, lane);
+        const int key0 = lo + (first + it * DW) * BN;
+        // a chunk that lies wholly before the first token's position (and inside every window) needs no mask arithmetic;
+        // rows beyond the tile then collect numbers nobody reads
+        if (key0 + BN - 1 <= pos0 && (p.window <= 0 || key0 > hi - 1 - p.window))
+            attend_chunk<D, BN, false>(qa, cur, cur + TILE, o, m, l, key0, row_pos, row_ok, p.window, p.scale_log2, lane);
+        else
+            attend_chunk<D, BN, true>(qa, cur, cur + TILE, o, m, l, key0, row_pos, row_ok, p.window, p.scale_log2, lane);
         __syncwarp();
     }
     cp_async_wait<0>();
@@ -410,7 +423,7 @@ __global__ void __launch_bounds__(WARPS * 32) attn_mma_prefill_kernel(const Para
     constexpr int BM = 64, BN = 64, TILE = BN * D;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     bf16* qs = reinterpret_cast<bf16*>(smem_raw);   // [BM][D]
-    bf16* kv = qs + BM * D;                         // [2 stages][K, V][BN][D]
+    bf16* kv = qs + BM * D;                         // [3 stages][K, V][BN][D]
     __shared__ int flag;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int tile = gridDim.x - 1 - blockIdx.x;  // later tiles of a prompt see more keys: start them first
@@ -437,7 +450,10 @@ __global__ void __launch_bounds__(WARPS * 32) attn_mma_prefill_kernel(const Para
         if (row < nrows) cp_async16(dst, p.q + (size_t)(n0 + row / G) * p.q_stride + (size_t)(kvh * G + row % G) * D + ch * 8);
         else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
     }
+    // a ring of three key chunks: chunk c + 2 is on its way while chunk c is computed, with one block-wide barrier per chunk
     if (c_begin < c_end) load_rows_warp<D, BN / WARPS>(p, table, kvh, lo + c_begin * BN + warp * (BN / WARPS), hi - 1, warp * (BN / WARPS), kv, kv + TILE, lane);
+    cp_async_commit();
+    if (c_begin + 1 < c_end) load_rows_warp<D, BN / WARPS>(p, table, kvh, lo + (c_begin + 1) * BN + warp * (BN / WARPS), hi - 1, warp * (BN / WARPS), kv + 2 * TILE, kv + 3 * TILE, lane);
     cp_async_commit();
 
     int row_pos[2];
@@ -458,15 +474,16 @@ __global__ void __launch_bounds__(WARPS * 32) attn_mma_prefill_kernel(const Para
     for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
 
+    const int warp_min_pos = warp_first_pos;  // every row of the warp sees keys up to at least here
     for (int c = c_begin; c < c_end; ++c) {
-        const int stage = (c - c_begin) & 1;
-        if (c + 1 < c_end) {
-            bf16* dst = kv + (stage ^ 1) * 2 * TILE;
-            load_rows_warp<D, BN / WARPS>(p, table, kvh, lo + (c + 1) * BN + warp * (BN / WARPS), hi - 1, warp * (BN / WARPS), dst, dst + TILE, lane);
+        const int stage = (c - c_begin) % 3;
+        cp_async_wait<1>();   // chunk c has landed (chunk c + 1 may still be in flight)
+        __syncthreads();      // ... for every warp; and every warp is done with chunk c - 1, whose buffer is filled next
+        if (c + 2 < c_end) {
+            bf16* dst = kv + ((c + 2 - c_begin) % 3) * 2 * TILE;
+            load_rows_warp<D, BN / WARPS>(p, table, kvh, lo + (c + 2) * BN + warp * (BN / WARPS), hi - 1, warp * (BN / WARPS), dst, dst + TILE, lane);
         }
         cp_async_commit();
-        cp_async_wait<1>();
-        __syncthreads();
         if (c == c_begin) {
 #pragma unroll
             for (int kk = 0; kk < D / 16; ++kk) {
@@ -479,9 +496,11 @@ __global__ void __launch_bounds__(WARPS * 32) attn_mma_prefill_kernel(const Para
         const bool visible = warp_has_rows && key0 <= warp_last_pos && (p.window <= 0 || key0 + BN - 1 > warp_first_pos - p.window);
         if (visible) {
             const bf16* cur = kv + stage * 2 * TILE;
-            attend_chunk<D, BN>(qa, cur, cur + TILE, o, m, l, key0, row_pos, row_ok, p.window, p.scale_log2, lane);
+            // a chunk that every row of the warp sees in full needs no mask arithmetic
+            const bool interior = key0 + BN - 1 <= warp_min_pos && warp * 16 + 15 < nrows && (p.window <= 0 || key0 > warp_last_pos - p.window);
+            if (interior) attend_chunk<D, BN, false>(qa, cur, cur + TILE, o, m, l, key0, row_pos, row_ok, p.window, p.scale_log2, lane);
+            else attend_chunk<D, BN, true>(qa, cur, cur + TILE, o, m, l, key0, row_pos, row_ok, p.window, p.scale_log2, lane);
         }
-        __syncthreads();
     }
     cp_async_wait<0>();
 #pragma unroll
@@ -556,7 +575,7 @@ int launch(const Params& p, int num_tiles, int decode_mode, cudaStream_t s) {
         }
         return launch_kernel(attn_mma_decode_kernel<D, BN, STAGES, DW>, grid, dim3(DW * 32), smem, s, p);
     } else {
-        constexpr size_t tiles = (size_t)(64 * D + 2 * 2 * 64 * D) * sizeof(bf16);
+        constexpr size_t tiles = (size_t)(64 * D + 3 * 2 * 64 * D) * sizeof(bf16);
         constexpr size_t merge = (size_t)(64 * (D + 2)) * sizeof(float);
         constexpr size_t smem = tiles > merge ? tiles : merge;
         static bool set = false;

@@ -192,20 +192,31 @@ template <typename TI, typename TO, int VEC>
 __global__ void silu_mul_kernel(TI* __restrict__ gu, TO* __restrict__ out, int I, int clear_in) {
     pdl_trigger();
     pdl_wait();
-    const int i = (blockIdx.x * blockDim.x + threadIdx.x) * VEC;
-    if (i >= I) return;
-    TI* g_ptr = gu + (size_t)blockIdx.y * 2 * I + i;
-    TI* u_ptr = g_ptr + I;
-    float g[VEC], u[VEC], y[VEC];
-    if constexpr (VEC == 4) { load4(g_ptr, g); load4(u_ptr, u); } else { g[0] = to_f32(*g_ptr); u[0] = to_f32(*u_ptr); }
-    if (clear_in) {
-        const float zero[4] = {0.f, 0.f, 0.f, 0.f};
-        if constexpr (VEC == 4) { store4(g_ptr, zero); store4(u_ptr, zero); } else { *g_ptr = from_f32<TI>(0.f); *u_ptr = from_f32<TI>(0.f); }
+    constexpr int PER = VEC == 4 ? 2 : 1;  // vectors per thread: two loads of gate and two of up are in flight together
+    const int i0 = (blockIdx.x * blockDim.x + threadIdx.x) * VEC * PER;
+    TI* row = gu + (size_t)blockIdx.y * 2 * I;
+    float g[PER][VEC], u[PER][VEC];
+#pragma unroll
+    for (int v = 0; v < PER; ++v) {
+        const int i = i0 + v * VEC;
+        if (i < I) {
+            if constexpr (VEC == 4) { load4(row + i, g[v]); load4(row + I + i, u[v]); } else { g[v][0] = to_f32(row[i]); u[v][0] = to_f32(row[I + i]); }
+        }
     }
 #pragma unroll
-    for (int j = 0; j < VEC; ++j) y[j] = g[j] / (1.0f + expf(-g[j])) * u[j];
-    TO* o = out + (size_t)blockIdx.y * I + i;
-    if constexpr (VEC == 4) store4(o, y); else *o = from_f32<TO>(y[0]);
+    for (int v = 0; v < PER; ++v) {
+        const int i = i0 + v * VEC;
+        if (i >= I) continue;
+        if (clear_in) {
+            const float zero[4] = {0.f, 0.f, 0.f, 0.f};
+            if constexpr (VEC == 4) { store4(row + i, zero); store4(row + I + i, zero); } else { row[i] = from_f32<TI>(0.f); row[I + i] = from_f32<TI>(0.f); }
+        }
+        float y[VEC];
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) y[j] = g[v][j] / (1.0f + expf(-g[v][j])) * u[v][j];
+        TO* o = out + (size_t)blockIdx.y * I + i;
+        if constexpr (VEC == 4) store4(o, y); else *o = from_f32<TO>(y[0]);
+    }
 }
 
 template <typename TI, typename TO>
@@ -218,7 +229,7 @@ static int launch_silu_mul(TI* gu, TO* out, int N, int I, int clear_in, cudaStre
         return 0;
     }
     const bool vec = I % 4 == 0 && ((uintptr_t)gu % 16 == 0) && ((uintptr_t)out % 16 == 0);
-    if (vec) return launch_kernel(silu_mul_kernel<TI, TO, 4>, dim3((I / 4 + 127) / 128, N), dim3(128), 0, s, gu, out, I, clear_in);
+    if (vec) return launch_kernel(silu_mul_kernel<TI, TO, 4>, dim3((I / 8 + 127) / 128, N), dim3(128), 0, s, gu, out, I, clear_in);
     return launch_kernel(silu_mul_kernel<TI, TO, 1>, dim3((I + 127) / 128, N), dim3(128), 0, s, gu, out, I, clear_in);
 }
 
