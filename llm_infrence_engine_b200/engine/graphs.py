@@ -14,6 +14,7 @@ the kernel cuts each token's own keys into that many slices on the device, whate
 """
 from __future__ import annotations
 
+import gc
 from typing import Dict, List, Sequence
 
 import torch
@@ -80,8 +81,18 @@ class DecodeGraphs:
             self.pool = torch.cuda.graph_pool_handle()
         ctx._tables.clear()
         before = r.K.launches
-        with torch.cuda.graph(graph, pool=self.pool):
-            logits = r.forward(ctx, rows)
+        # Nothing but the step's own kernels may touch CUDA while the stream is capturing. Python's cyclic collector could:
+        # an old runner's graphs, found to be garbage in the middle of the capture, are destroyed with a CUDA call that the
+        # capture forbids and that invalidates it. So: collect first, then keep the collector off until the capture ends.
+        gc.collect()
+        was_enabled = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.cuda.graph(graph, pool=self.pool, capture_error_mode="relaxed"):
+                logits = r.forward(ctx, rows)
+        finally:
+            if was_enabled:
+                gc.enable()
         return _Captured(graph, static_in, logits, r.K.launches - before)
 
     @torch.inference_mode()
