@@ -12,6 +12,19 @@ LLMIE_API int llmie_set_pdl(int on) {
 }
 
 // ------------------------------------------------------------------------------------------------
+// A kernel that does nothing but take its place in the stream's dependency chain: what a kernel boundary costs
+// on this device (with and without programmatic dependent launch) is measured with chains of these.
+__global__ void noop_kernel(int* sink) {
+    pdl_trigger();
+    pdl_wait();
+    if (sink && threadIdx.x == 0 && blockIdx.x == 0xffffffffu) *sink = 0;
+}
+
+LLMIE_API int llmie_noop(int blocks, int threads, int* sink, cudaStream_t s) {
+    return launch_kernel(noop_kernel, dim3(blocks), dim3(threads), 0, s, sink);
+}
+
+// ------------------------------------------------------------------------------------------------
 // x[n, :] = table[ids[n], :]  widened to float (the residual stream)
 template <typename T>
 __global__ void embed_kernel(const int* __restrict__ ids, const T* __restrict__ table, float* __restrict__ out, int H) {
@@ -60,9 +73,14 @@ LLMIE_API int llmie_rope_tables(const int* pos, const float* inv_freq, float* co
 template <typename T, int VEC>
 __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __restrict__ delta, const float* __restrict__ weight,
                                    T* __restrict__ out, const int* __restrict__ rows, int H, float eps) {
-    extern __shared__ __align__(16) float row_buf[];  // H floats, then 33 for the reduction
+    extern __shared__ __align__(16) float row_buf[];  // H floats, 33 for the reduction, H floats of weights
     float* scratch = row_buf + H;
+    float* w_buf = scratch + 36;  // the norm's weights, H floats: fetched before the wait, they do not depend on the kernel before
     pdl_trigger();
+    for (int i = threadIdx.x * VEC; i < H; i += blockDim.x * VEC) {
+        if constexpr (VEC == 4) *reinterpret_cast<float4*>(w_buf + i) = *reinterpret_cast<const float4*>(weight + i);
+        else w_buf[i] = weight[i];
+    }
     pdl_wait();
     const int r = rows ? rows[blockIdx.x] : blockIdx.x;
     float* x = residual + (size_t)r * H;
@@ -85,10 +103,9 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __rest
     const float rstd = 1.0f / sqrtf(ss / (float)H + eps);
     T* o = out + (size_t)blockIdx.x * H;
     for (int i = threadIdx.x * VEC; i < H; i += blockDim.x * VEC) {
-        float w[VEC], y[VEC];
-        if constexpr (VEC == 4) load4(weight + i, w); else w[0] = weight[i];
+        float y[VEC];
 #pragma unroll
-        for (int j = 0; j < VEC; ++j) y[j] = w[j] * round_through<T>(row_buf[i + j] * rstd);
+        for (int j = 0; j < VEC; ++j) y[j] = w_buf[i + j] * round_through<T>(row_buf[i + j] * rstd);
         if constexpr (VEC == 4) store4(o + i, y); else o[i] = from_f32<T>(y[0]);
     }
 }
@@ -96,7 +113,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __rest
 template <typename T>
 static int launch_add_rmsnorm(float* residual, const T* delta, const float* weight, T* out, const int* rows, int n_out, int H, float eps,
                               cudaStream_t s) {
-    const size_t smem = (size_t)(H + 33) * sizeof(float);
+    const size_t smem = (size_t)(2 * H + 36) * sizeof(float);
     const bool vec = H % 4 == 0 && ((uintptr_t)residual % 16 == 0) && ((uintptr_t)out % 8 == 0) && ((uintptr_t)delta % 8 == 0) &&
                      ((uintptr_t)weight % 16 == 0);
     const int per = vec ? 4 : 1;
@@ -114,7 +131,7 @@ static int launch_add_rmsnorm(float* residual, const T* delta, const float* weig
 LLMIE_API int llmie_add_rmsnorm(float* residual, const void* delta, const float* weight, void* out, const int* rows,
                                 int n_out, int H, float eps, int dtype, cudaStream_t s) {
     if (n_out <= 0) return 0;
-    if ((size_t)(H + 33) * sizeof(float) > 200 * 1024) return LLMIE_ERR_BAD_ARGUMENT;
+    if ((size_t)(2 * H + 36) * sizeof(float) > 200 * 1024) return LLMIE_ERR_BAD_ARGUMENT;
     if (dtype == DT_F32) return launch_add_rmsnorm<float>(residual, (const float*)delta, weight, (float*)out, rows, n_out, H, eps, s);
     return launch_add_rmsnorm<bf16>(residual, (const bf16*)delta, weight, (bf16*)out, rows, n_out, H, eps, s);
 }

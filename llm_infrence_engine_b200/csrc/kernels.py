@@ -144,8 +144,8 @@ class CudaKernels:
             self._need(delta, "delta", out_dtype, 2)
             if delta.shape != residual.shape:
                 raise KernelError(f"{what}: delta is {list(delta.shape)}, residual is {list(residual.shape)}")
-        if H > 50000:
-            raise KernelError(f"{what}: rows of {H} elements do not fit the kernel's shared memory (at most 50000)")
+        if H > 25000:
+            raise KernelError(f"{what}: rows of {H} elements do not fit the kernel's shared memory (at most 25000)")
         n_out = residual.shape[0] if rows is None else rows.shape[0]
         if rows is not None:
             self._need(rows, "rows", torch.int32, 1)

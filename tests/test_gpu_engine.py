@@ -304,3 +304,85 @@ def test_layer_sizes_of_the_half_billion_model(tmp_path, dtype):
     check(torch.stack(got_a), want_a[40:70], dtype, "graphs, request a")
     check(torch.stack(got_b), want_b[40:70], dtype, "graphs, request b")
     runner.K.check_device_errors()
+
+
+def _sharp_folder(tmp_path, name, factor=8.0):
+    """Tiny model whose query and key projections are scaled up: the softmax becomes nearly one-hot, so a key that is
+    skipped, misplaced, read from a wrong page or let in across a window's edge changes the logits by far more than rounding.
+    The factor is 8 (scores x 64): at 25 the plain implementation itself moves by 7e-5 when its weights are disturbed by
+    one part in 10^7, which is beyond the comparison's 2e-5; at 8 it moves by 1e-6."""
+    from llm_infrence_engine_b200.weights import SafetensorsFile, write_random_model, write_safetensors
+
+    folder = write_random_model(CONFIGS[name], tmp_path / f"sharp_{name}", 11, "float32")
+    f = SafetensorsFile(folder / "model.safetensors")
+    t = {n: f.tensor(n) for n in f.names()}
+    f.close()
+    for n in t:
+        if n.endswith("q_proj.weight") or n.endswith("k_proj.weight"):
+            t[n] = t[n] * factor
+    write_safetensors(folder / "model.safetensors", t)
+    return folder
+
+
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_sharp_attention_shows_a_wrong_key(tmp_path, name):
+    folder = _sharp_folder(tmp_path, name)
+    cfg, w = plain_load(folder)
+    p = random_prompt(cfg["vocab_size"], 150, 21)
+    want = plain_forward(cfg, w, p)
+    # the attention really is sharp: without the scaling the logits are far from these
+    base = dict(w)
+    assert (want - plain_forward(cfg, {k: (v / 8.0 if k.endswith(("q_proj.weight", "k_proj.weight")) else v) for k, v in base.items()}, p)).abs().max() > 1e-2
+    rp = replayer(folder, name, "float32", 192)
+    got = rp.step({"step": 0, "entries": [{"id": "w", "tokens": p, "want": list(range(150))}], "end": ["w"]})
+    assert first_bad(got, want, "float32") is None, f"whole: first wrong position {first_bad(got, want, 'float32')}"
+    outs = []
+    for i, (lo, hi) in enumerate(cut(150, [7, 16, 1, 33, 2, 15, 1, 1, 17])):
+        outs.append(rp.step({"step": i, "entries": [{"id": "c", "tokens": p[lo:hi], "want": list(range(hi - lo))}], "end": ["c"] if hi == 150 else []}))
+    got = torch.cat(outs)
+    assert first_bad(got, want, "float32") is None, f"portions: first wrong position {first_bad(got, want, 'float32')}"
+
+
+@pytest.mark.parametrize("seed", [0, 1, 2])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_random_traces(models, dtype, seed):
+    """Random cuts, random joins and leaves, random sitting out, on a pool that is only just large enough."""
+    import random
+
+    name = "ABC"[seed]
+    folder, cfg, w, prompts, want = models[(name, dtype)]
+    rng = random.Random(seed)
+    keys = list(prompts)
+    rng.shuffle(keys)
+    rp = replayer(folder, name, dtype, 4 * 192)
+    waiting, live, pos, got = list(keys), [], {}, {k: [] for k in keys}
+    step = 0
+    while waiting or live:
+        while waiting and len(live) < 4 and rng.random() < 0.7:
+            k = waiting.pop(0)
+            live.append(k)
+            pos[k] = 0
+        entries, end = [], []
+        for k in list(live):
+            if rng.random() < 0.2 and len(live) > 1:
+                continue
+            left = len(prompts[k]) - pos[k]
+            n = min(left, rng.choice([1, 1, 1, 2, 3, 8, 16, 17, 40, 64]))
+            entries.append({"id": k, "tokens": prompts[k][pos[k]:pos[k] + n], "want": list(range(n))})
+            pos[k] += n
+            if pos[k] == len(prompts[k]):
+                end.append(k)
+                live.remove(k)
+        if not entries:
+            continue
+        out = rp.step({"step": step, "entries": entries, "end": end})
+        o = 0
+        for e in entries:
+            got[e["id"]].append(out[o:o + len(e["tokens"])])
+            o += len(e["tokens"])
+        rp.cache.check_invariants()
+        step += 1
+    for k in keys:
+        bad = first_bad(torch.cat(got[k]), want[k], dtype)
+        assert bad is None, f"seed {seed}, request {k}: first wrong position {bad}"
+    assert all(p.num_free == p.capacity for p in rp.cache.pools)
