@@ -273,7 +273,13 @@ __global__ void __launch_bounds__(DW * 32) attn_mma_decode_kernel(const Params p
 
     const int tile = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
     pdl_trigger();
-    pdl_wait();
+    // What this block needs of the step's own integers (positions, table rows, block tables) was copied to the device
+    // before the step's first kernel, and keys and values of earlier positions were written by earlier steps: none of it
+    // depends on the kernels just before this one. So when tile i is simply token i, the block finds its key range and
+    // starts fetching its first chunks BEFORE the wait; only chunks that reach the new positions, and the queries, which
+    // the rotation kernel has just written, come after it.
+    const bool early = p.tile_info == nullptr;
+    if (!early) pdl_wait();
     const int n0 = p.tile_info ? p.tile_info[2 * tile] : tile;
     const int ntok = p.tile_info ? p.tile_info[2 * tile + 1] : 1;
     const int G = p.nq / p.nkv;
@@ -285,6 +291,18 @@ __global__ void __launch_bounds__(DW * 32) attn_mma_decode_kernel(const Params p
     const int chunks = (hi - lo + BN - 1) / BN;
     const int per = (chunks + p.num_splits - 1) / p.num_splits;
     const int c_begin = split * per, c_end = min(chunks, c_begin + per);
+
+    // this warp's chunks: c_begin + warp, + DW, ...
+    const int first = c_begin + warp;
+    const int mine = first < c_end ? (c_end - first + DW - 1) / DW : 0;
+    bool fetched[STAGES - 1];
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; ++s) {
+        const int key0 = lo + (first + s * DW) * BN;
+        fetched[s] = early && s < mine && key0 + BN <= pos0;  // wholly before the first new position
+        if (fetched[s]) load_rows_warp<D, BN>(p, table, kvh, key0, hi - 1, 0, my + s * 2 * TILE, my + s * 2 * TILE + TILE, lane);
+    }
+    if (early) pdl_wait();
 
     int row_pos[2];
     bool row_ok[2];
@@ -307,13 +325,10 @@ __global__ void __launch_bounds__(DW * 32) attn_mma_decode_kernel(const Params p
     for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
 
-    // this warp's chunks: c_begin + warp, + DW, ...
-    const int first = c_begin + warp;
-    const int mine = first < c_end ? (c_end - first + DW - 1) / DW : 0;
 #pragma unroll
     for (int s = 0; s < STAGES - 1; ++s) {
-        if (s < mine) load_rows_warp<D, BN>(p, table, kvh, lo + (first + s * DW) * BN, hi - 1, 0, my + s * 2 * TILE, my + s * 2 * TILE + TILE, lane);
-        cp_async_commit();
+        if (s < mine && !fetched[s]) load_rows_warp<D, BN>(p, table, kvh, lo + (first + s * DW) * BN, hi - 1, 0, my + s * 2 * TILE, my + s * 2 * TILE + TILE, lane);
+        cp_async_commit();  // stage 0's group may also hold later stages' early fetches: it then completes a little later, never too early
     }
     for (int it = 0; it < mine; ++it) {
         const int nxt = it + STAGES - 1;
