@@ -160,7 +160,7 @@ class Engine:
     def _emit(self, req: Request, tok: int) -> None:
         """src/miniserve/engine.py:279-291: a stop token ends the request and is not kept."""
         now = self.clock()
-        if tok in req.eos_ids:
+        if tok in req.eos_ids and not req.ignore_eos:
             self._finish(req, "stop", now)
             return
         req.output_ids.append(tok)

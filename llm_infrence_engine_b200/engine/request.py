@@ -15,6 +15,7 @@ class Request:
     top_k: int = 0               # 0: off
     top_p: float = 1.0           # 1: off
     seed: Optional[int] = None   # None: the engine's seed plus the request's id
+    ignore_eos: bool = False     # keep generating through stop tokens (src/miniserve/server.py:56,292)
 
     # --- filled in by the engine ---
     id: int = -1

@@ -251,6 +251,32 @@ HALF_B = dict(CONFIGS["A"], vocab_size=151936, hidden_size=896, intermediate_siz
               num_key_value_heads=2, rms_norm_eps=1e-6, rope_theta=1e6, tie_word_embeddings=True, max_position_embeddings=32768)
 
 
+WIDE = dict(CONFIGS["A"], vocab_size=32003, hidden_size=1536, intermediate_size=8960, num_hidden_layers=1, num_attention_heads=12,
+            num_key_value_heads=2, rms_norm_eps=1e-6, rope_theta=1e6, tie_word_embeddings=False, max_position_embeddings=32768)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_head_size_128(tmp_path, dtype):
+    """One layer with heads of 128 in groups of 6 (the 1.5B model's widths) and a vocabulary that is no multiple of the
+    GEMM's tile: whole, then most of it in one step and the rest token by token."""
+    from llm_infrence_engine_b200.engine import TraceReplayer
+    from llm_infrence_engine_b200.weights import write_random_model
+
+    folder = write_random_model(WIDE, tmp_path / "wide", 6, dtype)
+    cfg, w = plain_load(folder)
+    p = random_prompt(32003, 140, 3)
+    want = plain_forward(cfg, w, p)
+    rp = TraceReplayer(str(folder), dtype, 192)
+    got = rp.step({"step": 0, "entries": [{"id": "a", "tokens": p, "want": list(range(140))}], "end": ["a"]})
+    assert first_bad(got, want, dtype) is None, f"whole: first wrong position {first_bad(got, want, dtype)}"
+    outs = [rp.step({"step": 0, "entries": [{"id": "b", "tokens": p[:100], "want": list(range(100))}], "end": []})]
+    for i in range(100, 140):
+        outs.append(rp.step({"step": i, "entries": [{"id": "b", "tokens": [p[i]], "want": [0]}], "end": ["b"] if i == 139 else []}))
+    got = torch.cat(outs)
+    assert first_bad(got, want, dtype) is None, f"decoded: first wrong position {first_bad(got, want, dtype)}"
+    rp.runner.K.check_device_errors()
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_layer_sizes_of_the_half_billion_model(tmp_path, dtype):
     """Two layers with the real widths (hidden 896, 14 / 2 heads of 64, intermediate 4864, vocabulary 151936): the sizes
@@ -266,6 +292,9 @@ def test_layer_sizes_of_the_half_billion_model(tmp_path, dtype):
     from llm_infrence_engine_b200.engine import TraceReplayer
 
     rp = TraceReplayer(str(folder), dtype, 320)
+    for b in rp.runner.bindings:   # nothing may read a slot that was never written
+        b.k.fill_(float("nan"))
+        b.v.fill_(float("nan"))
     got = rp.step({"step": 0, "entries": [{"id": "a", "tokens": pa, "want": list(range(150))}], "end": ["a"]})
     assert first_bad(got, want_a, dtype) is None, f"whole: first wrong position {first_bad(got, want_a, dtype)}"
     # a in portions (one of two tokens) while b decodes token by token beside it, then a decodes too
@@ -386,3 +415,35 @@ def test_random_traces(models, dtype, seed):
         bad = first_bad(torch.cat(got[k]), want[k], dtype)
         assert bad is None, f"seed {seed}, request {k}: first wrong position {bad}"
     assert all(p.num_free == p.capacity for p in rp.cache.pools)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "C"])
+def test_nothing_reads_what_was_never_written(models, name, dtype):
+    """Every slot of every page starts as NaN: a kernel that reads a slot beyond a request's length, a page it does not
+    own, or multiplies a masked key's value by zero instead of skipping it, turns the logits into NaN."""
+    folder, cfg, w, prompts, want = models[(name, dtype)]
+    rp = replayer(folder, name, dtype, 448 + 128)
+    for b in rp.runner.bindings:
+        b.k.fill_(float("nan"))
+        b.v.fill_(float("nan"))
+    got = run_mixed(rp, prompts)
+    for k in prompts:
+        assert not torch.isnan(got[k]).any(), f"request {k}: NaN at position {int(torch.isnan(got[k]).any(-1).nonzero()[0])}"
+        assert first_bad(got[k], want[k], dtype) is None
+
+
+def test_stop_tokens_and_ignore_eos(models):
+    from llm_infrence_engine_b200.engine import Engine, Request
+
+    folder, cfg, w, prompts, want = models[("A", "float32")]
+    p = prompts["d"][:20]
+    ref = plain_generate(cfg, w, p, 12)
+    stop = ref[5]
+    first = ref.index(stop)
+    eng = Engine(str(folder), dtype="float32", block_size=16, num_blocks=20, max_seqs=2, max_len=64, max_num_batched_tokens=32)
+    a = eng.add_request(Request(p, max_new_tokens=12, eos_ids=(stop,)))
+    b = eng.add_request(Request(p, max_new_tokens=12, eos_ids=(stop,), ignore_eos=True))
+    eng.run_until_idle()
+    assert a.output_ids == ref[:first] and a.finish_reason == "stop"     # the stop token is not kept (src/miniserve/engine.py:279-291)
+    assert b.output_ids == ref and b.finish_reason == "length"
