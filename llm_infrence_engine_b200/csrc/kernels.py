@@ -243,11 +243,12 @@ class CudaKernels:
         return self._acc is not None and t.dtype == torch.float32 and t.untyped_storage().data_ptr() == self._acc.untyped_storage().data_ptr()
 
     def tc_splits(self, M: int, N: int, K: int) -> int:
-        """How many blocks share the K range of a small-batch product: enough blocks to draw on the whole memory
-        system (about two per SM), but no more atomic additions than the weights are worth."""
+        """How many blocks share the K range of a small-batch product: enough blocks to draw on the whole memory system
+        (three per SM for up to 16 rows, whose blocks are small enough to sit three to an SM; two beyond, as measured), but
+        no more atomic additions than the weights are worth."""
         tiles = -(-N // 128) * -(-M // 64)
         nkb = -(-K // 64)
-        want = max(1, (2 * self.num_sms) // tiles)
+        want = max(1, ((3 if M <= 16 else 2) * self.num_sms) // tiles)
         cap = max(1, (4 << 20) // max(1, M * N))
         return max(1, min(want, nkb, cap))
 
