@@ -142,7 +142,7 @@ LLMIE_API int llmie_add_rmsnorm(float* residual, const void* delta, const float*
 // copies the key and value heads into the token's cache slot: pool[page][kv head][offset][d],
 // slot = page * page_size + offset. With `clear_in` the input is set to zero after it was read: it is
 // then a float32 accumulation buffer that the next split-K product adds into.
-template <typename TI, typename TO>
+template <typename TI, typename TO, int VEC>
 __global__ void rope_kv_write_kernel(TI* __restrict__ in, TO* __restrict__ out, const float* __restrict__ bias,
                                      const float* __restrict__ cos_t, const float* __restrict__ sin_t, const int* __restrict__ slots,
                                      TO* __restrict__ k_pool, TO* __restrict__ v_pool, int nq, int nkv, int d, int page_size, int write_kv,
@@ -158,28 +158,54 @@ __global__ void rope_kv_write_kernel(TI* __restrict__ in, TO* __restrict__ out, 
     const float* sn = sin_t + (size_t)n * half;
     const int slot = write_kv ? slots[n] : -1;
     const int page = slot >= 0 ? slot / page_size : 0, off = slot >= 0 ? slot % page_size : 0;
-    for (int i = threadIdx.x; i < heads * half; i += blockDim.x) {
+    // a thread takes VEC neighbouring pairs (j, j + d/2) of one head
+    for (int i = threadIdx.x * VEC; i < heads * half; i += blockDim.x * VEC) {
         const int h = i / half, j = i % half;
         const int a = h * d + j, b = a + half;
-        float x1 = to_f32(src[a]), x2 = to_f32(src[b]);
-        if (clear_in) { src[a] = from_f32<TI>(0.f); src[b] = from_f32<TI>(0.f); }
-        if (bias) { x1 += bias[a]; x2 += bias[b]; }
-        float y1 = x1, y2 = x2;
-        if (h < nq + nkv) {
-            y1 = x1 * c[j] - x2 * sn[j];
-            y2 = x2 * c[j] + x1 * sn[j];
+        float x1[VEC], x2[VEC], y1[VEC], y2[VEC];
+        if constexpr (VEC == 4) { load4(src + a, x1); load4(src + b, x2); } else { x1[0] = to_f32(src[a]); x2[0] = to_f32(src[b]); }
+        if (clear_in) {
+            const float zero[4] = {0.f, 0.f, 0.f, 0.f};
+            if constexpr (VEC == 4) { store4(src + a, zero); store4(src + b, zero); } else { src[a] = from_f32<TI>(0.f); src[b] = from_f32<TI>(0.f); }
         }
-        const TO o1 = from_f32<TO>(y1), o2 = from_f32<TO>(y2);
-        row[a] = o1;
-        row[b] = o2;
+        if (bias) {
+#pragma unroll
+            for (int v = 0; v < VEC; ++v) { x1[v] += bias[a + v]; x2[v] += bias[b + v]; }
+        }
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) {
+            if (h < nq + nkv) {
+                y1[v] = x1[v] * c[j + v] - x2[v] * sn[j + v];
+                y2[v] = x2[v] * c[j + v] + x1[v] * sn[j + v];
+            } else {
+                y1[v] = x1[v];
+                y2[v] = x2[v];
+            }
+        }
+        if constexpr (VEC == 4) { store4(row + a, y1); store4(row + b, y2); } else { row[a] = from_f32<TO>(y1[0]); row[b] = from_f32<TO>(y2[0]); }
         if (slot >= 0 && h >= nq) {
             const int kvh = h < nq + nkv ? h - nq : h - nq - nkv;
             TO* pool = h < nq + nkv ? k_pool : v_pool;
             TO* dst = pool + (((size_t)page * nkv + kvh) * page_size + off) * d;
-            dst[j] = o1;
-            dst[j + half] = o2;
+            if constexpr (VEC == 4) { store4(dst + j, y1); store4(dst + j + half, y2); } else { dst[j] = from_f32<TO>(y1[0]); dst[j + half] = from_f32<TO>(y2[0]); }
         }
     }
+}
+
+template <typename TI, typename TO>
+static int launch_rope(TI* in, TO* out, const float* bias, const float* cos_t, const float* sin_t, const int* slots, TO* k_pool, TO* v_pool,
+                       int N, int nq, int nkv, int d, int page_size, int write_kv, int clear_in, cudaStream_t s) {
+    const int work = (nq + 2 * nkv) * (d / 2);
+    const bool vec = d % 8 == 0 && ((uintptr_t)in % 16 == 0) && ((uintptr_t)out % 16 == 0) && ((uintptr_t)k_pool % 16 == 0) &&
+                     ((uintptr_t)v_pool % 16 == 0);
+    if (vec) {
+        const int threads = work / 4 >= 256 ? 256 : 128;
+        return launch_kernel(rope_kv_write_kernel<TI, TO, 4>, dim3(N), dim3(threads), 0, s, in, out, bias, cos_t, sin_t, slots, k_pool, v_pool,
+                             nq, nkv, d, page_size, write_kv, clear_in);
+    }
+    const int threads = work >= 512 ? 256 : 128;
+    return launch_kernel(rope_kv_write_kernel<TI, TO, 1>, dim3(N), dim3(threads), 0, s, in, out, bias, cos_t, sin_t, slots, k_pool, v_pool, nq,
+                         nkv, d, page_size, write_kv, clear_in);
 }
 
 // in_dtype / out_dtype: 0 float32, 1 bfloat16; allowed pairs: equal types (out may alias in), or float32 in and bfloat16 out.
@@ -188,17 +214,15 @@ LLMIE_API int llmie_rope_kv_write(void* in, void* out, const float* bias, const 
                                   int clear_in, int in_dtype, int out_dtype, cudaStream_t s) {
     if (N <= 0) return 0;
     if (d <= 0 || (d & 1) || page_size <= 0 || (clear_in && in == out)) return LLMIE_ERR_BAD_ARGUMENT;
-    const int work = (nq + 2 * nkv) * (d / 2);
-    const int threads = work >= 512 ? 256 : 128;
     if (in_dtype == DT_F32 && out_dtype == DT_F32)
-        return launch_kernel(rope_kv_write_kernel<float, float>, dim3(N), dim3(threads), 0, s, (float*)in, (float*)out, bias, cos_t, sin_t,
-                             slots, (float*)k_pool, (float*)v_pool, nq, nkv, d, page_size, write_kv, clear_in);
-    else if (in_dtype == DT_BF16 && out_dtype == DT_BF16)
-        return launch_kernel(rope_kv_write_kernel<bf16, bf16>, dim3(N), dim3(threads), 0, s, (bf16*)in, (bf16*)out, bias, cos_t, sin_t,
-                             slots, (bf16*)k_pool, (bf16*)v_pool, nq, nkv, d, page_size, write_kv, clear_in);
-    else if (in_dtype == DT_F32 && out_dtype == DT_BF16)
-        return launch_kernel(rope_kv_write_kernel<float, bf16>, dim3(N), dim3(threads), 0, s, (float*)in, (bf16*)out, bias, cos_t, sin_t,
-                             slots, (bf16*)k_pool, (bf16*)v_pool, nq, nkv, d, page_size, write_kv, clear_in);
+        return launch_rope<float, float>((float*)in, (float*)out, bias, cos_t, sin_t, slots, (float*)k_pool, (float*)v_pool, N, nq, nkv, d, page_size,
+                                         write_kv, clear_in, s);
+    if (in_dtype == DT_BF16 && out_dtype == DT_BF16)
+        return launch_rope<bf16, bf16>((bf16*)in, (bf16*)out, bias, cos_t, sin_t, slots, (bf16*)k_pool, (bf16*)v_pool, N, nq, nkv, d, page_size,
+                                       write_kv, clear_in, s);
+    if (in_dtype == DT_F32 && out_dtype == DT_BF16)
+        return launch_rope<float, bf16>((float*)in, (bf16*)out, bias, cos_t, sin_t, slots, (bf16*)k_pool, (bf16*)v_pool, N, nq, nkv, d, page_size,
+                                        write_kv, clear_in, s);
     return LLMIE_ERR_BAD_ARGUMENT;
 }
 

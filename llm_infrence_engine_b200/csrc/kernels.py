@@ -71,6 +71,9 @@ class CudaKernels:
         self.tc_max_rows = 128        # batches up to this many rows take the small-batch tensor-core product
         self._acc: Optional[torch.Tensor] = None  # float32 zeros: split-K products add into it, their consumer clears it again
         self._slice_counters: Optional[torch.Tensor] = None
+        # A library product that is to be added into the residual stream is kept here until the next kernel that reads
+        # the stream: that kernel is usually the norm, which adds and normalises in one pass (see ``flush``).
+        self._pending_add: Optional[tuple] = None
         # Fold the norm before a product, and silu(gate) * up, into the tensor-core product. Off: measured on a B200 the
         # separate kernels (whose launch overlaps the product's weight fetch) are faster at every batch size, because a
         # block that makes its own token tiles adds a trip to memory between the wait and the first MMA.
@@ -154,10 +157,37 @@ class CudaKernels:
                                                ctypes.c_float(eps), _DT[out_dtype], self._stream()), what)
         return out
 
+    def flush(self, residual=None) -> None:
+        """Carry out an addition into the residual stream that ``linear(add_to=...)`` has put off. Every method of this
+        class that reads or writes the stream does this itself; code that reads the stream's tensor directly calls it first."""
+        if self._pending_add is None:
+            return
+        target, y = self._pending_add
+        if residual is not None and target.data_ptr() != residual.data_ptr():
+            residual = None  # another tensor is wanted: the pending one is finished all the same, nothing may stay behind
+        self._pending_add = None
+        self._check(self.lib.llmie_add_into(_ptr(target), _ptr(y), target.numel(), self._dt(y, "delta"), self._stream()), "add_into")
+
+    def _take_pending(self, residual, out_dtype):
+        """The put-off addend for ``residual`` if there is one that the norm kernel can add on its way (same dtype as its output)."""
+        if self._pending_add is None:
+            return None
+        target, y = self._pending_add
+        if target.data_ptr() == residual.data_ptr() and tuple(target.shape) == tuple(residual.shape) and y.dtype == out_dtype:
+            self._pending_add = None
+            return y
+        self.flush()
+        return None
+
     def add_rmsnorm(self, residual, delta, weight, eps, out_dtype):
+        if delta is None:
+            delta = self._take_pending(residual, out_dtype)
+        else:
+            self.flush()
         return self._norm(residual, delta, weight, eps, None, out_dtype, "add_rmsnorm")
 
     def rmsnorm_rows(self, residual, delta, weight, eps, rows, out_dtype):
+        self.flush()
         return self._norm(residual, delta, weight, eps, rows, out_dtype, "rmsnorm_rows")
 
     def _transient(self, M: int, N: int, device) -> torch.Tensor:
@@ -171,6 +201,8 @@ class CudaKernels:
         self._need(weight, "weight", torch.float32, 1)
         if weight.shape[0] != residual.shape[1]:
             raise KernelError("deferred_norm: weight does not match the rows")
+        if self._pending_add is not None and self._pending_add[0].data_ptr() != residual.data_ptr():
+            self.flush()
         return DeferredNorm(residual, weight, eps, out_dtype)
 
     def gated(self, gu, out_dtype):
@@ -207,21 +239,23 @@ class CudaKernels:
                 deferred = False
         if not deferred:
             self._need(x, "x", None, 2)
+        elif isinstance(x, DeferredNorm):
+            self.flush()  # the product will read the residual stream itself
         self._need(w, "w", x.dtype, 2)
         if K != w.shape[1]:
             raise KernelError(f"linear: x has {K} columns, w has {w.shape[1]}")
         bf16 = x.dtype == torch.bfloat16
         small = bf16 and self.use_tc_gemm and M <= self.tc_max_rows and K % 8 == 0
         if add_to is not None:
+            self.flush()
             self._need(add_to, "add_to", torch.float32, 2)
             if tuple(add_to.shape) != (M, N):
                 raise KernelError(f"linear: add_to is {list(add_to.shape)}, the product is [{M}, {N}]")
             if small:
                 self.linear_tc(x, w, out=add_to, accumulate=True)
-            elif bf16 and self.use_cublas:
+            elif bf16 and self.use_cublas and add_to.is_contiguous():
                 self.launches += 1
-                y = torch.matmul(x, w.t())
-                self._check(self.lib.llmie_add_into(_ptr(add_to), _ptr(y), M * N, 1, self._stream()), "add_into")
+                self._pending_add = (add_to, torch.matmul(x, w.t()))  # added by the norm that follows, or by flush()
             else:
                 self._check(self.lib.llmie_gemm_simt(_ptr(x), _ptr(w), _ptr(add_to), M, N, K, self._dt(x, "x"), 0, 1, self._stream()),
                             "linear (accumulate)")

@@ -70,18 +70,21 @@ def test_each_part_alone(tmp_path, name, dtype, tol):
         b = runner.bindings[i]
         r = res.clone().cuda()
         layer.mixer.forward(ctx, h.cuda(), b, r)
+        ctx.K.flush()   # an addition into the stream may be put off until the next kernel that reads it
         want = plain_attention(h.float(), w, f"model.layers.{i}.self_attn", c, pc, ps, c["window"][i])
         close(r.cpu() - res, want, tol)
 
     # feed-forward
     r = res.clone().cuda()
     spec.layers[1].ff.forward(ctx, h.cuda(), r)
+    ctx.K.flush()
     close(r.cpu() - res, plain_mlp(h.float(), w, "model.layers.1.mlp"), tol)
 
     # block: residual in, residual out
     res2 = torch.randn(T, H, generator=g) * 0.3
     r = res2.clone().cuda()
     spec.layers[1].forward(ctx, r, runner.bindings[1])
+    ctx.K.flush()
     close(r, plain_block(res2, w, 1, c, pc, ps), tol)
 
     # head
