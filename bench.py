@@ -13,7 +13,9 @@ batch of 8 requests and a context of 8192 tokens. A "step" is one decode step of
 ``e2e``       the same through ``Engine.step()``: requests are added as token lists on the host,
               their prompts are prefilled by the engine, and every timed step copies its inputs
               from pinned host memory and reads the sampled tokens back.
-``prefill``   one prompt of 2,048 tokens in one step; ``frac`` = flops / time / bfloat16 peak.
+``prefill``   one prompt of 2,048 tokens in one step (device time between two events, median of five runs after two
+              warm-up runs; a step shape that recurs is replayed from a CUDA graph, as in serving);
+              ``frac`` = flops / time / bfloat16 peak.
 ``roofline``  bytes a decode step must read (every weight once + the live requests' cache) / its time.
 ``points``    decode tokens per second at batch 1 and 64, same method as ``value``.
 
@@ -184,17 +186,17 @@ def decode_point(folder: Path, batch: int, steps: int, warmup: int, torch, graph
     return out
 
 
-def prefill_point(folder: Path, torch, reps: int = 3) -> dict:
+def prefill_point(folder: Path, torch, reps: int = 5, graphs: bool = True) -> dict:
     from llm_infrence_engine_b200.config import EngineConfig
     from llm_infrence_engine_b200.engine import StepEntry, build_runner
 
     cfg = EngineConfig(dtype="bfloat16", block_size=BLOCK, num_blocks=PREFILL_TOKENS // BLOCK + 2, max_seqs=1,
-                       max_len=PREFILL_TOKENS, max_num_batched_tokens=PREFILL_TOKENS)
+                       max_len=PREFILL_TOKENS, max_num_batched_tokens=PREFILL_TOKENS, cuda_graphs=graphs)
     spec, cache, runner = build_runner(folder, cfg)
     g = torch.Generator().manual_seed(5)
     prompt = torch.randint(0, MODEL["vocab_size"], (PREFILL_TOKENS,), generator=g).tolist()
     times = []
-    for i in range(reps + 1):
+    for i in range(reps + 2):  # the first two runs are warm-up: with graphs the step's shape is captured at its second coming
         cache.admit("p")
         cache.reserve("p", 0, PREFILL_TOKENS)
         torch.cuda.synchronize()
@@ -204,7 +206,7 @@ def prefill_point(folder: Path, torch, reps: int = 3) -> dict:
         stop.record()
         torch.cuda.synchronize()
         cache.free("p")
-        if i:
+        if i >= 2:
             times.append(start.elapsed_time(stop))
     ms = sorted(times)[len(times) // 2]
     del runner, spec, cache
@@ -278,7 +280,7 @@ def main() -> int:
         clocks = sampler.clocks
         b1 = decode_point(folder, 1, min(a.steps, 256), a.warmup, torch, graphs) if a.only == "all" else None
         b64 = decode_point(folder, 64, min(a.steps, 128), a.warmup, torch, graphs) if a.only == "all" else None
-        pre = prefill_point(folder, torch) if a.only in ("all", "prefill") else None
+        pre = prefill_point(folder, torch, graphs=graphs) if a.only in ("all", "prefill") else None
         e2e = None if (a.skip_e2e or a.only != "all") else e2e_point(folder, a.batch, min(a.steps, 512), a.warmup, torch, graphs)
 
     fl = flops_prefill(PREFILL_TOKENS) * a.layers / MODEL["num_hidden_layers"]

@@ -11,11 +11,18 @@ into the null page, which nobody reads.
 
 A graph fixes the launch shapes, so the number of key slices per token is planned for ``max_len``;
 the kernel cuts each token's own keys into that many slices on the device, whatever its length.
+
+Steps that bring prompt portions are launched kernel by kernel from Python, a few hundred launches that take the host
+longer than the device needs to run them. Their shape, the tuple of (tokens, wanted rows) per request, often comes
+again: a prompt cut under the token budget gives step after step of exactly the budget. So a shape that is seen a
+second time is captured too (a handful are kept, the least recently used goes), and from then on such a step is one
+launch.
 """
 from __future__ import annotations
 
 import gc
-from typing import Dict, List, Sequence
+from collections import OrderedDict
+from typing import Dict, List, Optional, Sequence
 
 import torch
 
@@ -45,12 +52,91 @@ class DecodeGraphs:
             and not any(isinstance(b, StateBinding) for b in runner.bindings)
         self.buckets = bucket_sizes(runner.max_seqs)
         self.captured: Dict[int, _Captured] = {}
+        self.shapes: "OrderedDict[tuple, _Captured]" = OrderedDict()  # captured prompt-portion steps, least recently used first
+        self.seen: Dict[tuple, int] = {}
+        self.max_shapes = 6
+        self.max_shape_tokens = 8192
         self.pool = None
         self.replays = 0
+        self.shape_replays = 0
 
     def fits(self, entries: Sequence[StepEntry]) -> bool:
         return self.usable and len(entries) <= self.buckets[-1] and \
             all(len(e.tokens) == 1 and e.context_len > 0 and len(e.want) == 1 for e in entries)
+
+    def shape_key(self, entries: Sequence[StepEntry]) -> Optional[tuple]:
+        """The shape of a step with prompt portions, if such steps may be captured at all."""
+        if not self.usable:
+            return None
+        n = sum(len(e.tokens) for e in entries)
+        if n > self.max_shape_tokens or len(entries) > 8:
+            return None
+        return tuple((len(e.tokens), len(e.want)) for e in entries)
+
+    def run_shape(self, entries: Sequence[StepEntry]):
+        """Replays (capturing first, if this is the second time) the graph of this step's shape; returns ``(handled, logits)``."""
+        key = self.shape_key(entries)
+        if key is None:
+            return False, None
+        r = self.runner
+        cap = self.shapes.get(key)
+        if cap is None:
+            self.seen[key] = self.seen.get(key, 0) + 1
+            if self.seen[key] < 2:
+                if len(self.seen) > 256:
+                    self.seen.clear()
+                return False, None
+        packed, N, R, M, changed, starts, lens, ctxs, slots = r._build(entries)
+        static_len = 3 * N + R + (R + 1) + M + len(r.cache.groups) * N
+        if cap is None:
+            static_in = torch.zeros(static_len, dtype=torch.int32, device=r.device)
+            full = r._upload(packed)
+            static_in.copy_(full[:static_len])
+            r._sync_tables(full, changed)
+            ctx = StepContext(r.K, r.dtype, r.device, r.page_size)
+            rows = r._fill_context(ctx, static_in, N, R, M)
+            ctx.seq_starts, ctx.seq_lens, ctx.seq_context, ctx.seq_slot_list = starts, lens, ctxs, slots
+            ctx.max_context, ctx.max_seq_len = r.max_len, max(lens)
+            cap = self._capture_context(ctx, rows)
+            cap.static_in = static_in
+            self.shapes[key] = cap
+            while len(self.shapes) > self.max_shapes:
+                self.shapes.popitem(last=False)
+        else:
+            self.shapes.move_to_end(key)
+            full = r._upload(packed)
+            cap.static_in.copy_(full[:static_len])
+            r._sync_tables(full, changed)
+        cap.graph.replay()
+        self.shape_replays += 1
+        return True, cap.logits
+
+    def _capture_context(self, ctx: StepContext, rows: torch.Tensor) -> _Captured:
+        """Warm up, then capture ``forward`` on a context whose tensors are views of a static buffer."""
+        r = self.runner
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                ctx._tables.clear()
+                r.forward(ctx, rows)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        if self.pool is None:
+            self.pool = torch.cuda.graph_pool_handle()
+        ctx._tables.clear()
+        before = r.K.launches
+        gc.collect()
+        was_enabled = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.cuda.graph(graph, pool=self.pool, capture_error_mode="relaxed"):
+                logits = r.forward(ctx, rows)
+        finally:
+            if was_enabled:
+                gc.enable()
+        return _Captured(graph, None, logits, r.K.launches - before)
 
     def _layout_len(self, B: int) -> int:
         # ids, positions, table rows, state slots, first rows (B + 1), wanted rows, then one cache slot per group

@@ -315,8 +315,12 @@ class ModelRunner:
         entries and of their ``want``, or None if nothing was wanted."""
         if not entries:
             return None
-        if self.graphs is not None and self.graphs.fits(entries):
-            return self.graphs.run(entries)
+        if self.graphs is not None:
+            if self.graphs.fits(entries):
+                return self.graphs.run(entries)
+            handled, logits = self.graphs.run_shape(entries)
+            if handled:
+                return logits
         ctx, logit_rows = self.make_context(entries)
         fresh = [s for s, c in zip(ctx.seq_slot_list, ctx.seq_context) if c == 0]
         if fresh:
@@ -334,6 +338,8 @@ class ModelRunner:
                 b = type(b)(**{**b.__dict__, "write": call.write})
             spec.layers[call.layer].forward(ctx, residual, b)
         if logit_rows.numel() == 0:
+            if hasattr(self.K, "flush"):
+                self.K.flush()  # nothing reads the residual stream any more: an addition that was put off must not stay behind
             return None
         h = spec.final_norm.norm_rows(ctx, residual, logit_rows)
         return spec.head.forward(ctx, h)

@@ -447,3 +447,39 @@ def test_stop_tokens_and_ignore_eos(models):
     eng.run_until_idle()
     assert a.output_ids == ref[:first] and a.finish_reason == "stop"     # the stop token is not kept (src/miniserve/engine.py:279-291)
     assert b.output_ids == ref and b.finish_reason == "length"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_recurring_step_shapes_from_cuda_graphs(models, dtype):
+    """A step shape that comes a second time is captured; from then on such steps are replayed. Portions of equal size of
+    one request, then of two requests together, with other contexts, pages and tokens each time."""
+    from llm_infrence_engine_b200.config import EngineConfig
+    from llm_infrence_engine_b200.engine import StepEntry, build_runner
+
+    folder, cfg, w, prompts, want = models[("C", dtype)]
+    ec = EngineConfig(dtype=dtype, block_size=16, num_blocks=40, max_seqs=4, max_len=160, max_num_batched_tokens=256, cuda_graphs=True)
+    spec, cache, runner = build_runner(folder, ec)
+    got = {"a": [], "b": []}
+    for k in ("a", "b"):
+        cache.admit(k)
+    pos = {"a": 0, "b": 0}
+
+    def portion(k, n, wanted):
+        cache.reserve(k, pos[k], pos[k] + n)
+        e = StepEntry(k, prompts[k][pos[k]:pos[k] + n], pos[k], list(range(n)) if wanted else ())
+        pos[k] += n
+        return e
+
+    for _ in range(5):                       # shape ((16, 16),): eager, then captured, then replayed three times
+        out = runner.step([portion("a", 16, True)])
+        got["a"].append(out.float().cpu())
+    for _ in range(4):                       # shape ((8, 8), (16, 16))
+        out = runner.step([portion("a", 8, True), portion("b", 16, True)]).float().cpu()
+        got["a"].append(out[:8]); got["b"].append(out[8:])
+    for _ in range(3):                       # a shape without wanted rows
+        assert runner.step([portion("b", 5, False)]) is None
+    out = runner.step([portion("b", 18, True)]).float().cpu()   # seen once only: eager
+    assert runner.graphs.shape_replays == 4 + 3 + 2 and len(runner.graphs.shapes) == 3
+    check(torch.cat(got["a"]), want["a"][:112], dtype, "request a")
+    check(torch.cat(got["b"]), want["b"][:64], dtype, "request b, first 64")
+    check(out, want["b"][79:97], dtype, "request b after the unwanted portions")
