@@ -13,7 +13,7 @@ batch of 8 requests and a context of 8192 tokens. A "step" is one decode step of
 ``e2e``       the same through ``Engine.step()``: requests are added as token lists on the host,
               their prompts are prefilled by the engine, and every timed step copies its inputs
               from pinned host memory and reads the sampled tokens back.
-``prefill``   one prompt of 2,048 tokens in one step (device time between two events, median of five runs after two
+``prefill``   one prompt of 2,048 tokens in one step (device time between two events, median of five runs after three
               warm-up runs; a step shape that recurs is replayed from a CUDA graph, as in serving);
               ``frac`` = flops / time / bfloat16 peak.
 ``roofline``  bytes a decode step must read (every weight once + the live requests' cache) / its time.
@@ -196,7 +196,7 @@ def prefill_point(folder: Path, torch, reps: int = 5, graphs: bool = True) -> di
     g = torch.Generator().manual_seed(5)
     prompt = torch.randint(0, MODEL["vocab_size"], (PREFILL_TOKENS,), generator=g).tolist()
     times = []
-    for i in range(reps + 2):  # the first two runs are warm-up: with graphs the step's shape is captured at its second coming
+    for i in range(reps + 3):  # the first three runs are warm-up: with graphs the step's shape is captured at its third coming
         cache.admit("p")
         cache.reserve("p", 0, PREFILL_TOKENS)
         torch.cuda.synchronize()
@@ -206,7 +206,7 @@ def prefill_point(folder: Path, torch, reps: int = 5, graphs: bool = True) -> di
         stop.record()
         torch.cuda.synchronize()
         cache.free("p")
-        if i >= 2:
+        if i >= 3:
             times.append(start.elapsed_time(stop))
     ms = sorted(times)[len(times) // 2]
     del runner, spec, cache

@@ -15,7 +15,7 @@ the kernel cuts each token's own keys into that many slices on the device, whate
 Steps that bring prompt portions are launched kernel by kernel from Python, a few hundred launches that take the host
 longer than the device needs to run them. Their shape, the tuple of (tokens, wanted rows) per request, often comes
 again: a prompt cut under the token budget gives step after step of exactly the budget. So a shape that is seen a
-second time is captured too (a handful are kept, the least recently used goes), and from then on such a step is one
+third time is captured too (a handful are kept, the least recently used goes), and from then on such a step is one
 launch.
 """
 from __future__ import annotations
@@ -55,6 +55,7 @@ class DecodeGraphs:
         self.shapes: "OrderedDict[tuple, _Captured]" = OrderedDict()  # captured prompt-portion steps, least recently used first
         self.seen: Dict[tuple, int] = {}
         self.max_shapes = 6
+        self.capture_after = 3   # a capture costs about a hundred eager steps: only shapes that keep coming are worth it
         self.max_shape_tokens = 8192
         self.pool = None
         self.replays = 0
@@ -82,7 +83,7 @@ class DecodeGraphs:
         cap = self.shapes.get(key)
         if cap is None:
             self.seen[key] = self.seen.get(key, 0) + 1
-            if self.seen[key] < 2:
+            if self.seen[key] < self.capture_after:
                 if len(self.seen) > 256:
                     self.seen.clear()
                 return False, None

@@ -470,6 +470,7 @@ def test_recurring_step_shapes_from_cuda_graphs(models, dtype):
         pos[k] += n
         return e
 
+    runner.graphs.capture_after = 2
     for _ in range(5):                       # shape ((16, 16),): eager, then captured, then replayed three times
         out = runner.step([portion("a", 16, True)])
         got["a"].append(out.float().cpu())
