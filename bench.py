@@ -145,11 +145,11 @@ def decode_point(folder: Path, batch: int, steps: int, warmup: int, torch, graph
     if graphs:
         runner.step(entries)  # captures the graph for this batch size and leaves the step's inputs in its static buffer
         cap = runner.graphs.captured[batch]
-        per_step = cap.launches + 1
+        per_step = cap.launches  # the captured step ends with the argmax over its logits
 
         def one():
             cap.graph.replay()
-            return K.argmax(cap.logits[:batch])
+            return cap.tokens
     else:
         ctx, rows = runner.make_context(entries)
         n0 = K.launches

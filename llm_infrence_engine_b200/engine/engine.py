@@ -127,7 +127,8 @@ class Engine:
             rows = [s.req for s in plan.items if s.samples]
             if rows:
                 params = [SamplingParams(r.temperature, r.top_k, r.top_p, self._seed(r)) for r in rows]
-                tokens = self.sampler.sample(logits, params, [len(r.output_ids) for r in rows])
+                greedy = self.runner.greedy_tokens if len(rows) == len(plan.items) else None
+                tokens = self.sampler.sample(logits, params, [len(r.output_ids) for r in rows], greedy)
                 for r, tok in zip(rows, tokens):
                     self._emit(r, int(tok))
                     useful += 1

@@ -40,9 +40,10 @@ def bucket_sizes(max_batch: int) -> List[int]:
 
 
 class _Captured:
-    def __init__(self, graph, static_in, logits, launches):
+    def __init__(self, graph, static_in, logits, launches, tokens=None):
         self.graph, self.static_in, self.logits = graph, static_in, logits
         self.launches = launches  # kernels that one replay launches
+        self.tokens = tokens      # argmax of every row of ``logits``, made inside the graph (decode graphs)
 
 
 class DecodeGraphs:
@@ -160,7 +161,7 @@ class DecodeGraphs:
         with torch.cuda.stream(side):
             for _ in range(3):
                 ctx._tables.clear()
-                r.forward(ctx, rows)
+                r.K.argmax(r.forward(ctx, rows))
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
@@ -177,10 +178,12 @@ class DecodeGraphs:
         try:
             with torch.cuda.graph(graph, pool=self.pool, capture_error_mode="relaxed"):
                 logits = r.forward(ctx, rows)
+                tokens = r.K.argmax(logits)  # greedy rows need nothing more than this; the others are sampled from ``logits``
         finally:
             if was_enabled:
                 gc.enable()
-        return _Captured(graph, static_in, logits, r.K.launches - before)
+        return _Captured(graph, static_in, logits, r.K.launches - before, tokens)
+
 
     @torch.inference_mode()
     def run(self, entries: Sequence[StepEntry]) -> torch.Tensor:
@@ -199,4 +202,5 @@ class DecodeGraphs:
             r._sync_tables(full, changed)
         cap.graph.replay()
         self.replays += 1
+        r.greedy_tokens = cap.tokens[:n]
         return cap.logits[:n]

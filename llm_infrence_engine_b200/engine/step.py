@@ -112,6 +112,7 @@ class ModelRunner:
         self._staging: List[list] = []  # ring of [pinned buffer, event of the copy that last read it]
         self._next_staging = 0
         self.last_h2d_bytes = 0  # bytes of step inputs copied to the device by the last step
+        self.greedy_tokens = None
         self.graphs = None
         if cuda_graphs:
             from .graphs import DecodeGraphs
@@ -315,6 +316,7 @@ class ModelRunner:
         entries and of their ``want``, or None if nothing was wanted."""
         if not entries:
             return None
+        self.greedy_tokens = None  # set by a captured decode step: the argmax of the returned rows, already on the device
         if self.graphs is not None:
             if self.graphs.fits(entries):
                 return self.graphs.run(entries)

@@ -15,7 +15,7 @@ the same tokens whatever else is in the batch and after a preemption.
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import List, Sequence
+from typing import List, Optional, Sequence
 
 import torch
 
@@ -51,11 +51,15 @@ class Sampler:
     def __init__(self, kernels):
         self.K = kernels
 
-    def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], counters: Sequence[int]) -> List[int]:
-        """logits ``[M, vocab]`` float32 on the device -> M token ids on the host."""
+    def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], counters: Sequence[int],
+               greedy_tokens: Optional[torch.Tensor] = None) -> List[int]:
+        """logits ``[M, vocab]`` float32 on the device -> M token ids on the host. ``greedy_tokens``: the rows' argmax if
+        the step already made it on the device."""
         if logits.shape[0] != len(params):
             raise ValueError("one SamplingParams per row of logits is needed")
         if all(p.temperature <= 0.0 for p in params):
+            if greedy_tokens is not None and greedy_tokens.shape[0] == logits.shape[0]:
+                return greedy_tokens.tolist()
             return self.K.argmax(logits).tolist()
         dev = logits.device
         t = torch.tensor([p.temperature for p in params], dtype=torch.float32).to(dev)
