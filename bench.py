@@ -12,7 +12,8 @@ batch of 8 requests and a context of 8192 tokens. A "step" is one decode step of
               depend on them); weights plus cache are far larger than L2, so nothing is flushed.
 ``e2e``       the same through ``Engine.step()``: requests are added as token lists on the host,
               their prompts are prefilled by the engine, and every timed step copies its inputs
-              from pinned host memory and reads the sampled tokens back.
+              from pinned host memory and reads sampled tokens back (the engine runs pipelined: a
+              step is launched before the tokens of the step before it have been read).
 ``prefill``   one prompt of 2,048 tokens in one step (device time between two events, median of five runs after three
               warm-up runs; a step shape that recurs is replayed from a CUDA graph, as in serving);
               ``frac`` = flops / time / bfloat16 peak.
@@ -222,7 +223,7 @@ def e2e_point(folder: Path, batch: int, steps: int, warmup: int, torch, graphs: 
     prompt_len = CONTEXT - total
     per_seq = -(-(CONTEXT + 8) // BLOCK)
     eng = Engine(str(folder), dtype="bfloat16", block_size=BLOCK, num_blocks=batch * per_seq + 1, max_seqs=batch,
-                 max_len=CONTEXT + 8, max_num_batched_tokens=2048, cuda_graphs=graphs)
+                 max_len=CONTEXT + 8, max_num_batched_tokens=2048, cuda_graphs=graphs, pipeline=True)
     g = torch.Generator().manual_seed(9)
     reqs = [eng.add_request(Request(torch.randint(0, MODEL["vocab_size"], (prompt_len,), generator=g).tolist(), max_new_tokens=total))
             for _ in range(batch)]

@@ -23,6 +23,7 @@ class EngineConfig:
     max_len: int = 1024              # most tokens (prompt + generated) one request may reach
     max_num_batched_tokens: int = 2048  # token budget of one step
     cuda_graphs: bool = False        # replay decode-only steps from captured graphs
+    pipeline: bool = False           # launch a step before the host has read the tokens of the step before it
     seed: int = 0                    # engine seed for requests that bring none
 
     def validate(self) -> None:

@@ -44,6 +44,21 @@ LLMIE_API int llmie_embed(const int* ids, const void* table, float* out, int N, 
 }
 
 // ------------------------------------------------------------------------------------------------
+// ids[i] = previous[src[i]] where src[i] >= 0: a request's next token taken from the tokens the step before chose, which
+// are still on the device (the host has not read them yet)
+__global__ void feed_tokens_kernel(int* __restrict__ ids, const int* __restrict__ src, const int* __restrict__ previous, int N) {
+    pdl_trigger();
+    pdl_wait();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < N && src[i] >= 0) ids[i] = previous[src[i]];
+}
+
+LLMIE_API int llmie_feed_tokens(int* ids, const int* src, const int* previous, int N, cudaStream_t s) {
+    if (N <= 0) return 0;
+    return launch_kernel(feed_tokens_kernel, dim3((N + 127) / 128), dim3(128), 0, s, ids, (const int*)src, previous, N);
+}
+
+// ------------------------------------------------------------------------------------------------
 // cos/sin[n, j] of the angle float(position[n]) * inv_freq[j], all in 32-bit
 __global__ void rope_tables_kernel(const int* __restrict__ pos, const float* __restrict__ inv_freq, float* __restrict__ cos_out,
                                    float* __restrict__ sin_out, int N, int half) {

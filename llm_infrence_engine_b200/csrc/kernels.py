@@ -81,7 +81,7 @@ class CudaKernels:
         self.fuse_max_rows = 16       # ... for batches up to this many rows: every block redoes the row work, which must stay small
         self._error_flag: Optional[torch.Tensor] = None
         self.num_sms = torch.cuda.get_device_properties(0).multi_processor_count or NUM_SMS_FALLBACK
-        for fn in ("llmie_embed", "llmie_rope_tables", "llmie_add_rmsnorm", "llmie_rope_kv_write", "llmie_silu_mul",
+        for fn in ("llmie_embed", "llmie_feed_tokens", "llmie_rope_tables", "llmie_add_rmsnorm", "llmie_rope_kv_write", "llmie_silu_mul",
                    "llmie_gemm_simt", "llmie_gemm_tc", "llmie_gemm_tc_norm", "llmie_gemm_tc_silu", "llmie_add_into", "llmie_attn_plan", "llmie_paged_attention_mma", "llmie_paged_attention_f32", "llmie_paged_attention_bf16", "llmie_argmax", "llmie_sample"):
             getattr(self.lib, fn).restype = ctypes.c_int
         # kernels of a step overlap their set-up with the tail of the kernel before (programmatic dependent launch)
@@ -126,6 +126,15 @@ class CudaKernels:
         self._check(self.lib.llmie_embed(_ptr(token_ids), _ptr(table), _ptr(out), N, H, self._dt(table, "table"), self._stream()),
                     "embed")
         return out
+
+    def feed_tokens(self, token_ids, source_rows, previous_tokens):
+        """``token_ids[i] = previous_tokens[source_rows[i]]`` wherever ``source_rows[i] >= 0`` (all int32, on the device)."""
+        for name, t in (("token_ids", token_ids), ("source_rows", source_rows), ("previous_tokens", previous_tokens)):
+            self._need(t, name, torch.int32, 1)
+        if source_rows.shape[0] != token_ids.shape[0]:
+            raise KernelError("feed_tokens: one source row per token is needed")
+        self._check(self.lib.llmie_feed_tokens(_ptr(token_ids), _ptr(source_rows), _ptr(previous_tokens), token_ids.shape[0],
+                                               self._stream()), "feed_tokens")
 
     def rope_tables(self, positions, inv_freq):
         self._need(positions, "positions", torch.int32, 1)

@@ -67,6 +67,10 @@ class Engine:
         self.peak_running = 0
         self.peak_pages_in_use = 0
         self.prefill_tokens_computed = 0
+        self._pipeline = bool(self.config.pipeline) and torch.device(self.config.device).type == "cuda"
+        self._inflight = None        # (requests, their tokens on the device, pinned copy, event) of the step that was launched last
+        self._token_ring: list = []
+        self._token_next = 0
 
     @classmethod
     def from_pretrained(cls, model: Union[str, Path], **kw) -> "Engine":
@@ -96,7 +100,7 @@ class Engine:
         return req
 
     def has_work(self) -> bool:
-        return self.scheduler.has_work()
+        return self.scheduler.has_work() or self._inflight is not None
 
     def cancel(self, req: Request) -> None:
         """Honoured at the start of the next step (src/miniserve/engine.py:163-177)."""
@@ -107,7 +111,12 @@ class Engine:
             self.step()
 
     def step(self) -> StepRecord:
+        """One step of the engine. With ``EngineConfig.pipeline`` the tokens a step chooses stay on the device: the next
+        step is launched with them (``StepEntry.from_previous``) before the host reads them, so the device never waits for
+        the host's book-keeping; what this call emits are then the tokens of the step BEFORE the one it launches. A request
+        whose token turns out to be a stop token has by then been given one more row, whose result is dropped."""
         t0 = self.clock()
+        prev, self._inflight = self._inflight, None
         plan = self.scheduler.schedule()
         now = self.clock()
         for r in plan.aborted:
@@ -118,20 +127,36 @@ class Engine:
         if plan.items:
             entries = []
             for s in plan.items:
-                ids = s.req.tokens(s.start, s.start + s.count)
-                if s.req.admitted_time is None:
-                    s.req.admitted_time = now
-                entries.append(StepEntry(s.req.id, ids, s.start, (s.count - 1,) if s.samples else ()))
-            logits = self.runner.step(entries)
+                r = s.req
+                if r.admitted_time is None:
+                    r.admitted_time = now
+                want = (s.count - 1,) if s.samples else ()
+                if s.start + s.count > len(r.prompt_ids) + len(r.output_ids):  # its last token is still on the device
+                    if prev is None or s.count != 1 or r not in prev[0]:
+                        raise RuntimeError(f"request {r.id} was scheduled past its known tokens")
+                    entries.append(StepEntry(r.id, [0], s.start, want, from_previous=prev[0].index(r)))
+                else:
+                    entries.append(StepEntry(r.id, r.tokens(s.start, s.start + s.count), s.start, want))
+            logits = self.runner.step(entries, previous_tokens=prev[1] if prev is not None else None)
             self.scheduler.advance(plan)
             rows = [s.req for s in plan.items if s.samples]
             if rows:
                 params = [SamplingParams(r.temperature, r.top_k, r.top_p, self._seed(r)) for r in rows]
                 greedy = self.runner.greedy_tokens if len(rows) == len(plan.items) else None
-                tokens = self.sampler.sample(logits, params, [len(r.output_ids) for r in rows], greedy)
-                for r, tok in zip(rows, tokens):
-                    self._emit(r, int(tok))
-                    useful += 1
+                chosen = self.sampler.sample_device(logits, params, [len(r.output_ids) + r.in_flight for r in rows], greedy)
+                if self._pipeline:
+                    pinned, event = self._token_buffer()
+                    pinned[:len(rows)].copy_(chosen, non_blocking=True)
+                    event.record()
+                    for r in rows:
+                        r.in_flight += 1
+                    self._inflight = (rows, chosen, pinned, event)
+                else:
+                    for r, tok in zip(rows, chosen.tolist()):
+                        self._emit(r, int(tok))
+                        useful += 1
+        if prev is not None:
+            useful += self._read(prev)
         decode = sum(1 for s in plan.items if s.count == 1 and s.start > 0)
         n_tok = plan.num_tokens
         self.prefill_tokens_computed += n_tok - decode
@@ -141,6 +166,33 @@ class Engine:
         rec = StepRecord(plan.admitted, decode, useful, self.clock() - t0, plan.preempted, n_tok, n_tok - decode)
         self.steps.append(rec)
         return rec
+
+    def _token_buffer(self):
+        """A pinned buffer for one step's chosen tokens and the event of its copy, from a ring of three."""
+        if not self._token_ring:
+            self._token_ring = [(torch.empty(max(self.config.max_seqs, 1), dtype=torch.int32, pin_memory=True), torch.cuda.Event())
+                                for _ in range(3)]
+        self._token_next = (self._token_next + 1) % len(self._token_ring)
+        return self._token_ring[self._token_next]
+
+    def _read(self, inflight) -> int:
+        """Wait for a launched step's tokens and hand them to their requests; returns how many were kept."""
+        rows, _, pinned, event = inflight
+        event.synchronize()
+        kept = 0
+        for r, tok in zip(rows, pinned[:len(rows)].tolist()):
+            r.in_flight -= 1
+            if r.state == "finished":
+                continue  # ended by the token before this one (a stop token), or cancelled: this row was one too many
+            self._emit(r, int(tok))
+            kept += 1
+        return kept
+
+    def drain(self) -> None:
+        """Read the tokens of a step that is still on its way (pipelined engine), launching nothing new."""
+        if self._inflight is not None:
+            prev, self._inflight = self._inflight, None
+            self._read(prev)
 
     def stats(self) -> dict:
         """src/miniserve/paged_engine.py:68-80, without the prefix-cache figures."""
@@ -196,6 +248,7 @@ class Engine:
                                          None if seed is None else seed + i)) for i, p in enumerate(batch)]
         while any(r.state != "finished" for r in reqs):
             self.step()
+        self.drain()
         total = self.clock() - t0
         out = []
         for r in reqs:

@@ -26,7 +26,7 @@ from typing import Dict, List, Optional, Sequence
 
 import torch
 
-from .step import StateBinding, StepContext, StepEntry
+from .step import StateBinding, StepContext, StepEntry, step_layout
 
 
 def bucket_sizes(max_batch: int) -> List[int]:
@@ -75,7 +75,7 @@ class DecodeGraphs:
             return None
         return tuple((len(e.tokens), len(e.want)) for e in entries)
 
-    def run_shape(self, entries: Sequence[StepEntry]):
+    def run_shape(self, entries: Sequence[StepEntry], previous_tokens: Optional[torch.Tensor] = None):
         """Replays (capturing first, if this is the second time) the graph of this step's shape; returns ``(handled, logits)``."""
         key = self.shape_key(entries)
         if key is None:
@@ -89,7 +89,7 @@ class DecodeGraphs:
                     self.seen.clear()
                 return False, None
         packed, N, R, M, changed, starts, lens, ctxs, slots = r._build(entries)
-        static_len = 3 * N + R + (R + 1) + M + len(r.cache.groups) * N
+        static_len = step_layout(N, R, M, len(r.cache.groups))["end"][0]
         if cap is None:
             static_in = torch.zeros(static_len, dtype=torch.int32, device=r.device)
             full = r._upload(packed)
@@ -99,6 +99,7 @@ class DecodeGraphs:
             rows = r._fill_context(ctx, static_in, N, R, M)
             ctx.seq_starts, ctx.seq_lens, ctx.seq_context, ctx.seq_slot_list = starts, lens, ctxs, slots
             ctx.max_context, ctx.max_seq_len = r.max_len, max(lens)
+            r.feed(ctx, entries, previous_tokens)
             cap = self._capture_context(ctx, rows)
             cap.static_in = static_in
             self.shapes[key] = cap
@@ -109,6 +110,11 @@ class DecodeGraphs:
             full = r._upload(packed)
             cap.static_in.copy_(full[:static_len])
             r._sync_tables(full, changed)
+            if any(e.from_previous is not None for e in entries):
+                lay = step_layout(N, R, M, len(r.cache.groups))
+                if previous_tokens is None:
+                    raise ValueError("an entry takes its token from the previous step, but no previous tokens were given")
+                r.K.feed_tokens(cap.static_in[:N], cap.static_in[lay["feed"][0]:lay["feed"][0] + N], previous_tokens)
         cap.graph.replay()
         self.shape_replays += 1
         return True, cap.logits
@@ -141,8 +147,7 @@ class DecodeGraphs:
         return _Captured(graph, None, logits, r.K.launches - before)
 
     def _layout_len(self, B: int) -> int:
-        # ids, positions, table rows, state slots, first rows (B + 1), wanted rows, then one cache slot per group
-        return B * (6 + len(self.runner.cache.groups)) + 1
+        return step_layout(B, B, B, len(self.runner.cache.groups))["end"][0]
 
     def _capture(self, B: int) -> _Captured:
         r = self.runner
@@ -153,9 +158,11 @@ class DecodeGraphs:
         ctx.seq_slot_list = [r.max_seqs] * B
         ctx.max_context, ctx.max_seq_len = r.max_len, 1
         # padding values, so that warm-up and capture run on harmless inputs
-        static_in[2 * B:3 * B] = r.max_seqs
-        static_in[4 * B:5 * B + 1] = torch.arange(B + 1, dtype=torch.int32, device=r.device)
-        static_in[5 * B + 1:6 * B + 1] = torch.arange(B, dtype=torch.int32, device=r.device)
+        lay = step_layout(B, B, B, len(r.cache.groups))
+        static_in[lay["tok_slot"][0]:lay["tok_slot"][0] + B] = r.max_seqs
+        static_in[lay["starts"][0]:lay["starts"][0] + B + 1] = torch.arange(B + 1, dtype=torch.int32, device=r.device)
+        static_in[lay["rows"][0]:lay["rows"][0] + B] = torch.arange(B, dtype=torch.int32, device=r.device)
+        static_in[lay["feed"][0]:lay["feed"][0] + B] = -1
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
@@ -186,7 +193,7 @@ class DecodeGraphs:
 
 
     @torch.inference_mode()
-    def run(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+    def run(self, entries: Sequence[StepEntry], previous_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
         r = self.runner
         n = len(entries)
         B = next(b for b in self.buckets if b >= n)
@@ -200,6 +207,11 @@ class DecodeGraphs:
             full = r._upload(packed)
             cap.static_in.copy_(full[: self._layout_len(B)])
             r._sync_tables(full, changed)
+        if any(e.from_previous is not None for e in entries):
+            if previous_tokens is None:
+                raise ValueError("an entry takes its token from the previous step, but no previous tokens were given")
+            lay = step_layout(B, B, B, len(r.cache.groups))
+            r.K.feed_tokens(cap.static_in[:B], cap.static_in[lay["feed"][0]:lay["feed"][0] + B], previous_tokens)
         cap.graph.replay()
         self.replays += 1
         r.greedy_tokens = cap.tokens[:n]

@@ -24,6 +24,7 @@ class Request:
     finish_reason: Optional[str] = None  # "stop" | "length" | "abort"
     cancelled: bool = False
     num_computed: int = 0        # tokens of prompt + output whose keys and values are in the cache
+    in_flight: int = 0           # tokens chosen on the device that the host has not read yet (pipelined engine): 0 or 1
     preemptions: int = 0
     admit_seq: int = 0           # admission order; the youngest is preempted first
     arrival_time: float = 0.0
@@ -38,8 +39,8 @@ class Request:
 
     @property
     def num_tokens(self) -> int:
-        """Tokens known so far: prompt plus output."""
-        return len(self.prompt_ids) + len(self.output_ids)
+        """Tokens so far: prompt plus output, the one still on the device included."""
+        return len(self.prompt_ids) + len(self.output_ids) + self.in_flight
 
     def tokens(self, start: int, stop: int) -> List[int]:
         """``all_ids[start:stop]`` without joining the two lists."""

@@ -79,9 +79,12 @@ class Scheduler:
         return bool(self.waiting) or bool(self.running)
 
     def finish(self, req: Request) -> None:
-        """A running request ends: everything it holds goes back."""
-        self.running.remove(req)
-        self.cache.free(req.id)
+        """A request ends: everything it holds goes back. (It may be waiting: preempted while its last token was on its way.)"""
+        if req in self.running:
+            self.running.remove(req)
+            self.cache.free(req.id)
+        elif req in self.waiting:
+            self.waiting.remove(req)
         req.state = "finished"
 
     def _preempt(self, victim: Request) -> None:
@@ -111,6 +114,8 @@ class Scheduler:
         for r in order:
             if r.state != "running" or budget <= 0:
                 continue
+            if r.in_flight and len(r.output_ids) + r.in_flight >= r.max_new_tokens:
+                continue  # the token on its way is its last
             pending = r.num_tokens - r.num_computed
             count = min(pending, budget)
             while True:
@@ -134,6 +139,8 @@ class Scheduler:
         while self.waiting and not plan.preempted and budget > 0 and len(self.running) < self.max_seqs \
                 and self.cache.num_free_slots() > 0:
             r = self.waiting[0]
+            if r.in_flight:
+                break  # preempted with a token still on the device: it comes back once that token has been read
             pending = r.num_tokens
             count = min(pending, budget)
             self.cache.admit(r.id)

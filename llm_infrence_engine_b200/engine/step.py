@@ -31,6 +31,8 @@ class StepEntry:
     tokens: Sequence[int]         # its next tokens
     context_len: int              # tokens of it that are already in the cache
     want: Sequence[int] = ()      # places among ``tokens`` whose logits are asked for
+    from_previous: Optional[int] = None  # the entry's single token is row ``from_previous`` of the device tensor of tokens
+                                         # given to ``step(previous_tokens=...)``; ``tokens`` then holds a placeholder
 
 
 @dataclass
@@ -63,6 +65,7 @@ class StepContext:
         self.token_seq: torch.Tensor = None      # [N] int32, the token's row in the block tables (= its request's state slot)
         self.seq_slots: torch.Tensor = None      # [R] int32, state slot of each request
         self.seq_starts_dev: torch.Tensor = None  # [R + 1] int32, first row of each request in the flat batch, then N
+        self.feed_rows: torch.Tensor = None       # [N] int32, row of the previous step's tokens a token comes from, or -1
         self.block_tables: List[torch.Tensor] = []  # per group [state slots + 1, max_blocks] int32, a row per state slot
         self.slot_mapping: List[torch.Tensor] = []  # per group [N] int32: page * page_size + offset of the token's key
         self.seq_starts: List[int] = []          # host: first row of each request in the flat batch
@@ -78,6 +81,20 @@ class StepContext:
         if key not in self._tables:
             self._tables[key] = encoding.tables(self)
         return self._tables[key]
+
+
+def step_layout(N: int, R: int, M: int, groups: int) -> Dict[str, tuple]:
+    """Where each array of a step lies in the packed int32 buffer: name -> (offset, length). Block-table rows that
+    changed ride behind ``end``."""
+    out, o = {}, 0
+    for name, n in (("ids", N), ("pos", N), ("tok_slot", N), ("slots", R), ("starts", R + 1), ("rows", M), ("feed", N)):
+        out[name] = (o, n)
+        o += n
+    for g in range(groups):
+        out[f"map{g}"] = (o, N)
+        o += N
+    out["end"] = (o, 0)
+    return out
 
 
 class ModelRunner:
@@ -154,10 +171,17 @@ class ModelRunner:
                 rows.append(int(st) + int(w))
         N, M = int(ids.shape[0]), len(rows)
         pad = max(0, pad_to - N)
+        feed = np.full(N + pad, -1, np.int64)
+        for st, e, n in zip(starts, entries, lens):
+            if e.from_previous is not None:
+                if n != 1:
+                    raise ValueError(f"request {e.req!r}: only a single token can come from the previous step's tokens")
+                feed[int(st)] = int(e.from_previous)
         parts = [ids, np.zeros(pad, np.int64), pos, np.zeros(pad, np.int64), tok_slot, np.full(pad, self.max_seqs, np.int64),
                  np.asarray(slots, dtype=np.int64), np.zeros(pad, np.int64),
                  starts, np.arange(N, N + pad + 1, dtype=np.int64),
-                 np.asarray(rows, dtype=np.int64), np.arange(N, N + pad, dtype=np.int64) if pad_to else np.zeros(0, np.int64)]
+                 np.asarray(rows, dtype=np.int64), np.arange(N, N + pad, dtype=np.int64) if pad_to else np.zeros(0, np.int64),
+                 feed]
         changed = []  # (group, slot, offset of the row in the packed array)
         offset = sum(len(p) for p in parts)
         for g in range(groups):
@@ -211,8 +235,9 @@ class ModelRunner:
                 rows.append(i)
         pad = max(0, pad_to - R)
         zeros = [0] * pad
+        feed = [-1 if e.from_previous is None else int(e.from_previous) for e in entries] + [-1] * pad
         packed = (ids + zeros + ctxs + zeros + slots + [self.max_seqs] * pad + slots + zeros + list(range(R + pad + 1)) + rows
-                  + (list(range(R, R + pad)) if pad_to else []))
+                  + (list(range(R, R + pad)) if pad_to else []) + feed)
         for g in range(groups):
             for e, c in zip(entries, ctxs):
                 t = cache.block_table(e.req, g)
@@ -249,14 +274,16 @@ class ModelRunner:
         n = int(packed.shape[0])
         self.last_h2d_bytes = 4 * n
         if not self._staging:
-            self._staging = [[None, None] for _ in range(4)]
+            self._staging = [[None, None, None] for _ in range(4)]  # pinned tensor, event of its last copy, numpy view
         slot = self._staging[self._next_staging]
         self._next_staging = (self._next_staging + 1) % len(self._staging)
         if slot[1] is not None:
             slot[1].synchronize()
         if slot[0] is None or slot[0].numel() < n:
             slot[0] = torch.empty(max(2 * n, 8192), dtype=torch.int32, pin_memory=True)
-        slot[0][:n].copy_(torch.from_numpy(packed))
+            slot[2] = slot[0].numpy()
+            slot[1] = torch.cuda.Event()
+        slot[2][:n] = packed
         self._last_slot = slot
         return slot[0][:n]
 
@@ -273,7 +300,6 @@ class ModelRunner:
             dev = into
         else:
             dev = pinned.to(self.device, non_blocking=True)
-        self._last_slot[1] = torch.cuda.Event()
         self._last_slot[1].record()
         return dev
 
@@ -294,36 +320,48 @@ class ModelRunner:
         return ctx, logit_rows
 
     def _fill_context(self, ctx: StepContext, dev: torch.Tensor, N: int, R: int, M: int) -> torch.Tensor:
-        """Point the context's tensors at their places in the packed device array (layout of ``_build``)."""
+        """Point the context's tensors at their places in the packed device array (``step_layout``)."""
         ctx.num_tokens, ctx.num_seqs = N, R
-        o = 0
-        ctx.token_ids = dev[o:o + N]; o += N
-        ctx.positions = dev[o:o + N]; o += N
-        ctx.token_seq = dev[o:o + N]; o += N
-        ctx.seq_slots = dev[o:o + R]; o += R
-        ctx.seq_starts_dev = dev[o:o + R + 1]; o += R + 1
-        logit_rows = dev[o:o + M]; o += M
+        lay = step_layout(N, R, M, len(self.cache.groups))
+
+        def view(name):
+            o, n = lay[name]
+            return dev[o:o + n]
+
+        ctx.token_ids, ctx.positions, ctx.token_seq = view("ids"), view("pos"), view("tok_slot")
+        ctx.seq_slots, ctx.seq_starts_dev = view("slots"), view("starts")
+        ctx.feed_rows = view("feed")
         ctx.slot_mapping, ctx.block_tables = [], []
         for g in range(len(self.cache.groups)):
-            ctx.slot_mapping.append(dev[o:o + N]); o += N
+            ctx.slot_mapping.append(view(f"map{g}"))
             ctx.block_tables.append(self.tables_dev[g])
-        return logit_rows
+        return view("rows")
+
+    def feed(self, ctx: StepContext, entries: Sequence[StepEntry], previous_tokens: Optional[torch.Tensor]) -> None:
+        """Fill in the tokens that come from the step before (``StepEntry.from_previous``), on the device."""
+        if any(e.from_previous is not None for e in entries):
+            if previous_tokens is None:
+                raise ValueError("an entry takes its token from the previous step, but no previous tokens were given")
+            self.K.feed_tokens(ctx.token_ids, ctx.feed_rows, previous_tokens)
 
     # ------------------------------------------------------------------ the step
     @torch.inference_mode()
-    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+    def step(self, entries: Sequence[StepEntry], previous_tokens: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
         """Run the entries as one batch; returns float32 logits ``[wanted, vocab]`` in the order of the
-        entries and of their ``want``, or None if nothing was wanted."""
+        entries and of their ``want``, or None if nothing was wanted. ``previous_tokens``: int32 tokens on the device
+        that entries with ``from_previous`` take their token from (the step before chose them; the host need not have
+        read them yet)."""
         if not entries:
             return None
         self.greedy_tokens = None  # set by a captured decode step: the argmax of the returned rows, already on the device
         if self.graphs is not None:
             if self.graphs.fits(entries):
-                return self.graphs.run(entries)
-            handled, logits = self.graphs.run_shape(entries)
+                return self.graphs.run(entries, previous_tokens)
+            handled, logits = self.graphs.run_shape(entries, previous_tokens)
             if handled:
                 return logits
         ctx, logit_rows = self.make_context(entries)
+        self.feed(ctx, entries, previous_tokens)
         fresh = [s for s, c in zip(ctx.seq_slot_list, ctx.seq_context) if c == 0]
         if fresh:
             for b in self.bindings:

@@ -51,19 +51,24 @@ class Sampler:
     def __init__(self, kernels):
         self.K = kernels
 
-    def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], counters: Sequence[int],
-               greedy_tokens: Optional[torch.Tensor] = None) -> List[int]:
-        """logits ``[M, vocab]`` float32 on the device -> M token ids on the host. ``greedy_tokens``: the rows' argmax if
-        the step already made it on the device."""
+    def sample_device(self, logits: torch.Tensor, params: Sequence[SamplingParams], counters: Sequence[int],
+                      greedy_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """logits ``[M, vocab]`` float32 on the device -> M token ids (int32) still on the device. ``greedy_tokens``: the
+        rows' argmax if the step already made it."""
         if logits.shape[0] != len(params):
             raise ValueError("one SamplingParams per row of logits is needed")
         if all(p.temperature <= 0.0 for p in params):
             if greedy_tokens is not None and greedy_tokens.shape[0] == logits.shape[0]:
-                return greedy_tokens.tolist()
-            return self.K.argmax(logits).tolist()
+                return greedy_tokens
+            return self.K.argmax(logits)
         dev = logits.device
         t = torch.tensor([p.temperature for p in params], dtype=torch.float32).to(dev)
         k = torch.tensor([p.top_k for p in params], dtype=torch.int32).to(dev)
         pp = torch.tensor([p.top_p for p in params], dtype=torch.float32).to(dev)
         u = torch.tensor([uniform_from(p.seed, c) for p, c in zip(params, counters)], dtype=torch.float32).to(dev)
-        return self.K.sample(logits, t, k, pp, u).tolist()
+        return self.K.sample(logits, t, k, pp, u)
+
+    def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], counters: Sequence[int],
+               greedy_tokens: Optional[torch.Tensor] = None) -> List[int]:
+        """The same, read back: M token ids on the host."""
+        return self.sample_device(logits, params, counters, greedy_tokens).tolist()

@@ -484,3 +484,39 @@ def test_recurring_step_shapes_from_cuda_graphs(models, dtype):
     check(torch.cat(got["a"]), want["a"][:112], dtype, "request a")
     check(torch.cat(got["b"]), want["b"][:64], dtype, "request b, first 64")
     check(out, want["b"][79:97], dtype, "request b after the unwanted portions")
+
+
+@pytest.mark.parametrize("graphs", [False, True])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_pipelined_engine_gives_the_same_tokens(models, name, graphs):
+    """Launching a step before the host has read the tokens of the step before changes nothing that a request sees:
+    greedy and sampled requests, stop tokens, length limits, a pool so small that requests are preempted."""
+    from llm_infrence_engine_b200.engine import Engine, Request
+
+    folder, cfg, w, prompts, want = models[(name, "float32")]
+    vocab = cfg["vocab_size"]
+    ps = [random_prompt(vocab, n, 70 + n) for n in (1, 7, 3, 5, 2, 9)]   # short prompts, long outputs: the pool overflows while decoding
+    ref = plain_generate(cfg, w, ps[2], 40)
+    stop = ref[9]
+
+    def run(pipeline):
+        eng = Engine(str(folder), dtype="float32", block_size=PAGE_SIZES[name], num_blocks=8 if PAGE_SIZES[name] == 16 else 14,
+                     max_seqs=4, max_len=80, max_num_batched_tokens=24, cuda_graphs=graphs, pipeline=pipeline)
+        reqs = [eng.add_request(Request(p, max_new_tokens=40 if i != 3 else 5, eos_ids=(stop,) if i == 2 else (),
+                                        temperature=0.0 if i % 2 == 0 else 0.9, top_k=0 if i != 5 else 30, top_p=1.0 if i != 1 else 0.9,
+                                        seed=100 + i)) for i, p in enumerate(ps)]
+        steps = 0
+        while eng.has_work():
+            eng.step()
+            eng.cache.check_invariants()
+            steps += 1
+            assert steps < 2000
+        assert all(pool.num_free == pool.capacity for pool in eng.cache.pools) and eng.cache.num_free_slots() == 4
+        return [(r.output_ids, r.finish_reason) for r in reqs], eng.preemptions
+
+    plain_out, pre_a = run(False)
+    piped_out, pre_b = run(True)
+    assert piped_out == plain_out
+    assert plain_out[2][1] == "stop" and plain_out[2][0] == ref[:ref.index(stop)]
+    assert plain_out[0][0] == plain_generate(cfg, w, ps[0], 40)
+    assert pre_a > 0 and pre_b > 0   # the pool was small enough to force preemptions in both runs

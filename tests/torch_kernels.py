@@ -23,6 +23,10 @@ class TorchKernels:
     def embed(self, token_ids, table):
         return table[token_ids.long()].float()
 
+    def feed_tokens(self, token_ids, source_rows, previous_tokens):
+        take = source_rows >= 0
+        token_ids[take] = previous_tokens[source_rows[take].long()]
+
     def rope_tables(self, positions, inv_freq):
         ang = positions.float()[:, None] * inv_freq.float()[None, :]
         return ang.cos(), ang.sin()
