@@ -277,11 +277,19 @@ def main() -> int:
     with tempfile.TemporaryDirectory() as tmp:
         folder = write_random_model(model, Path(tmp) / "model", seed=0, store_dtype="bfloat16")
         sampler = ClockSampler()
-        main_pt = decode_point(folder, a.batch, a.steps if a.only != "prefill" else 3, a.warmup, torch, graphs, sampler)
+        if a.only == "prefill":  # for profiling the prompt step alone: no decode step runs before it
+            pre = prefill_point(folder, torch, graphs=graphs)
+            fl = flops_prefill(PREFILL_TOKENS) * a.layers / MODEL["num_hidden_layers"]
+            print(json.dumps({"prefill": {"value": round(PREFILL_TOKENS / (pre["ms"] * 1e-3), 1), "tokens": PREFILL_TOKENS,
+                                          "ms": round(pre["ms"], 3),
+                                          "frac": round(fl / (pre["ms"] * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)},
+                              "layers": a.layers, "cuda_graphs": graphs}))
+            return 0
+        main_pt = decode_point(folder, a.batch, a.steps, a.warmup, torch, graphs, sampler)
         clocks = sampler.clocks
         b1 = decode_point(folder, 1, min(a.steps, 256), a.warmup, torch, graphs) if a.only == "all" else None
         b64 = decode_point(folder, 64, min(a.steps, 128), a.warmup, torch, graphs) if a.only == "all" else None
-        pre = prefill_point(folder, torch, graphs=graphs) if a.only in ("all", "prefill") else None
+        pre = prefill_point(folder, torch, graphs=graphs) if a.only == "all" else None
         e2e = None if (a.skip_e2e or a.only != "all") else e2e_point(folder, a.batch, min(a.steps, 512), a.warmup, torch, graphs)
 
     fl = flops_prefill(PREFILL_TOKENS) * a.layers / MODEL["num_hidden_layers"]

@@ -285,7 +285,7 @@ static int launch_silu_mul(TI* gu, TO* out, int N, int I, int clear_in, cudaStre
         return 0;
     }
     const bool vec = I % 4 == 0 && ((uintptr_t)gu % 16 == 0) && ((uintptr_t)out % 16 == 0);
-    if (vec) return launch_kernel(silu_mul_kernel<TI, TO, 4>, dim3((I / 8 + 127) / 128, N), dim3(128), 0, s, gu, out, I, clear_in);
+    if (vec) return launch_kernel(silu_mul_kernel<TI, TO, 4>, dim3(((I + 7) / 8 + 127) / 128, N), dim3(128), 0, s, gu, out, I, clear_in);
     return launch_kernel(silu_mul_kernel<TI, TO, 1>, dim3((I + 127) / 128, N), dim3(128), 0, s, gu, out, I, clear_in);
 }
 
