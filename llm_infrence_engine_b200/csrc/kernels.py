@@ -66,6 +66,7 @@ class CudaKernels:
         self._attn_scratch: Optional[torch.Tensor] = None
         self._attn_counters: Optional[torch.Tensor] = None
         self.use_mma_attention = True
+        self.use_tc_attention = True   # prompt portions of head size 64: scores and outputs through tcgen05 and tensor memory
         self.cluster_merge = True      # decode attention: the key slices of a token form a cluster and merge in shared memory
         self.use_tc_gemm = True
         self.tc_max_rows = 128        # batches up to this many rows take the small-batch tensor-core product
@@ -82,7 +83,7 @@ class CudaKernels:
         self._error_flag: Optional[torch.Tensor] = None
         self.num_sms = torch.cuda.get_device_properties(0).multi_processor_count or NUM_SMS_FALLBACK
         for fn in ("llmie_embed", "llmie_feed_tokens", "llmie_rope_tables", "llmie_add_rmsnorm", "llmie_rope_kv_write", "llmie_silu_mul",
-                   "llmie_gemm_simt", "llmie_gemm_tc", "llmie_gemm_tc_norm", "llmie_gemm_tc_silu", "llmie_add_into", "llmie_attn_plan", "llmie_paged_attention_mma", "llmie_paged_attention_f32", "llmie_paged_attention_bf16", "llmie_argmax", "llmie_sample"):
+                   "llmie_gemm_simt", "llmie_gemm_tc", "llmie_gemm_tc_norm", "llmie_gemm_tc_silu", "llmie_add_into", "llmie_attn_plan", "llmie_paged_attention_mma", "llmie_paged_attention_tc", "llmie_paged_attention_f32", "llmie_paged_attention_bf16", "llmie_argmax", "llmie_sample"):
             getattr(self.lib, fn).restype = ctypes.c_int
         # kernels of a step overlap their set-up with the tail of the kernel before (programmatic dependent launch)
         self.lib.llmie_set_pdl(0 if os.environ.get("LLMIE_PDL", "1") == "0" else 1)
@@ -331,13 +332,19 @@ class CudaKernels:
         self._check(rc, "linear_tc")
         return out
 
+    def _errors(self, device) -> torch.Tensor:
+        if self._error_flag is None:
+            self._error_flag = torch.zeros(1, dtype=torch.int32, device=device)
+        return self._error_flag
+
     def check_device_errors(self) -> None:
         """Raise if a kernel gave up on a bounded wait since the last check (reads one integer back)."""
         if self._error_flag is not None:
             code = int(self._error_flag.item())
             if code:
                 self._error_flag.zero_()
-                raise KernelError(f"a tensor-core GEMM block gave up waiting on a barrier (stage {code}); its output is not valid")
+                raise KernelError(f"a block of a tcgen05 kernel gave up waiting on a barrier (code {code}: 1-4 matrix product, "
+                                  "11-16 attention); its output is not valid")
 
     def rope_kv_write(self, qkv, bias, cos, sin, slot_mapping, k_pool, v_pool, num_heads, num_kv_heads, head_dim, page_size,
                       write_kv=True, out_dtype=None):
@@ -425,23 +432,50 @@ class CudaKernels:
             self.launches += 1
         return out
 
+    def _tiles(self, batch, per_tile: int, device):
+        """(number of tiles, device table [tiles, 2] of (first token, tokens)) for tiles of up to ``per_tile`` tokens of one request."""
+        tiles = sum(-(-n // per_tile) for n in batch.seq_lens)
+        key = ("attention tiles", per_tile)
+        if key not in batch._tables:
+            info = torch.empty((tiles, 2), dtype=torch.int32, device=device)
+            self._check(self.lib.llmie_attn_plan(_ptr(batch.seq_starts_dev), len(batch.seq_lens), per_tile, _ptr(info), tiles,
+                                                 self._stream()), "attention plan")
+            batch._tables[key] = info
+        return tiles, batch._tables[key]
+
+    def _attention_tc(self, qkv, k_pool, v_pool, block_table, token_seq, positions, out, num_heads, num_kv_heads, head_dim,
+                      page_size, scale, window, span, batch, num_splits):
+        """The tcgen05 kernel for prompt portions, if it takes this case: returns ``out`` or None."""
+        group = num_heads // num_kv_heads
+        if not (self.use_tc_attention and head_dim == 64 and batch.max_seq_len > 1 and group <= 128 and page_size % 8 == 0
+                and (64 % page_size == 0 or page_size % 64 == 0) and num_splits in (None, 1)):
+            return None
+        tiles = sum(-(-n // (128 // group)) for n in batch.seq_lens)
+        if num_splits is None and min(self.num_sms // max(1, tiles * num_kv_heads), -(-span // 64) // 8) > 1:
+            return None  # few tiles with long key ranges: the kernel that cuts the keys of a tile into slices fills the device better
+        tiles, tile_info = self._tiles(batch, 128 // group, qkv.device)
+        self._check(self.lib.llmie_paged_attention_tc(
+            _ptr(qkv), qkv.shape[1], _ptr(k_pool), _ptr(v_pool), ctypes.c_longlong(k_pool.shape[0]), _ptr(block_table),
+            block_table.shape[1], _ptr(token_seq), _ptr(positions), _ptr(tile_info), tiles, _ptr(out), num_heads, num_kv_heads,
+            head_dim, page_size, ctypes.c_float(scale), int(window), _ptr(self._errors(qkv.device)), self._stream()),
+            "paged_attention (tcgen05)")
+        return out
+
     def _attention_mma(self, qkv, k_pool, v_pool, block_table, token_seq, positions, out, num_heads, num_kv_heads, head_dim,
                        page_size, scale, window, span, batch, num_splits):
         group = num_heads // num_kv_heads
         decode = batch.max_seq_len == 1
         N = qkv.shape[0]
+        if not decode:
+            done = self._attention_tc(qkv, k_pool, v_pool, block_table, token_seq, positions, out, num_heads, num_kv_heads, head_dim,
+                                      page_size, scale, window, span, batch, num_splits)
+            if done is not None:
+                return done
         if decode:
             tiles, tile_info, rows, chunk = N, None, 16, (32 if head_dim == 64 else 16)
         else:
-            per_tile = max(1, 64 // group)
-            tiles = sum(-(-n // per_tile) for n in batch.seq_lens)
-            key = ("attention tiles", per_tile)
-            if key not in batch._tables:
-                info = torch.empty((tiles, 2), dtype=torch.int32, device=qkv.device)
-                self._check(self.lib.llmie_attn_plan(_ptr(batch.seq_starts_dev), len(batch.seq_lens), per_tile, _ptr(info), tiles,
-                                                     self._stream()), "attention plan")
-                batch._tables[key] = info
-            tile_info, rows, chunk = batch._tables[key], 64, 64
+            tiles, tile_info = self._tiles(batch, max(1, 64 // group), qkv.device)
+            rows, chunk = 64, 64
         chunks = max(1, -(-span // chunk))
         explicit = num_splits
         if num_splits is None:

@@ -276,6 +276,43 @@ def test_paged_attention_tensor_cores(K, nq, nkv, d, ps, lens, qlens, window, sp
         close(got, want, 1e-2)
 
 
+@pytest.mark.parametrize("nq,nkv,ps,lens,qlens,window", [
+    (14, 2, 16, [2048], [2048], 0),                       # the bench's prompt: 18 tokens x 7 heads per tile
+    (14, 2, 16, [300, 77, 500], [300, 1, 37], 0),        # a decode token and a late portion beside a prompt
+    (8, 8, 8, [700, 130], [700, 2], 0),                   # no grouping: 128 tokens per tile; pages of 8
+    (16, 1, 32, [257, 90], [257, 64], 0),                 # 16 heads on one key/value head
+    (6, 3, 64, [200, 1000], [200, 520], 48),              # window; a page is a whole chunk
+    (12, 4, 128, [640], [400], 0),                        # pages larger than a chunk
+    (5, 5, 16, [333], [333], 100),                        # window longer than a chunk
+    (3, 1, 16, [4500], [4500], 0),
+])
+def test_paged_attention_tcgen05(K, monkeypatch, nq, nkv, ps, lens, qlens, window):
+    """Prompt portions of head size 64 through tcgen05 and tensor memory. Every slot of the cache that no visible key
+    occupies holds NaN (free pages, the null page, the rest of each request's last page): nothing of it may reach a result."""
+    d = 64
+    taken = []
+    inner = K._attention_tc
+    monkeypatch.setattr(K, "_attention_tc", lambda *a: (taken.append(inner(*a)), taken[-1])[1])
+    for spike in (False, True):
+        qkv, kp, vp, table, tseq, pos = _attention_case(torch.bfloat16, nq, nkv, d, ps, lens, qlens, window, 21, spike)
+        used = torch.zeros(kp.shape[0], ps, dtype=torch.bool)
+        for r, L in enumerate(lens):
+            for i in range(L):
+                used[int(table[r, i // ps]), i % ps] = True
+        kp_nan, vp_nan = kp.clone(), vp.clone()
+        kp_nan.permute(0, 2, 1, 3)[~used] = float("nan")
+        vp_nan.permute(0, 2, 1, 3)[~used] = float("nan")
+        scale = 1.0 / math.sqrt(d)
+        want = REF.paged_attention(qkv, kp, vp, table, tseq, pos, nq, nkv, d, ps, scale, window, max(lens))
+        for _ in range(2):
+            got = K.paged_attention(qkv.cuda(), kp_nan.cuda(), vp_nan.cuda(), table.cuda(), tseq.cuda(), pos.cuda(), nq, nkv, d, ps,
+                                    scale, window, max(lens), batch=_Batch(qlens))
+            K.check_device_errors()
+            assert not torch.isnan(got).any()
+            close(got, want, 1e-2)
+    assert len(taken) == 4 and all(t is not None for t in taken)
+
+
 @pytest.mark.parametrize("M,N,K_,splits,accumulate", [
     (1, 128, 64, 1, False),
     (8, 1152, 896, 1, False),
