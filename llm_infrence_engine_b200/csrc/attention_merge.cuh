@@ -1,0 +1,83 @@
+// The end of an attention tile, shared by the kernels that cut a tile's keys into slices.
+#pragma once
+
+#include "common.cuh"
+
+namespace {
+
+// `Params` has: out [tokens][nq * D] bfloat16, part_o [tiles][nkv][splits][ROWS][D] and part_ml [tiles][nkv][splits][ROWS][2]
+// float32 scratch, counters [tiles * nkv] (zero between launches), nq, nkv, num_splits.
+// The block's finished rows are in shared memory as (max, sum, output); write them out, or, with
+// several key slices, store the partial and let the last block of the tile merge all slices.
+template <int D, int ROWS, int THREADS, typename Params>
+__device__ __forceinline__ void finish_tile(const Params& p, const float* row_m, const float* row_l, const float* row_o, int tile,
+                                            int kvh, int split, int n0, int nrows, int G, int* flag_smem) {
+    const int tid = threadIdx.x;
+    if (p.num_splits == 1) {
+        for (int i = tid; i < nrows * D; i += THREADS) {
+            const int r = i / D, dim = i % D;
+            const float L = row_l[r];
+            const float val = L > 0.f ? row_o[r * D + dim] / L : 0.f;
+            p.out[(size_t)(n0 + r / G) * p.nq * D + (size_t)(kvh * G + r % G) * D + dim] = __float2bfloat16_rn(val);
+        }
+        return;
+    }
+    const size_t base = ((size_t)tile * p.nkv + kvh) * p.num_splits;
+    float* po = p.part_o + (base + split) * ROWS * D;
+    float* pml = p.part_ml + (base + split) * ROWS * 2;
+    for (int i = tid * 4; i < nrows * D; i += THREADS * 4) *reinterpret_cast<float4*>(po + i) = *reinterpret_cast<const float4*>(row_o + i);
+    for (int r = tid; r < nrows; r += THREADS) { pml[2 * r] = row_m[r]; pml[2 * r + 1] = row_l[r]; }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        const int prev = atomicAdd(p.counters + tile * p.nkv + kvh, 1);
+        *flag_smem = prev == p.num_splits - 1;
+    }
+    __syncthreads();
+    if (!*flag_smem) return;
+    __threadfence();
+    // Last block of the tile: first the slices' (max, sum) pairs become per-row weights in shared memory (the
+    // block's own row_m / row_l / row_o are not needed any more), then every output element is one weighted sum
+    // whose loads do not depend on each other.
+    float* wgt = const_cast<float*>(row_o);                 // [num_splits][nrows] weights e^(m_s - M) / L
+    float* mx = const_cast<float*>(row_m);                  // [nrows] overall maximum
+    for (int r = tid; r < nrows; r += THREADS) {
+        float M = -INFINITY;
+        for (int s = 0; s < p.num_splits; ++s) M = fmaxf(M, __ldcg(p.part_ml + (base + s) * ROWS * 2 + 2 * r));
+        mx[r] = M;
+    }
+    __syncthreads();
+    for (int i = tid; i < nrows * p.num_splits; i += THREADS) {
+        const int s = i / nrows, r = i % nrows;
+        const float M = mx[r];
+        wgt[i] = M > -INFINITY ? exp2f(__ldcg(p.part_ml + (base + s) * ROWS * 2 + 2 * r) - M) : 0.f;
+    }
+    __syncthreads();
+    for (int r = tid; r < nrows; r += THREADS) {
+        float L = 0.f;
+        for (int s = 0; s < p.num_splits; ++s) L = fmaf(__ldcg(p.part_ml + (base + s) * ROWS * 2 + 2 * r + 1), wgt[s * nrows + r], L);
+        const_cast<float*>(row_l)[r] = L > 0.f ? 1.f / L : 0.f;
+    }
+    __syncthreads();
+    // four neighbouring outputs of a row per thread and step (16-byte loads that do not depend on each other)
+#pragma unroll 2
+    for (int i = tid * 4; i < nrows * D; i += THREADS * 4) {
+        const int r = i / D, dim = i % D;
+        float4 O = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+        for (int s = 0; s < p.num_splits; ++s) {
+            const float4 a = __ldcg(reinterpret_cast<const float4*>(p.part_o + (base + s) * ROWS * D + i));
+            const float w = wgt[s * nrows + r];
+            O.x = fmaf(a.x, w, O.x); O.y = fmaf(a.y, w, O.y); O.z = fmaf(a.z, w, O.z); O.w = fmaf(a.w, w, O.w);
+        }
+        const float inv = row_l[r];
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(O.x * inv, O.y * inv), hi = __floats2bfloat162_rn(O.z * inv, O.w * inv);
+        uint2 packed;
+        packed.x = *reinterpret_cast<const uint32_t*>(&lo);
+        packed.y = *reinterpret_cast<const uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(p.out + (size_t)(n0 + r / G) * p.nq * D + (size_t)(kvh * G + r % G) * D + dim) = packed;
+    }
+    if (tid == 0) p.counters[tile * p.nkv + kvh] = 0;  // ready for the next launch
+}
+
+}  // namespace

@@ -20,6 +20,7 @@
 #include <math.h>
 
 #include "common.cuh"
+#include "attention_merge.cuh"
 
 namespace {
 
@@ -192,75 +193,6 @@ __device__ __forceinline__ void attend_chunk(const uint32_t (&qa)[D / 16][4], co
     }
 }
 
-// The block's finished rows are in shared memory as (max, sum, output); write them out, or, with
-// several key slices, store the partial and let the last block of the tile merge all slices.
-template <int D, int ROWS, int THREADS>
-__device__ __forceinline__ void finish_tile(const Params& p, const float* row_m, const float* row_l, const float* row_o, int tile,
-                                            int kvh, int split, int n0, int nrows, int G, int* flag_smem) {
-    const int tid = threadIdx.x;
-    if (p.num_splits == 1) {
-        for (int i = tid; i < nrows * D; i += THREADS) {
-            const int r = i / D, dim = i % D;
-            const float L = row_l[r];
-            const float val = L > 0.f ? row_o[r * D + dim] / L : 0.f;
-            p.out[(size_t)(n0 + r / G) * p.nq * D + (size_t)(kvh * G + r % G) * D + dim] = __float2bfloat16_rn(val);
-        }
-        return;
-    }
-    const size_t base = ((size_t)tile * p.nkv + kvh) * p.num_splits;
-    float* po = p.part_o + (base + split) * ROWS * D;
-    float* pml = p.part_ml + (base + split) * ROWS * 2;
-    for (int i = tid; i < nrows * D; i += THREADS) po[i] = row_o[i];
-    for (int r = tid; r < nrows; r += THREADS) { pml[2 * r] = row_m[r]; pml[2 * r + 1] = row_l[r]; }
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) {
-        const int prev = atomicAdd(p.counters + tile * p.nkv + kvh, 1);
-        *flag_smem = prev == p.num_splits - 1;
-    }
-    __syncthreads();
-    if (!*flag_smem) return;
-    __threadfence();
-    // Last block of the tile: first the slices' (max, sum) pairs become per-row weights in shared memory (the
-    // block's own row_m / row_l / row_o are not needed any more), then every output element is one weighted sum
-    // whose loads do not depend on each other.
-    float* wgt = const_cast<float*>(row_o);                 // [num_splits][nrows] weights e^(m_s - M) / L
-    float* mx = const_cast<float*>(row_m);                  // [nrows] overall maximum
-    for (int r = tid; r < nrows; r += THREADS) {
-        float M = -INFINITY;
-        for (int s = 0; s < p.num_splits; ++s) M = fmaxf(M, __ldcg(p.part_ml + (base + s) * ROWS * 2 + 2 * r));
-        mx[r] = M;
-    }
-    __syncthreads();
-    for (int i = tid; i < nrows * p.num_splits; i += THREADS) {
-        const int s = i / nrows, r = i % nrows;
-        const float M = mx[r];
-        wgt[i] = M > -INFINITY ? exp2f(__ldcg(p.part_ml + (base + s) * ROWS * 2 + 2 * r) - M) : 0.f;
-    }
-    __syncthreads();
-    for (int r = tid; r < nrows; r += THREADS) {
-        float L = 0.f;
-        for (int s = 0; s < p.num_splits; ++s) L = fmaf(__ldcg(p.part_ml + (base + s) * ROWS * 2 + 2 * r + 1), wgt[s * nrows + r], L);
-        const_cast<float*>(row_l)[r] = L > 0.f ? 1.f / L : 0.f;
-    }
-    __syncthreads();
-    for (int i = tid; i < nrows * D; i += THREADS) {
-        const int r = i / D, dim = i % D;
-        float O = 0.f;
-        int s = 0;
-        for (; s + 4 <= p.num_splits; s += 4) {
-            const float a0 = __ldcg(p.part_o + (base + s) * ROWS * D + i), a1 = __ldcg(p.part_o + (base + s + 1) * ROWS * D + i);
-            const float a2 = __ldcg(p.part_o + (base + s + 2) * ROWS * D + i), a3 = __ldcg(p.part_o + (base + s + 3) * ROWS * D + i);
-            O = fmaf(a0, wgt[s * nrows + r], O);
-            O = fmaf(a1, wgt[(s + 1) * nrows + r], O);
-            O = fmaf(a2, wgt[(s + 2) * nrows + r], O);
-            O = fmaf(a3, wgt[(s + 3) * nrows + r], O);
-        }
-        for (; s < p.num_splits; ++s) O = fmaf(__ldcg(p.part_o + (base + s) * ROWS * D + i), wgt[s * nrows + r], O);
-        p.out[(size_t)(n0 + r / G) * p.nq * D + (size_t)(kvh * G + r % G) * D + dim] = __float2bfloat16_rn(O * row_l[r]);
-    }
-    if (tid == 0) p.counters[tile * p.nkv + kvh] = 0;  // ready for the next launch
-}
 
 // ---------------------------------------------------------------------------------------------- decode
 template <int D, int BN, int STAGES, int DW>

@@ -27,6 +27,7 @@
 // Every wait on an mbarrier is bounded: after SPIN_LIMIT polls the block records an error, every role leaves its
 // loop, the copies in flight are given (bounded) time to land, tensor memory is freed and the block returns.
 #include "common.cuh"
+#include "attention_merge.cuh"
 #include "tcgen05.cuh"
 
 namespace {
@@ -43,6 +44,10 @@ struct TcParams {
     const int* positions;   // [tokens]
     const int* tile_info;   // [tiles][2] = (first token, tokens)
     bf16* out;              // [tokens][nq * D]
+    float* part_o;          // [tiles][nkv][splits][BM][D]   scratch for tiles whose keys are cut into slices
+    float* part_ml;         // [tiles][nkv][splits][BM][2]
+    int* counters;          // [tiles * nkv], zero between launches
+    int num_splits;
     int* error_flag;
     int q_stride, max_blocks, nq, nkv, page_size, window;
     int box_rows;           // rows per TMA box: min(page_size, BN)
@@ -103,7 +108,8 @@ __global__ void __launch_bounds__(THREADS, 2) attn_tc_prefill_kernel(const __gri
     // tile down; all blocks are resident at once (two to an SM), the first `first_round` one to an SM, the others beside
     // them in the same order of SMs: those take the list from its short end, so that every SM's two blocks add up alike.
     const int total = gridDim.x, b = blockIdx.x;
-    const int item = b < p.first_round ? b : total - 1 - (b - p.first_round);
+    const int work = b < p.first_round ? b : total - 1 - (b - p.first_round);
+    const int split = work % p.num_splits, item = work / p.num_splits;
     const int tile = p.num_tiles - 1 - item / p.nkv;
     const int kvh = item % p.nkv;
 
@@ -145,7 +151,11 @@ __global__ void __launch_bounds__(THREADS, 2) attn_tc_prefill_kernel(const __gri
     const int hi = pos0 + ntok;  // one past the last visible key
     const int lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
     const int lo_al = lo / p.box_rows * p.box_rows;  // chunks start where a TMA box starts
-    const int chunks = ntok > 0 ? (hi - lo_al + BN - 1) / BN : 0;
+    // this block's slice of the tile's chunks: [chunk0, chunk0 + chunks), empty for the later slices of a short tile
+    const int all_chunks = ntok > 0 ? (hi - lo_al + BN - 1) / BN : 0;
+    const int per_split = (all_chunks + p.num_splits - 1) / p.num_splits;
+    const int chunk0 = split * per_split;
+    const int chunks = max(0, min(all_chunks, chunk0 + per_split) - chunk0);
     const int* table = p.block_table + (size_t)(ntok > 0 ? p.token_seq[n0] : 0) * p.max_blocks;
 
     if (warp == 4) {
@@ -155,7 +165,7 @@ __global__ void __launch_bounds__(THREADS, 2) attn_tc_prefill_kernel(const __gri
         auto box_row = [&](int c) {
             int row = 0;
             if (lane < boxes) {
-                const int key = lo_al + c * BN + lane * p.box_rows;
+                const int key = lo_al + (chunk0 + c) * BN + lane * p.box_rows;
                 const int page = key < hi ? table[key / p.page_size] : 0;  // behind the sequence: any page, its keys are masked
                 row = (page * p.nkv + kvh) * p.page_size + key % p.page_size;
             }
@@ -289,7 +299,7 @@ __global__ void __launch_bounds__(THREADS, 2) attn_tc_prefill_kernel(const __gri
 #pragma unroll
             for (int j = 0; j < BN; j += 16) tmem_ld16(lane_base + (c & 1) * BN + j, s + j);
             asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-            const int key0 = lo_al + c * BN;
+            const int key0 = lo_al + (chunk0 + c) * BN;
             // A chunk that every row of the tile sees in full needs no mask arithmetic (rows beyond the tile have zero
             // queries and collect numbers nobody reads). The scale is positive: the maximum is taken over the raw scores.
             const bool interior = key0 >= lo && key0 + BN - 1 <= pos0 && (p.window <= 0 || key0 > hi - 1 - p.window);
@@ -351,16 +361,28 @@ __global__ void __launch_bounds__(THREADS, 2) attn_tc_prefill_kernel(const __gri
             corr_before = corr;
         }
         if (ok && chunks > 0) ok = take_outputs(chunks - 1, corr_before);
-        if (ok && row_ok) {
-            const float inv = l > 0.f ? 1.f / l : 0.f;
-            uint4* dst = reinterpret_cast<uint4*>(p.out + (size_t)(n0 + tok) * p.nq * D + (size_t)(kvh * G + row % G) * D);
+        if (ok && p.num_splits == 1) {
+            if (row_ok) {
+                const float inv = l > 0.f ? 1.f / l : 0.f;
+                uint4* dst = reinterpret_cast<uint4*>(p.out + (size_t)(n0 + tok) * p.nq * D + (size_t)(kvh * G + row % G) * D);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                uint4 packed;
-                packed.x = pack_bf16x2(o[8 * j] * inv, o[8 * j + 1] * inv); packed.y = pack_bf16x2(o[8 * j + 2] * inv, o[8 * j + 3] * inv);
-                packed.z = pack_bf16x2(o[8 * j + 4] * inv, o[8 * j + 5] * inv); packed.w = pack_bf16x2(o[8 * j + 6] * inv, o[8 * j + 7] * inv);
-                dst[j] = packed;
+                for (int j = 0; j < 8; ++j) {
+                    uint4 packed;
+                    packed.x = pack_bf16x2(o[8 * j] * inv, o[8 * j + 1] * inv); packed.y = pack_bf16x2(o[8 * j + 2] * inv, o[8 * j + 3] * inv);
+                    packed.z = pack_bf16x2(o[8 * j + 4] * inv, o[8 * j + 5] * inv); packed.w = pack_bf16x2(o[8 * j + 6] * inv, o[8 * j + 7] * inv);
+                    dst[j] = packed;
+                }
             }
+        } else if (ok) {
+            // one slice of several: (max, sum, outputs) of the row go to shared memory (every product has been waited for and
+            // no copy is in flight: the tiles' space is free), from where the whole block hands them on below
+            float* fm = reinterpret_cast<float*>(p_s);
+            float* fl = fm + BM;
+            float* fo = fl + BM;
+            fm[row] = m;
+            fl[row] = l;
+#pragma unroll
+            for (int i = 0; i < D; i += 4) *reinterpret_cast<float4*>(fo + row * D + i) = make_float4(o[i], o[i + 1], o[i + 2], o[i + 3]);
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
@@ -380,25 +402,34 @@ __global__ void __launch_bounds__(THREADS, 2) attn_tc_prefill_kernel(const __gri
     }
     __syncthreads();
     if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "n"(TMEM_COLS) : "memory");
+    if (p.num_splits > 1 && !*abort_flag) {
+        float* fm = reinterpret_cast<float*>(p_s);
+        __shared__ int last_flag;
+        finish_tile<D, BM, THREADS>(p, fm, fm + BM, fm + 2 * BM, tile, kvh, split, n0, nrows, G, &last_flag);
+    }
 }
 
 }  // namespace
 
 // Attention of prompt portions over the paged cache on the tcgen05 tensor cores: head size 64, bfloat16, up to 128 rows
-// (tokens x heads of a group) per tile as listed in tile_info, every tile's whole key range in one block. page_size must be
-// a multiple of 8 that divides 64 or is a multiple of 64. Pools: [pages][nkv][page_size][64].
+// (tokens x heads of a group) per tile as listed in tile_info. page_size must be a multiple of 8 that divides 64 or is a
+// multiple of 64. Pools: [pages][nkv][page_size][64]. With num_splits > 1 the keys of every tile are cut into that many slices,
+// one block each, which meet in scratch_o [tiles * nkv * splits * 128 * 64] and scratch_ml [tiles * nkv * splits * 128 * 2]
+// floats; the block that finishes a tile last (counters [tiles * nkv], zero before and after) merges them.
 LLMIE_API int llmie_paged_attention_tc(const bf16* q, int q_stride, const bf16* k_pool, const bf16* v_pool, long long pool_pages,
                                        const int* block_table, int max_blocks, const int* token_seq, const int* positions,
-                                       const int* tile_info, int num_tiles, bf16* out, int nq, int nkv, int d, int page_size, float scale,
-                                       int window, int* error_flag, cudaStream_t s) {
+                                       const int* tile_info, int num_tiles, bf16* out, float* scratch_o, float* scratch_ml, int* counters,
+                                       int nq, int nkv, int d, int page_size, float scale, int window, int num_splits, int* error_flag,
+                                       cudaStream_t s) {
     if (num_tiles <= 0) return 0;
     if (d != D || nkv <= 0 || nq % nkv || nq / nkv > BM || page_size <= 0 || page_size % 8 || q_stride % 8 ||
         !(BN % page_size == 0 || page_size % BN == 0) || !tile_info || !error_flag || pool_pages <= 0 || ((uintptr_t)q & 15) ||
-        ((uintptr_t)out & 15) || pool_pages * nkv * page_size > 0x7fffffffLL)
+        ((uintptr_t)out & 15) || pool_pages * nkv * page_size > 0x7fffffffLL || num_splits < 1 || num_splits > 16 ||
+        (num_splits > 1 && (!scratch_o || !scratch_ml || !counters)))
         return LLMIE_ERR_BAD_ARGUMENT;
     TcParams p;
     p.q = q; p.block_table = block_table; p.token_seq = token_seq; p.positions = positions; p.tile_info = tile_info; p.out = out;
-    p.error_flag = error_flag; p.q_stride = q_stride; p.max_blocks = max_blocks; p.nq = nq; p.nkv = nkv; p.page_size = page_size;
+    p.error_flag = error_flag; p.part_o = scratch_o; p.part_ml = scratch_ml; p.counters = counters; p.num_splits = num_splits; p.q_stride = q_stride; p.max_blocks = max_blocks; p.nq = nq; p.nkv = nkv; p.page_size = page_size;
     p.window = window; p.box_rows = page_size < BN ? page_size : BN; p.scale_log2 = scale * LOG2E;
     CUtensorMap mk, mv;
     const int rows = (int)(pool_pages * nkv * page_size);
@@ -418,7 +449,7 @@ LLMIE_API int llmie_paged_attention_tc(const bf16* q, int q_stride, const bf16* 
         int dev = 0;
         if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return LLMIE_ERR_BAD_ARGUMENT;
     }
-    const long long blocks = (long long)num_tiles * nkv;
+    const long long blocks = (long long)num_tiles * nkv * num_splits;
     if (blocks > 0x7fffffffLL) return LLMIE_ERR_BAD_ARGUMENT;
     p.num_tiles = num_tiles;
     p.first_round = blocks < num_sms ? (int)blocks : num_sms;

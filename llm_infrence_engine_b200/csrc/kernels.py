@@ -67,6 +67,7 @@ class CudaKernels:
         self._attn_counters: Optional[torch.Tensor] = None
         self.use_mma_attention = True
         self.use_tc_attention = True   # prompt portions of head size 64: scores and outputs through tcgen05 and tensor memory
+        self.tc_attention_max_splits = 16
         self.cluster_merge = True      # decode attention: the key slices of a token form a cluster and merge in shared memory
         self.use_tc_gemm = True
         self.tc_max_rows = 128        # batches up to this many rows take the small-batch tensor-core product
@@ -448,17 +449,31 @@ class CudaKernels:
         """The tcgen05 kernel for prompt portions, if it takes this case: returns ``out`` or None."""
         group = num_heads // num_kv_heads
         if not (self.use_tc_attention and head_dim == 64 and batch.max_seq_len > 1 and group <= 128 and page_size % 8 == 0
-                and (64 % page_size == 0 or page_size % 64 == 0) and num_splits in (None, 1)):
+                and (64 % page_size == 0 or page_size % 64 == 0) and (num_splits is None or 1 <= num_splits <= 16)):
             return None
         tiles = sum(-(-n // (128 // group)) for n in batch.seq_lens)
-        if num_splits is None and min(self.num_sms // max(1, tiles * num_kv_heads), -(-span // 64) // 8) > 1:
-            return None  # few tiles with long key ranges: the kernel that cuts the keys of a tile into slices fills the device better
+        blocks, chunks = max(1, tiles * num_kv_heads), -(-span // 64)
+        if num_splits is None:
+            # A tile's chunks run one after the other, about a microsecond each. While the blocks would leave SMs idle, the
+            # keys of every tile are cut into slices that run side by side on SMs of their own and meet in scratch memory
+            # (measured: slices that have to share SMs cost more than they bring).
+            num_splits = max(1, min(self.tc_attention_max_splits, chunks // 8, self.num_sms // blocks))
         tiles, tile_info = self._tiles(batch, 128 // group, qkv.device)
+        scratch_o = scratch_ml = counters = None
+        if num_splits > 1:
+            cells = tiles * num_kv_heads * num_splits * 128
+            buf = self._scratch(cells * (head_dim + 2), qkv.device)
+            scratch_o, scratch_ml = buf, buf[cells * head_dim:]
+            if tiles * num_kv_heads > (1 << 20):
+                return None
+            if self._attn_counters is None or self._attn_counters.device != qkv.device:
+                self._attn_counters = torch.zeros(1 << 20, dtype=torch.int32, device=qkv.device)
+            counters = self._attn_counters
         self._check(self.lib.llmie_paged_attention_tc(
             _ptr(qkv), qkv.shape[1], _ptr(k_pool), _ptr(v_pool), ctypes.c_longlong(k_pool.shape[0]), _ptr(block_table),
-            block_table.shape[1], _ptr(token_seq), _ptr(positions), _ptr(tile_info), tiles, _ptr(out), num_heads, num_kv_heads,
-            head_dim, page_size, ctypes.c_float(scale), int(window), _ptr(self._errors(qkv.device)), self._stream()),
-            "paged_attention (tcgen05)")
+            block_table.shape[1], _ptr(token_seq), _ptr(positions), _ptr(tile_info), tiles, _ptr(out), _ptr(scratch_o), _ptr(scratch_ml),
+            _ptr(counters), num_heads, num_kv_heads, head_dim, page_size, ctypes.c_float(scale), int(window), int(num_splits),
+            _ptr(self._errors(qkv.device)), self._stream()), "paged_attention (tcgen05)")
         return out
 
     def _attention_mma(self, qkv, k_pool, v_pool, block_table, token_seq, positions, out, num_heads, num_kv_heads, head_dim,

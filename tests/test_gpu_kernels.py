@@ -278,6 +278,8 @@ def test_paged_attention_tensor_cores(K, nq, nkv, d, ps, lens, qlens, window, sp
 
 @pytest.mark.parametrize("nq,nkv,ps,lens,qlens,window", [
     (14, 2, 16, [2048], [2048], 0),                       # the bench's prompt: 18 tokens x 7 heads per tile
+    (14, 2, 16, [3000], [40], 0),                         # a short portion far into a long request: few tiles, their keys in slices
+    (4, 1, 16, [1500, 700], [100, 5], 0),                 # slices, and a tile whose later slices are empty
     (14, 2, 16, [300, 77, 500], [300, 1, 37], 0),        # a decode token and a late portion beside a prompt
     (8, 8, 8, [700, 130], [700, 2], 0),                   # no grouping: 128 tokens per tile; pages of 8
     (16, 1, 32, [257, 90], [257, 64], 0),                 # 16 heads on one key/value head
@@ -311,6 +313,7 @@ def test_paged_attention_tcgen05(K, monkeypatch, nq, nkv, ps, lens, qlens, windo
             assert not torch.isnan(got).any()
             close(got, want, 1e-2)
     assert len(taken) == 4 and all(t is not None for t in taken)
+    assert K._attn_counters is None or K._attn_counters.abs().sum().item() == 0  # the slice counters are back at zero
 
 
 @pytest.mark.parametrize("M,N,K_,splits,accumulate", [
