@@ -19,14 +19,6 @@
 // the whole memory system; the partial sums meet in the float32 output by atomic addition, which is
 // also how a projection adds itself into the residual stream without a separate kernel.
 //
-// Where the token rows come from (x_mode):
-//   0  a bfloat16 matrix, fetched by TMA like the weights
-//   1  the float32 residual stream, RMS-normalised on the way in: warps 2 and 3 compute 1/rms of the block's
-//      rows once, then write each stage's tile as bf16(weight[k] * bf16(x[m][k] / rms[m])) straight into the
-//      swizzled shared-memory layout the tensor core reads (the norm kernel and its round trip disappear)
-//   2  a float32 [rows, 2 I] gate/up accumulation: the tile is bf16(silu(gate) * up); the block that reads a
-//      slice last (a counter per slice) sets it back to zero for the next product that accumulates there
-//
 // Every wait on an mbarrier is bounded: after SPIN_LIMIT polls the block records an error in
 // `error_flag`, stops issuing work, lets the copies it started land (again bounded), frees its tensor
 // memory and returns. The host reads the flag and raises.
@@ -36,26 +28,11 @@
 namespace {
 
 constexpr int BM = 128, BK = 64, STAGES = 4, UMMA_K = 16;
-struct XSource {
-    int mode;              // 0 TMA, 1 normalised residual, 2 silu(gate) * up
-    float* src;            // mode 1: residual [M, K]; mode 2: gate/up accumulation [M, 2 K]
-    int ld;                // row stride of src in floats
-    const float* norm_w;   // mode 1: weight [K]
-    float eps;             // mode 1
-    int* counters;         // mode 2: one per (row tile, K slice), zero between launches
-};
 
-__device__ __forceinline__ void named_sync_64() { asm volatile("bar.sync 1, 64;\n" ::: "memory"); }
-
-__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
-    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-    return *reinterpret_cast<const uint32_t*>(&v);
-}
-
-template <int TN, int XMODE>
+template <int TN>
 __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                                                       float* __restrict__ out, int ldo, int M, int N, int K, int kb_per_split,
-                                                      int accumulate, int* error_flag, const XSource xs) {
+                                                      int accumulate, int* error_flag) {
     constexpr int W_BYTES = BM * BK * 2, X_BYTES = TN * BK * 2, STAGE_BYTES = W_BYTES + X_BYTES;
     constexpr int COLS = TN < 32 ? 32 : TN;  // tensor-memory columns: a power of two, at least 32
     extern __shared__ unsigned char raw[];
@@ -66,7 +43,6 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     volatile int* issued = abort_flag + 1;
-    float* rstd = reinterpret_cast<float*>(const_cast<int*>(issued) + 1);  // [3 TN], mode 1
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n0 = blockIdx.x * BM, m0 = blockIdx.y * TN;
@@ -75,7 +51,7 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
     const int iters = kb1 - kb0;
 
     if (tid == 0) {
-        for (int s = 0; s < STAGES; ++s) { mbar_init(full + s, XMODE == 0 ? 1 : 3); mbar_init(empty + s, 1); }
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, 1); }
         mbar_init(accum, 1);
         *abort_flag = 0;
         *issued = 0;
@@ -98,22 +74,21 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
         // The weights do not depend on the kernel before this one: the first stages' weight tiles are on their way
         // before the wait; the token tiles, which that kernel wrote, follow after it.
         const int early = min(iters, STAGES);
-        constexpr uint32_t tx = XMODE == 0 ? STAGE_BYTES : W_BYTES;
+        constexpr uint32_t tx = STAGE_BYTES;
         for (int it = 0; it < early; ++it) {
             mbar_expect_tx(full + it, tx);
             tma_load_2d(tiles + it * STAGE_BYTES, &tmap_w, (kb0 + it) * BK, n0, full + it);
             *issued = it + 1;
         }
         pdl_wait();
-        if constexpr (XMODE == 0)
-            for (int it = 0; it < early; ++it) tma_load_2d(tiles + it * STAGE_BYTES + W_BYTES, &tmap_x, (kb0 + it) * BK, m0, full + it);
+        for (int it = 0; it < early; ++it) tma_load_2d(tiles + it * STAGE_BYTES + W_BYTES, &tmap_x, (kb0 + it) * BK, m0, full + it);
         for (int it = early; it < iters; ++it) {
             const int s = it % STAGES;
             if (!mbar_wait(empty + s, ((it / STAGES) & 1) ^ 1, abort_flag, error_flag, 1)) break;
             unsigned char* st = tiles + s * STAGE_BYTES;
             mbar_expect_tx(full + s, tx);
             tma_load_2d(st, &tmap_w, (kb0 + it) * BK, n0, full + s);
-            if constexpr (XMODE == 0) tma_load_2d(st + W_BYTES, &tmap_x, (kb0 + it) * BK, m0, full + s);
+            tma_load_2d(st + W_BYTES, &tmap_x, (kb0 + it) * BK, m0, full + s);
             *issued = it + 1;
         }
     } else if (warp == 1 && lane == 0) {
@@ -133,98 +108,6 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
             umma_commit(empty + s);
         }
         if (ok) umma_commit(accum);
-    } else if (XMODE != 0 && warp >= 2) {
-        // The two token-tile warps: 64 threads turn float32 rows into the bfloat16 tile of every stage.
-        const int t = tid - 64;
-        const int rows = min(TN, M - m0);
-        pdl_wait();
-        if constexpr (XMODE == 1) {
-            // Sum of squares of each of the block's rows over the whole row: a warp takes two rows at a time, so the
-            // loads of one row do not wait for the reduction of the other.
-            for (int r = (warp - 2) * 2; r < rows; r += 4) {
-                const bool two = r + 1 < rows;
-                const float* x0 = xs.src + (size_t)(m0 + r) * xs.ld;
-                const float* x1 = xs.src + (size_t)(m0 + (two ? r + 1 : r)) * xs.ld;
-                float s0 = 0.f, s1 = 0.f;
-                for (int k = lane * 4; k < K; k += 32 * 4) {
-                    float a[4], b[4];
-                    load4(x0 + k, a);
-                    load4(x1 + k, b);
-                    s0 += a[0] * a[0] + a[1] * a[1] + a[2] * a[2] + a[3] * a[3];
-                    s1 += b[0] * b[0] + b[1] * b[1] + b[2] * b[2] + b[3] * b[3];
-                }
-                s0 = warp_sum(s0);
-                s1 = warp_sum(s1);
-                if (lane == 0) { rstd[TN + r] = s0; if (two) rstd[TN + r + 1] = s1; }
-            }
-            named_sync_64();
-            for (int r = t; r < rows; r += 64) rstd[r] = 1.0f / sqrtf(rstd[TN + r] / (float)K + xs.eps);
-            named_sync_64();
-        }
-        // Tiles are made for a whole round of the ring at once (up to STAGES k-blocks): the loads of all of them are
-        // independent, so a round costs one trip to memory instead of one per stage.
-        bool ok = true;
-        for (int g0 = 0; g0 < iters && ok; g0 += STAGES) {
-            const int gn = min(STAGES, iters - g0);
-            if (g0 > 0) {
-                if (lane == 0)
-                    for (int st = 0; st < gn && ok; ++st) ok = mbar_wait(empty + st, (((g0 + st) / STAGES) & 1) ^ 1, abort_flag, error_flag, 4);
-                ok = __shfl_sync(0xffffffffu, ok, 0);
-                if (!ok) break;
-            }
-#pragma unroll 4
-            for (int c = t; c < gn * TN * 8; c += 64) {
-                const int st = c / (TN * 8), rem = c % (TN * 8);
-                const int r = rem >> 3, ch = rem & 7, k = (kb0 + g0 + st) * BK + ch * 8;
-                uint4 packed = make_uint4(0, 0, 0, 0);
-                if (r < rows && k < K) {
-                    float a[8], y[8];
-                    if constexpr (XMODE == 1) {
-                        const float* x = xs.src + (size_t)(m0 + r) * xs.ld + k;
-                        float w[8];
-                        load4(x, a); load4(x + 4, a + 4);
-                        load4(xs.norm_w + k, w); load4(xs.norm_w + k + 4, w + 4);
-                        const float rs = rstd[r];
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) y[j] = w[j] * round_through<bf16>(a[j] * rs);
-                    } else {
-                        const float* g = xs.src + (size_t)(m0 + r) * xs.ld + k;
-                        float u[8];
-                        load4(g, a); load4(g + 4, a + 4);
-                        load4(g + K, u); load4(g + K + 4, u + 4);
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) y[j] = a[j] / (1.0f + expf(-a[j])) * u[j];
-                    }
-                    packed.x = pack2(y[0], y[1]); packed.y = pack2(y[2], y[3]); packed.z = pack2(y[4], y[5]); packed.w = pack2(y[6], y[7]);
-                }
-                *reinterpret_cast<uint4*>(tiles + st * STAGE_BYTES + W_BYTES + r * 128 + ((ch ^ (r & 7)) << 4)) = packed;
-            }
-            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // the tensor core reads shared memory through the async proxy
-            __syncwarp();
-            if (lane == 0)
-                for (int st = 0; st < gn; ++st) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(full + st)) : "memory");
-        }
-        if (XMODE == 2 && ok) {
-            // Whichever warp (two per block, over all blocks of the slice) finishes reading this (row tile, K slice)
-            // last sets it back to zero. Warp-level only: no barrier that a warp which gave up could leave hanging.
-            __threadfence();
-            __syncwarp();
-            int last = 0;
-            if (lane == 0) last = atomicAdd(xs.counters + blockIdx.y * gridDim.z + blockIdx.z, 1) == 2 * (int)gridDim.x - 1;
-            last = __shfl_sync(0xffffffffu, last, 0);
-            if (last) {
-                __threadfence();
-                const int k_lo = kb0 * BK, k_hi = min(K, kb1 * BK);
-                const int width = k_hi - k_lo;
-                for (int i = lane * 4; i < rows * width; i += 32 * 4) {
-                    const int r = i / width, k = k_lo + i % width;
-                    float* g = xs.src + (size_t)(m0 + r) * xs.ld + k;
-                    *reinterpret_cast<float4*>(g) = make_float4(0.f, 0.f, 0.f, 0.f);
-                    *reinterpret_cast<float4*>(g + K) = make_float4(0.f, 0.f, 0.f, 0.f);
-                }
-                if (lane == 0) xs.counters[blockIdx.y * gridDim.z + blockIdx.z] = 0;
-            }
-        }
     }
     __syncwarp();
     pdl_wait();  // every thread: the epilogue writes where the kernel before may still read or write
@@ -268,13 +151,13 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
 }
 
 // ------------------------------------------------------------------------------------------------ host side
-template <int TN, int XMODE>
+template <int TN>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, float* out, int ldo, int M, int N, int K, int k_splits, int accumulate,
-           int* error_flag, const XSource& xs, cudaStream_t s) {
-    constexpr size_t smem = (size_t)STAGES * (BM * BK * 2 + TN * BK * 2) + 1024 + 256 + 3 * TN * sizeof(float);
+           int* error_flag, cudaStream_t s) {
+    constexpr size_t smem = (size_t)STAGES * (BM * BK * 2 + TN * BK * 2) + 1024 + 256;
     static bool set = false;
     if (!set) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<TN, XMODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<TN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         set = true;
     }
@@ -282,40 +165,24 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, float* out, int ldo, in
     const int per = (nkb + k_splits - 1) / k_splits;
     const int splits = (nkb + per - 1) / per;  // no empty split
     const dim3 grid((N + BM - 1) / BM, (M + TN - 1) / TN, splits);
-    return launch_kernel(gemm_tc_kernel<TN, XMODE>, grid, dim3(128), smem, s, mw, mx, out, ldo, M, N, K, per, accumulate, error_flag, xs);
+    return launch_kernel(gemm_tc_kernel<TN>, grid, dim3(128), smem, s, mw, mx, out, ldo, M, N, K, per, accumulate, error_flag);
 }
 
-
-
 static int run(const bf16* x, const bf16* w, float* out, int ldo, int M, int N, int K, int k_splits, int accumulate, int* error_flag,
-               const XSource& xs, cudaStream_t s) {
+               cudaStream_t s) {
     if (M <= 0 || N <= 0) return 0;
-    if (K <= 0 || K % 8 || ((uintptr_t)w & 15) || k_splits < 1 || (!accumulate && k_splits != 1) || !error_flag || ldo < N)
+    if (K <= 0 || K % 8 || ((uintptr_t)w & 15) || ((uintptr_t)x & 15) || k_splits < 1 || (!accumulate && k_splits != 1) || !error_flag ||
+        ldo < N)
         return LLMIE_ERR_BAD_ARGUMENT;
     const int TN = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
     CUtensorMap mw, mx;
     int rc = tensor_map(w, N, K, BM, &mw);
     if (rc) return rc;
-    if (xs.mode == 0) {
-        if ((uintptr_t)x & 15) return LLMIE_ERR_BAD_ARGUMENT;
-        rc = tensor_map(x, M, K, TN, &mx);
-        if (rc) return rc;
-    } else {
-        if (!xs.src || ((uintptr_t)xs.src & 15) || xs.ld % 4 || (xs.mode == 1 && (!xs.norm_w || ((uintptr_t)xs.norm_w & 15))) ||
-            (xs.mode == 2 && !xs.counters))
-            return LLMIE_ERR_BAD_ARGUMENT;
-        mx = mw;  // not read
-    }
-#define LLMIE_TC_LAUNCH(MODE)                                                                                        \
-    do {                                                                                                            \
-        if (TN == 16) return launch<16, MODE>(mw, mx, out, ldo, M, N, K, k_splits, accumulate, error_flag, xs, s); \
-        if (TN == 32) return launch<32, MODE>(mw, mx, out, ldo, M, N, K, k_splits, accumulate, error_flag, xs, s); \
-        return launch<64, MODE>(mw, mx, out, ldo, M, N, K, k_splits, accumulate, error_flag, xs, s);               \
-    } while (0)
-    if (xs.mode == 0) LLMIE_TC_LAUNCH(0);
-    if (xs.mode == 1) LLMIE_TC_LAUNCH(1);
-    LLMIE_TC_LAUNCH(2);
-#undef LLMIE_TC_LAUNCH
+    rc = tensor_map(x, M, K, TN, &mx);
+    if (rc) return rc;
+    if (TN == 16) return launch<16>(mw, mx, out, ldo, M, N, K, k_splits, accumulate, error_flag, s);
+    if (TN == 32) return launch<32>(mw, mx, out, ldo, M, N, K, k_splits, accumulate, error_flag, s);
+    return launch<64>(mw, mx, out, ldo, M, N, K, k_splits, accumulate, error_flag, s);
 }
 
 }  // namespace
@@ -324,23 +191,5 @@ static int run(const bf16* x, const bf16* w, float* out, int ldo, int M, int N, 
 // accumulate = 0 needs k_splits = 1 and stores; accumulate = 1 adds atomically into what `out` holds.
 LLMIE_API int llmie_gemm_tc(const bf16* x, const bf16* w, float* out, int ldo, int M, int N, int K, int k_splits, int accumulate,
                             int* error_flag, cudaStream_t s) {
-    XSource xs = {};
-    return run(x, w, out, ldo, M, N, K, k_splits, accumulate, error_flag, xs, s);
-}
-
-// The same product with x = RMS-normalised rows of the float32 `residual` [M, K] (row stride ld_res), weight `norm_w`.
-LLMIE_API int llmie_gemm_tc_norm(float* residual, int ld_res, const float* norm_w, float eps, const bf16* w, float* out, int ldo, int M,
-                                 int N, int K, int k_splits, int accumulate, int* error_flag, cudaStream_t s) {
-    XSource xs = {};
-    xs.mode = 1; xs.src = residual; xs.ld = ld_res; xs.norm_w = norm_w; xs.eps = eps;
-    return run(nullptr, w, out, ldo, M, N, K, k_splits, accumulate, error_flag, xs, s);
-}
-
-// The same product with x = silu(gate) * up taken from the float32 `gate_up` [M, 2 K] (gate first, row stride ld_gu), which is
-// set back to zero once every block has read it. `counters`: at least ceil(M / 64) * k_splits ints, zero (the kernel leaves them zero).
-LLMIE_API int llmie_gemm_tc_silu(float* gate_up, int ld_gu, int* counters, const bf16* w, float* out, int ldo, int M, int N, int K,
-                                 int k_splits, int accumulate, int* error_flag, cudaStream_t s) {
-    XSource xs = {};
-    xs.mode = 2; xs.src = gate_up; xs.ld = ld_gu; xs.counters = counters;
-    return run(nullptr, w, out, ldo, M, N, K, k_splits, accumulate, error_flag, xs, s);
+    return run(x, w, out, ldo, M, N, K, k_splits, accumulate, error_flag, s);
 }

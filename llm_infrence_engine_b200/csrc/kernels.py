@@ -34,26 +34,6 @@ class KernelError(RuntimeError):
     pass
 
 
-class DeferredNorm:
-    """Rows of the residual stream that are to be RMS-normalised by whoever multiplies them next.
-
-    ``CudaKernels.linear`` takes it in place of a tensor: for small bfloat16 batches the tensor-core product
-    normalises the rows on their way into shared memory and no normalised copy is ever written; otherwise it
-    is turned into a tensor first (``CudaKernels.materialize``)."""
-
-    def __init__(self, residual, weight, eps, dtype):
-        self.residual, self.weight, self.eps, self.dtype = residual, weight, float(eps), dtype
-        self.shape = residual.shape
-
-
-class DeferredGate:
-    """``silu(gate) * up`` of a float32 gate/up accumulation, to be applied by the product that reads it."""
-
-    def __init__(self, gate_up, dtype):
-        self.gate_up, self.dtype = gate_up, dtype
-        self.shape = (gate_up.shape[0], gate_up.shape[1] // 2)
-
-
 class CudaKernels:
     name = "cuda-sm100a"
 
@@ -72,19 +52,13 @@ class CudaKernels:
         self.use_tc_gemm = True
         self.tc_max_rows = 128        # batches up to this many rows take the small-batch tensor-core product
         self._acc: Optional[torch.Tensor] = None  # float32 zeros: split-K products add into it, their consumer clears it again
-        self._slice_counters: Optional[torch.Tensor] = None
         # A library product that is to be added into the residual stream is kept here until the next kernel that reads
         # the stream: that kernel is usually the norm, which adds and normalises in one pass (see ``flush``).
         self._pending_add: Optional[tuple] = None
-        # Fold the norm before a product, and silu(gate) * up, into the tensor-core product. Off: measured on a B200 the
-        # separate kernels (whose launch overlaps the product's weight fetch) are faster at every batch size, because a
-        # block that makes its own token tiles adds a trip to memory between the wait and the first MMA.
-        self.fuse_into_gemm = False
-        self.fuse_max_rows = 16       # ... for batches up to this many rows: every block redoes the row work, which must stay small
         self._error_flag: Optional[torch.Tensor] = None
         self.num_sms = torch.cuda.get_device_properties(0).multi_processor_count or NUM_SMS_FALLBACK
         for fn in ("llmie_embed", "llmie_feed_tokens", "llmie_rope_tables", "llmie_add_rmsnorm", "llmie_rope_kv_write", "llmie_silu_mul",
-                   "llmie_gemm_simt", "llmie_gemm_tc", "llmie_gemm_tc_norm", "llmie_gemm_tc_silu", "llmie_add_into", "llmie_attn_plan", "llmie_paged_attention_mma", "llmie_paged_attention_tc", "llmie_paged_attention_f32", "llmie_paged_attention_bf16", "llmie_argmax", "llmie_sample"):
+                   "llmie_gemm_simt", "llmie_gemm_tc", "llmie_add_into", "llmie_attn_plan", "llmie_paged_attention_mma", "llmie_paged_attention_tc", "llmie_paged_attention_f32", "llmie_paged_attention_bf16", "llmie_argmax", "llmie_sample"):
             getattr(self.lib, fn).restype = ctypes.c_int
         # kernels of a step overlap their set-up with the tail of the kernel before (programmatic dependent launch)
         self.lib.llmie_set_pdl(0 if os.environ.get("LLMIE_PDL", "1") == "0" else 1)
@@ -206,52 +180,16 @@ class CudaKernels:
             self._acc = torch.zeros(max(M * N, 1 << 20), dtype=torch.float32, device=device)
         return self._acc[: M * N].view(M, N)
 
-    def deferred_norm(self, residual, weight, eps, out_dtype):
-        """The normalised rows of ``residual`` as something ``linear`` can take (see ``DeferredNorm``)."""
-        self._need(residual, "residual", torch.float32, 2)
-        self._need(weight, "weight", torch.float32, 1)
-        if weight.shape[0] != residual.shape[1]:
-            raise KernelError("deferred_norm: weight does not match the rows")
-        if self._pending_add is not None and self._pending_add[0].data_ptr() != residual.data_ptr():
-            self.flush()
-        return DeferredNorm(residual, weight, eps, out_dtype)
-
-    def gated(self, gu, out_dtype):
-        """``silu(gate) * up`` of a fused gate/up projection, for ``linear``: deferred when ``gu`` is a transient float32
-        accumulation (the product applies it and clears the accumulation), computed right away otherwise."""
-        if self.fuse_into_gemm and self._is_transient(gu) and gu.shape[0] <= self.fuse_max_rows and (gu.shape[1] // 2) % 8 == 0:
-            return DeferredGate(gu, out_dtype)
-        return self.silu_mul(gu, out_dtype)
-
-    def materialize(self, x):
-        if isinstance(x, DeferredNorm):
-            return self.add_rmsnorm(x.residual, None, x.weight, x.eps, x.dtype)
-        if isinstance(x, DeferredGate):
-            return self.silu_mul(x.gate_up, x.dtype)
-        return x
-
     def linear(self, x, w, out_dtype=None, add_to=None, transient=False):
         """``x w^T`` for ``x [rows, K]`` and ``w [outputs, K]``.
 
         ``add_to``: a float32 ``[rows, outputs]`` tensor (the residual stream) that the product is added into;
-        nothing is returned. ``transient``: the caller hands the result straight to ``rope_kv_write``, ``gated`` or
-        ``silu_mul`` and nowhere else; for small bfloat16 batches it is then a float32 view of the library's
-        accumulation buffer, which those kernels read and set back to zero. ``x`` may be a ``DeferredNorm`` or a
-        ``DeferredGate``."""
-        deferred = isinstance(x, (DeferredNorm, DeferredGate))
+        nothing is returned. ``transient``: the caller hands the result straight to ``rope_kv_write`` or ``silu_mul``
+        and nowhere else; for small bfloat16 batches it is then a float32 view of the library's accumulation buffer,
+        which those kernels read and set back to zero."""
+        self._need(x, "x", None, 2)
         M, K = x.shape
         N = w.shape[0]
-        if deferred:
-            fusable = (self.fuse_into_gemm and self.use_tc_gemm and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
-                       and (M <= self.fuse_max_rows or isinstance(x, DeferredGate)) and K % 8 == 0
-                       and (add_to is not None or transient or out_dtype == torch.float32))
-            if not fusable:
-                x = self.materialize(x)
-                deferred = False
-        if not deferred:
-            self._need(x, "x", None, 2)
-        elif isinstance(x, DeferredNorm):
-            self.flush()  # the product will read the residual stream itself
         self._need(w, "w", x.dtype, 2)
         if K != w.shape[1]:
             raise KernelError(f"linear: x has {K} columns, w has {w.shape[1]}")
@@ -299,8 +237,7 @@ class CudaKernels:
 
     def linear_tc(self, x, w, out=None, accumulate=False, k_splits=None):
         """``out (+)= x w^T`` in float32 from bfloat16 operands on the tcgen05 tensor cores, for small batches.
-        ``accumulate`` adds into ``out`` (which may be a strided view, e.g. the residual stream) atomically.
-        ``x``: a bfloat16 tensor, a ``DeferredNorm`` or a ``DeferredGate``."""
+        ``accumulate`` adds into ``out`` (which may be a strided view, e.g. the residual stream) atomically."""
         self._need(w, "w", torch.bfloat16, 2)
         M, K = x.shape
         N = w.shape[0]
@@ -318,18 +255,9 @@ class CudaKernels:
             self._error_flag = torch.zeros(1, dtype=torch.int32, device=w.device)
         if k_splits is None:
             k_splits = self.tc_splits(M, N, K) if accumulate else 1
-        tail = (_ptr(w), _ptr(out), out.stride(0), M, N, K, int(k_splits), int(bool(accumulate)), _ptr(self._error_flag), self._stream())
-        if isinstance(x, DeferredNorm):
-            rc = self.lib.llmie_gemm_tc_norm(_ptr(x.residual), x.residual.stride(0), _ptr(x.weight), ctypes.c_float(x.eps), *tail)
-        elif isinstance(x, DeferredGate):
-            if self._slice_counters is None:
-                self._slice_counters = torch.zeros(4096, dtype=torch.int32, device=w.device)
-            if -(-M // 16) * int(k_splits) > 4096:
-                raise KernelError("linear_tc: too many slices for the clearing counters")
-            rc = self.lib.llmie_gemm_tc_silu(_ptr(x.gate_up), x.gate_up.stride(0), _ptr(self._slice_counters), *tail)
-        else:
-            self._need(x, "x", torch.bfloat16, 2)
-            rc = self.lib.llmie_gemm_tc(_ptr(x), *tail)
+        self._need(x, "x", torch.bfloat16, 2)
+        rc = self.lib.llmie_gemm_tc(_ptr(x), _ptr(w), _ptr(out), out.stride(0), M, N, K, int(k_splits), int(bool(accumulate)),
+                                    _ptr(self._error_flag), self._stream())
         self._check(rc, "linear_tc")
         return out
 

@@ -22,7 +22,6 @@ class PagedAttention(Mixer):
     """
 
     graph_safe = True
-    takes_deferred_input = True
 
     def __init__(self, hidden: int, num_heads: int, num_kv_heads: int, head_dim: int, position: PositionEncoding,
                  prefix: str, bias: bool = True, window: Optional[int] = None, scale: Optional[float] = None):

@@ -60,10 +60,6 @@ class ParamSpec:
 class Part:
     """Base of every part: named tensors in, ``bind`` once, then ``forward`` every step."""
 
-    # True if ``forward`` uses its input ``h`` only as the left operand of ``ctx.K.linear``: a block may then hand it
-    # a deferred norm (``Norm.deferred``) and the product does the normalising.
-    takes_deferred_input = False
-
     # True if ``forward`` only launches kernels on the current stream and reads nothing of the step on the
     # host (no host lists of the context, no synchronisation): such a part can be captured in a CUDA graph.
     graph_safe = False
@@ -91,11 +87,6 @@ class Part:
 class Norm(Part):
     def norm(self, ctx, residual: torch.Tensor) -> torch.Tensor:
         raise NotImplementedError
-
-    def deferred(self, ctx, residual: torch.Tensor):
-        """What a part with ``takes_deferred_input`` is handed instead of ``norm``'s tensor: something it may only
-        pass on to ``ctx.K.linear``. The default simply computes the tensor."""
-        return self.norm(ctx, residual)
 
     def norm_rows(self, ctx, residual: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
         """Normalise only ``residual[rows]``."""

@@ -28,7 +28,5 @@ class PreNormBlock(Part):
         return self.mixer.cache_spec()
 
     def forward(self, ctx, residual: torch.Tensor, cache) -> None:
-        h = self.norm1.deferred(ctx, residual) if self.mixer.takes_deferred_input else self.norm1.norm(ctx, residual)
-        self.mixer.forward(ctx, h, cache, residual)
-        h = self.norm2.deferred(ctx, residual) if self.ff.takes_deferred_input else self.norm2.norm(ctx, residual)
-        self.ff.forward(ctx, h, residual)
+        self.mixer.forward(ctx, self.norm1.norm(ctx, residual), cache, residual)
+        self.ff.forward(ctx, self.norm2.norm(ctx, residual), residual)

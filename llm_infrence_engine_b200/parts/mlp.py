@@ -18,7 +18,6 @@ class GatedMLP(FeedForward):
     """
 
     graph_safe = True
-    takes_deferred_input = True
 
     def __init__(self, hidden: int, intermediate: int, prefix: str, activation: str = "silu"):
         if activation not in ACTIVATIONS:
@@ -37,4 +36,4 @@ class GatedMLP(FeedForward):
     def forward(self, ctx, h, residual):
         K = ctx.K
         gu = K.linear(h, self.w_gate_up, transient=True)
-        K.linear(K.gated(gu, ctx.dtype), self.w_down, add_to=residual)
+        K.linear(K.silu_mul(gu, ctx.dtype), self.w_down, add_to=residual)

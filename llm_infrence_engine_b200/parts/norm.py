@@ -29,9 +29,5 @@ class RMSNorm(Norm):
     def norm(self, ctx, residual):
         return ctx.K.add_rmsnorm(residual, None, self.weight, self.eps, ctx.dtype)
 
-    def deferred(self, ctx, residual):
-        """The same rows, not computed yet: the matrix product that reads them normalises them on the way in."""
-        return ctx.K.deferred_norm(residual, self.weight, self.eps, ctx.dtype)
-
     def norm_rows(self, ctx, residual, rows):
         return ctx.K.rmsnorm_rows(residual, None, self.weight, self.eps, rows, ctx.dtype)

@@ -319,7 +319,9 @@ def test_paged_attention_tcgen05(K, monkeypatch, nq, nkv, ps, lens, qlens, windo
 @pytest.mark.parametrize("M,N,K_,splits,accumulate", [
     (1, 128, 64, 1, False),
     (8, 1152, 896, 1, False),
-    (8, 9728, 896, 3, True),
+    (8, 9728, 896, 3, True),         # 5 k-blocks per block: one more than the ring has stages
+    (8, 1152, 896, 5, True),         # 3 k-blocks per block, the last block 2
+    (33, 640, 960, 2, True),         # 8 k-blocks per block, two rounds of the ring
     (8, 896, 4864, 19, True),        # many blocks add into the same rows
     (64, 896, 896, 14, True),
     (40, 200, 72, 2, True),          # ragged: N and K are no multiples of the tile
@@ -389,41 +391,3 @@ def test_transient_products_are_consumed_and_cleared(K):
     assert K.linear(a, wd.cuda(), add_to=r) is None
     close(r, res.double() + a.double().cpu() @ wd.double().T, 2e-5)
     K.check_device_errors()
-
-
-@pytest.mark.parametrize("M,H,N,splits", [(1, 896, 1152, 14), (8, 896, 9728, 3), (40, 200, 136, 2), (100, 256, 384, None), (5, 1536, 2048, 1)])
-def test_linear_tc_with_the_norm_folded_in(K, M, H, N, splits):
-    g = torch.Generator().manual_seed(13)
-    res = torch.randn(M, H, generator=g) * 2
-    wn = 1 + 0.1 * torch.randn(H, generator=g)
-    w = (torch.randn(N, H, generator=g) * 0.05).to(torch.bfloat16)
-    h = REF.add_rmsnorm(res.clone(), None, wn, 1e-6, torch.bfloat16)
-    want = h.double() @ w.double().T
-    for _ in range(2):
-        out = torch.zeros(M, N, device="cuda")
-        r = res.clone().cuda()
-        K.linear_tc(K.deferred_norm(r, wn.cuda(), 1e-6, torch.bfloat16), w.cuda(), out=out, accumulate=True, k_splits=splits)
-        K.check_device_errors()
-        close(out, want, 6e-3)          # 1/rms is summed in another order than the reference: a few bfloat16 roundings differ
-        assert torch.equal(r.cpu(), res)
-
-
-@pytest.mark.parametrize("M,I,N,splits", [(8, 4864, 896, 38), (1, 64, 128, 1), (16, 200, 72, 2), (13, 512, 256, 4)])
-def test_linear_tc_with_the_gate_folded_in(K, M, I, N, splits):
-    from llm_infrence_engine_b200.csrc.kernels import DeferredGate
-
-    g = torch.Generator().manual_seed(14)
-    x = torch.randn(M, 96, generator=g).to(torch.bfloat16)
-    wgu = (torch.randn(2 * I, 96, generator=g) * 0.2).to(torch.bfloat16)
-    wd = (torch.randn(N, I, generator=g) * 0.05).to(torch.bfloat16)
-    res = torch.randn(M, N, generator=g)
-    gu_ref = x.float() @ wgu.float().T
-    want = res.double() + REF.silu_mul(gu_ref).to(torch.bfloat16).double() @ wd.double().T
-    for _ in range(2):
-        gu = K.linear(x.cuda(), wgu.cuda(), transient=True)
-        gated = DeferredGate(gu, torch.bfloat16)
-        r = res.clone().cuda()
-        K.linear_tc(gated, wd.cuda(), out=r, accumulate=True, k_splits=splits)
-        K.check_device_errors()
-        close(r, want, 5e-3)
-        assert K._acc.abs().sum().item() == 0 and K._slice_counters.abs().sum().item() == 0

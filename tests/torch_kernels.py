@@ -95,12 +95,6 @@ class TorchKernels:
                 out[t, h] = pr @ v[:, h // rep]
         return out.reshape(N, num_heads * d).to(qkv.dtype)
 
-    def deferred_norm(self, residual, weight, eps, out_dtype):
-        return self.add_rmsnorm(residual, None, weight, eps, out_dtype)
-
-    def gated(self, gu, out_dtype):
-        return self.silu_mul(gu, out_dtype)
-
     def silu_mul(self, gu, out_dtype=None):
         i = gu.shape[1] // 2
         g, u = gu[:, :i].float(), gu[:, i:].float()
