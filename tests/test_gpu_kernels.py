@@ -56,7 +56,8 @@ def test_rope_tables(K, half, theta):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("N,H,eps", [(5, 64, 1e-6), (3, 200, 1e-5), (2, 4100, 3e-6), (9, 896, 1e-6)])
+@pytest.mark.parametrize("N,H,eps", [(5, 64, 1e-6), (3, 200, 1e-5), (2, 4100, 3e-6), (9, 896, 1e-6),
+                                     (70, 896, 1e-6), (40, 1536, 1e-5)])
 def test_add_rmsnorm(K, dtype, N, H, eps):
     g = torch.Generator().manual_seed(1)
     res = torch.randn(N, H, generator=g) * 3
@@ -68,7 +69,7 @@ def test_add_rmsnorm(K, dtype, N, H, eps):
         want = REF.add_rmsnorm(r_ref, d, w, eps, dtype)
         close(got, want, tol(dtype, 2e-6, 8e-3))
         assert torch.equal(r_gpu.cpu(), r_ref)  # the residual sum is exact 32-bit addition on both sides
-    rows = torch.tensor([N - 1, 0, N // 2], dtype=torch.int32)
+    rows = torch.tensor([N - 1, 0, N // 2], dtype=torch.int32) if N < 32 else torch.randperm(N, generator=g)[:N - 1].int()
     r_gpu = res.clone().cuda()
     got = K.rmsnorm_rows(r_gpu, delta.cuda(), w.cuda(), eps, rows.cuda(), dtype)
     close(got, REF.rmsnorm_rows(res, delta, w, eps, rows, dtype), tol(dtype, 2e-6, 8e-3))
@@ -181,7 +182,7 @@ def test_paged_attention(K, dtype, nq, nkv, d, ps, lens, qlens, window, splits):
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_silu_mul(K, dtype):
     g = torch.Generator().manual_seed(5)
-    for rows, width in ((7, 203), (3, 1028), (2, 8)):  # odd widths take the scalar kernel; 1028 is 4 beyond a block of threads
+    for rows, width in ((7, 203), (3, 1028), (2, 8), (5, 4864), (40, 200)):  # odd widths take the scalar kernel; 1028 is 4 beyond a block of threads
         gu = (torch.randn(rows, 2 * width, generator=g) * 4).to(dtype)
         close(K.silu_mul(gu.cuda()), REF.silu_mul(gu), tol(dtype, 1e-6, 8e-3))
 
