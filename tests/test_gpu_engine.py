@@ -57,7 +57,7 @@ def first_bad(got, want, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_whole(models, name, dtype):
     folder, cfg, w, prompts, want = models[(name, dtype)]
     rp = replayer(folder, name, dtype, 192)
@@ -68,7 +68,7 @@ def test_whole(models, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_last_32_one_by_one(models, name, dtype):
     folder, cfg, w, prompts, want = models[(name, dtype)]
     rp = replayer(folder, name, dtype, 192)
@@ -83,7 +83,7 @@ def test_last_32_one_by_one(models, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_portions_of_changing_size(models, name, dtype):
     folder, cfg, w, prompts, want = models[(name, dtype)]
     rp = replayer(folder, name, dtype, 192)
@@ -144,7 +144,7 @@ def run_mixed(rp, prompts):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_mixed_on_few_pages(models, name, dtype):
     folder, cfg, w, prompts, want = models[(name, dtype)]
     # a(150)->192, b(97)->128, c(64)->64, d(41)->64 live together = 448; e takes pages that b, c or d gave back
