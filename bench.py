@@ -48,6 +48,15 @@ CONTEXT = 8192
 PREFILL_TOKENS = 2048
 BLOCK = 16
 
+# Other layer sizes of the same architecture (``--shape``): what changes against MODEL, and the context length they are quoted at.
+SHAPES = {
+    "0.5b": ("Qwen2.5-0.5B shape", {}, 8192),
+    "1.5b": ("Qwen2.5-1.5B shape", {"hidden_size": 1536, "intermediate_size": 8960, "num_hidden_layers": 28, "num_attention_heads": 12,
+                                    "num_key_value_heads": 2}, 8192),
+    "7b": ("Qwen2.5-7B shape", {"vocab_size": 152064, "hidden_size": 3584, "intermediate_size": 18944, "num_hidden_layers": 28,
+                                "num_attention_heads": 28, "num_key_value_heads": 4, "tie_word_embeddings": False}, 16384),
+}
+
 
 def peaks() -> dict:
     out = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
@@ -254,7 +263,9 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--layers", type=int, default=MODEL["num_hidden_layers"], help="fewer layers than the model has (named in config)")
+    ap.add_argument("--shape", default="0.5b", choices=sorted(SHAPES), help="layer sizes (the default is the one the headline is quoted on)")
+    ap.add_argument("--context", type=int, default=0, help="context length of the decode steps (default: the shape's own)")
+    ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (named in config)")
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--no-graphs", action="store_true", help="launch every kernel of a decode step from the host instead of replaying a CUDA graph")
     ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"], help="measure one part only (for profiling); the JSON line then lacks the rest")
@@ -264,6 +275,11 @@ def main() -> int:
     if a.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {a.gpus} is not supported")
         return 2
+    global CONTEXT
+    shape_name, changes, shape_context = SHAPES[a.shape]
+    MODEL.update(changes)
+    CONTEXT = a.context or shape_context
+    a.layers = a.layers or MODEL["num_hidden_layers"]
     a.warmup = max(a.warmup, 3)
     graphs = not a.no_graphs
 
@@ -295,14 +311,15 @@ def main() -> int:
     fl = flops_prefill(PREFILL_TOKENS) * a.layers / MODEL["num_hidden_layers"]
     achieved = main_pt["bytes"] / (main_pt["ms"] * 1e-3) / 1e9
     line = {
-        "metric": "decode tok/s at batch 8, context 8192 (Qwen2.5-0.5B shape, bf16, random weights)",
+        "metric": f"decode tok/s at batch {a.batch}, context {CONTEXT} ({shape_name}, bf16, random weights)",
         "value": round(main_pt["tok_s"], 1), "unit": "tokens/s", "n_gpus": 1, "steps": a.steps, "warmup": a.warmup,
         "ms_per_step": round(main_pt["ms"], 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic: random weights (seed 0), uniform random token ids, synthetic cache contents",
         "impl": "ours",
-        "config": {"model": "Qwen2.5-0.5B shape", "layers": a.layers, "layers_of_model": MODEL["num_hidden_layers"],
-                   "hidden": 896, "heads": 14, "kv_heads": 2, "head_dim": 64, "intermediate": 4864, "vocab": 151936,
-                   "tied": True, "global_batch": a.batch, "seq_len": CONTEXT, "block_size": BLOCK, "parallelism": "single GPU",
+        "config": {"model": shape_name, "layers": a.layers, "layers_of_model": MODEL["num_hidden_layers"],
+                   "hidden": MODEL["hidden_size"], "heads": MODEL["num_attention_heads"], "kv_heads": MODEL["num_key_value_heads"],
+                   "head_dim": MODEL["hidden_size"] // MODEL["num_attention_heads"], "intermediate": MODEL["intermediate_size"],
+                   "vocab": MODEL["vocab_size"], "tied": MODEL["tie_word_embeddings"], "global_batch": a.batch, "seq_len": CONTEXT, "block_size": BLOCK, "parallelism": "single GPU",
                    "cuda_graphs": graphs, "l2": "inputs larger than L2 (weights + cache per step >> 126 MB), no flush", "peaks": pk["source"]},
         "clocks": clocks,
         "gpu_launches": main_pt["launches"],
