@@ -227,9 +227,11 @@ __global__ void __launch_bounds__(DW * 32) attn_mma_decode_kernel(const Params p
     // this warp's chunks: c_begin + warp, + DW, ...
     const int first = c_begin + warp;
     const int mine = first < c_end ? (c_end - first + DW - 1) / DW : 0;
-    bool fetched[STAGES - 1];
+    // All STAGES slots of the ring are filled up front; a slot is filled again right AFTER its chunk has been used, so the
+    // instructions that issue a copy never stand between a landed chunk and its arithmetic.
+    bool fetched[STAGES];
 #pragma unroll
-    for (int s = 0; s < STAGES - 1; ++s) {
+    for (int s = 0; s < STAGES; ++s) {
         const int key0 = lo + (first + s * DW) * BN;
         fetched[s] = early && s < mine && key0 + BN <= pos0;  // wholly before the first new position
         if (fetched[s]) load_rows_warp<D, BN>(p, table, kvh, key0, hi - 1, 0, my + s * 2 * TILE, my + s * 2 * TILE + TILE, lane);
@@ -258,17 +260,13 @@ __global__ void __launch_bounds__(DW * 32) attn_mma_decode_kernel(const Params p
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
 
 #pragma unroll
-    for (int s = 0; s < STAGES - 1; ++s) {
+    for (int s = 0; s < STAGES; ++s) {
         if (s < mine && !fetched[s]) load_rows_warp<D, BN>(p, table, kvh, lo + (first + s * DW) * BN, hi - 1, 0, my + s * 2 * TILE, my + s * 2 * TILE + TILE, lane);
         cp_async_commit();  // stage 0's group may also hold later stages' early fetches: it then completes a little later, never too early
     }
     for (int it = 0; it < mine; ++it) {
-        const int nxt = it + STAGES - 1;
-        if (nxt < mine) {
-            bf16* dst = my + (nxt % STAGES) * 2 * TILE;
-            load_rows_warp<D, BN>(p, table, kvh, lo + (first + nxt * DW) * BN, hi - 1, 0, dst, dst + TILE, lane);
-        }
-        cp_async_commit();
+        // groups so far: STAGES from above and one per iteration before this one; chunk `it` is in group `it` (and the early
+        // fetches in group 0): everything but the STAGES - 1 youngest groups must have landed
         cp_async_wait<STAGES - 1>();
         __syncwarp();
         const bf16* cur = my + (it % STAGES) * 2 * TILE;
@@ -279,7 +277,13 @@ __global__ void __launch_bounds__(DW * 32) attn_mma_decode_kernel(const Params p
             attend_chunk<D, BN, false>(qa, cur, cur + TILE, o, m, l, key0, row_pos, row_ok, p.window, p.scale_log2, lane);
         else
             attend_chunk<D, BN, true>(qa, cur, cur + TILE, o, m, l, key0, row_pos, row_ok, p.window, p.scale_log2, lane);
-        __syncwarp();
+        __syncwarp();  // every lane is done with the slot
+        const int nxt = it + STAGES;
+        if (nxt < mine) {
+            bf16* dst = my + (it % STAGES) * 2 * TILE;
+            load_rows_warp<D, BN>(p, table, kvh, lo + (first + nxt * DW) * BN, hi - 1, 0, dst, dst + TILE, lane);
+        }
+        cp_async_commit();
     }
     cp_async_wait<0>();
 #pragma unroll
@@ -288,10 +292,12 @@ __global__ void __launch_bounds__(DW * 32) attn_mma_decode_kernel(const Params p
         l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
     }
     __syncthreads();  // every warp is done with its ring; the space is reused for the merge
-    float* wm = reinterpret_cast<float*>(smem_raw);        // [DW][16]
-    float* wl = wm + DW * 16;                           // [DW][16]
-    float* wo = wl + DW * 16;                           // [DW][16][D]
-    float* fm = wo + DW * 16 * D;                       // merged [16], [16], [16][D]
+    constexpr int WS = D + 8;                           // row stride of the warps' outputs: eight rows written at once spread over the banks
+    float* wm = reinterpret_cast<float*>(smem_raw);        // [DW][16] each warp's row maxima
+    float* wl = wm + DW * 16;                           // [DW][16] row sums
+    float* wf = wl + DW * 16;                           // [DW][16] the weight of each warp's row in the merged row
+    float* wo = wf + DW * 16;                           // [DW][16][WS] outputs
+    float* fm = wo + DW * 16 * WS;                      // merged [16], [16], [16][D]
     float* fl = fm + 16;
     float* fo = fl + 16;
 #pragma unroll
@@ -301,27 +307,32 @@ __global__ void __launch_bounds__(DW * 32) attn_mma_decode_kernel(const Params p
 #pragma unroll
         for (int dt = 0; dt < D / 8; ++dt) {
             const int col = dt * 8 + ((lane & 3) << 1);
-            wo[(warp * 16 + row) * D + col] = o[dt][2 * r];
-            wo[(warp * 16 + row) * D + col + 1] = o[dt][2 * r + 1];
+            *reinterpret_cast<float2*>(wo + (warp * 16 + row) * WS + col) = make_float2(o[dt][2 * r], o[dt][2 * r + 1]);
         }
+    }
+    __syncthreads();
+    // a row's weights once (not once per output element): exp2(warp's maximum - overall maximum); the row's merged maximum and sum
+    for (int i = tid; i < DW * 16; i += DW * 32) {
+        const int w = i / 16, r = i % 16;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w2 = 0; w2 < DW; ++w2) M = fmaxf(M, wm[w2 * 16 + r]);
+        wf[i] = M > -INFINITY ? fast_exp2(wm[i] - M) : 0.f;
+        if (w == 0) fm[r] = M;
     }
     __syncthreads();
     for (int i = tid; i < 16 * D; i += DW * 32) {
         const int r = i / D, dim = i % D;
-        float M = -INFINITY;
+        float O = 0.f;
 #pragma unroll
-        for (int w = 0; w < DW; ++w) M = fmaxf(M, wm[w * 16 + r]);
-        float L = 0.f, O = 0.f;
-        if (M > -INFINITY) {
-#pragma unroll
-            for (int w = 0; w < DW; ++w) {
-                const float f = exp2f(wm[w * 16 + r] - M);
-                L = fmaf(wl[w * 16 + r], f, L);
-                O = fmaf(wo[(w * 16 + r) * D + dim], f, O);
-            }
-        }
+        for (int w = 0; w < DW; ++w) O = fmaf(wo[(w * 16 + r) * WS + dim], wf[w * 16 + r], O);
         fo[i] = O;
-        if (dim == 0) { fm[r] = M; fl[r] = L; }
+        if (dim == 0) {
+            float L = 0.f;
+#pragma unroll
+            for (int w = 0; w < DW; ++w) L = fmaf(wl[w * 16 + r], wf[w * 16 + r], L);
+            fl[r] = L;
+        }
     }
     __syncthreads();
     if (p.cluster && p.num_splits > 1) {
@@ -495,7 +506,7 @@ int launch(const Params& p, int num_tiles, int decode_mode, cudaStream_t s) {
     if (decode_mode) {
         constexpr int BN = D == 64 ? 32 : 16, STAGES = 3, DW = 8;  // eight warps, each with its own ring of 4 KB + 4 KB chunks
         constexpr size_t ring = (size_t)DW * STAGES * 2 * BN * D * sizeof(bf16);
-        constexpr size_t merge = (size_t)(DW * 16 * (D + 2) + 16 * (D + 2)) * sizeof(float);
+        constexpr size_t merge = (size_t)(DW * 16 * (D + 8 + 3) + 16 * (D + 2)) * sizeof(float);
         constexpr size_t smem = ring > merge ? ring : merge;
         static bool set = false;
         if (!set) {
