@@ -27,15 +27,17 @@ __device__ __forceinline__ void finish_tile(const Params& p, const float* row_m,
     float* pml = p.part_ml + (base + split) * ROWS * 2;
     for (int i = tid * 4; i < nrows * D; i += THREADS * 4) *reinterpret_cast<float4*>(po + i) = *reinterpret_cast<const float4*>(row_o + i);
     for (int r = tid; r < nrows; r += THREADS) { pml[2 * r] = row_m[r]; pml[2 * r + 1] = row_l[r]; }
-    __threadfence();
+    // The block's partial is complete once every thread has passed the barrier; thread 0 then counts the block in with an
+    // atomic that RELEASES (what the block wrote is visible to whoever sees the count) and ACQUIRES (the last block sees what
+    // the others wrote): one trip to memory instead of a fence followed by an atomic.
     __syncthreads();
     if (tid == 0) {
-        const int prev = atomicAdd(p.counters + tile * p.nkv + kvh, 1);
+        int prev;
+        asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;\n" : "=r"(prev) : "l"(p.counters + tile * p.nkv + kvh) : "memory");
         *flag_smem = prev == p.num_splits - 1;
     }
     __syncthreads();
     if (!*flag_smem) return;
-    __threadfence();
     // Last block of the tile: first the slices' (max, sum) pairs become per-row weights in shared memory (the
     // block's own row_m / row_l / row_o are not needed any more), then every output element is one weighted sum
     // whose loads do not depend on each other.

@@ -40,6 +40,7 @@ struct Params {
     float* part_ml;         // [tiles][nkv][splits][ROWS][2]
     int* counters;          // [tiles * nkv], zero between launches
     int q_stride, max_blocks, nq, nkv, page_size, window, num_splits;
+    int page_shift;         // log2(page_size), or -1 if that is no power of two
     int cluster;            // 1: the slices of a tile are one thread-block cluster and merge through distributed shared memory
     float scale_log2;       // softmax scale * log2(e)
 };
@@ -95,28 +96,47 @@ template <int D> __device__ __forceinline__ int swz(int row, int col) { return r
 // One warp copies NKEYS consecutive cache rows (keys key_abs0 .., clamped to last_key) into rows tile_row0 .. of a
 // swizzled K tile and V tile. Every lane looks up the page of at most two keys; the row numbers then travel by
 // shuffle to the lanes that copy that row's 16-byte pieces, 8 (or 16) neighbouring lanes per row.
-template <int D, int NKEYS>
-__device__ __forceinline__ void load_rows_warp(const Params& p, const int* table, int kvh, int key_abs0, int last_key, int tile_row0,
-                                               bf16* ks, bf16* vs, int lane) {
-    constexpr int CH = D / 8, KPI = 32 / CH, NH = (NKEYS + 31) / 32;
-    int rowidx[NH];
+template <int NKEYS>
+struct PoolRows {
+    int idx[(NKEYS + 31) / 32];  // lane l: row of key l (l + 32, ...) of the chunk in the [pages * heads * page_size, D] pool
+};
+
+// First half of a load: where the chunk's keys lie. A read of the block table that the copies depend on; a caller that can
+// issues it well before `copy_rows_warp`, so that its latency passes while it does something else.
+template <int NKEYS>
+__device__ __forceinline__ PoolRows<NKEYS> find_rows_warp(const Params& p, const int* table, int kvh, int key_abs0, int last_key, int lane) {
+    PoolRows<NKEYS> rows;
 #pragma unroll
-    for (int h = 0; h < NH; ++h) {
+    for (int h = 0; h < (NKEYS + 31) / 32; ++h) {
         const int ka = min(key_abs0 + h * 32 + lane, last_key);
-        const int page = table[ka / p.page_size];
-        rowidx[h] = (page * p.nkv + kvh) * p.page_size + ka % p.page_size;
+        const int pg = p.page_shift >= 0 ? ka >> p.page_shift : ka / p.page_size;  // page sizes are powers of two as a rule
+        rows.idx[h] = (table[pg] * p.nkv + kvh) * p.page_size + (ka - pg * p.page_size);
     }
+    return rows;
+}
+
+// Second half: the row numbers travel by shuffle to the lanes that copy that row's 16-byte pieces, 8 (or 16) neighbouring
+// lanes per row, into the swizzled K tile and V tile.
+template <int D, int NKEYS>
+__device__ __forceinline__ void copy_rows_warp(const Params& p, const PoolRows<NKEYS>& rows, int tile_row0, bf16* ks, bf16* vs, int lane) {
+    constexpr int CH = D / 8, KPI = 32 / CH;
     const int ch = lane % CH, sub = lane / CH;
 #pragma unroll
     for (int i = 0; i < NKEYS / KPI; ++i) {
         const int key = i * KPI + sub;
-        const int r = __shfl_sync(0xffffffffu, rowidx[(i * KPI) >> 5], key & 31);
+        const int r = __shfl_sync(0xffffffffu, rows.idx[(i * KPI) >> 5], key & 31);
         const int trow = tile_row0 + key;
         const int dst = trow * D + ((ch ^ (trow & 7)) << 3);
         const size_t src = (size_t)r * D + ch * 8;
         cp_async16(ks + dst, p.k_pool + src);
         cp_async16(vs + dst, p.v_pool + src);
     }
+}
+
+template <int D, int NKEYS>
+__device__ __forceinline__ void load_rows_warp(const Params& p, const int* table, int kvh, int key_abs0, int last_key, int tile_row0,
+                                               bf16* ks, bf16* vs, int lane) {
+    copy_rows_warp<D, NKEYS>(p, find_rows_warp<NKEYS>(p, table, kvh, key_abs0, last_key, lane), tile_row0, ks, vs, lane);
 }
 
 // One chunk of BN keys for one warp's 16 rows: S = Q K^T, masked online softmax, O += P V.
@@ -264,6 +284,10 @@ __global__ void __launch_bounds__(DW * 32) attn_mma_decode_kernel(const Params p
         if (s < mine && !fetched[s]) load_rows_warp<D, BN>(p, table, kvh, lo + (first + s * DW) * BN, hi - 1, 0, my + s * 2 * TILE, my + s * 2 * TILE + TILE, lane);
         cp_async_commit();  // stage 0's group may also hold later stages' early fetches: it then completes a little later, never too early
     }
+    // where the chunk lies that refills the first slot: the block table is read now, not between a chunk's arithmetic and the
+    // copies that refill its slot
+    PoolRows<BN> refill;
+    if (STAGES < mine) refill = find_rows_warp<BN>(p, table, kvh, lo + (first + STAGES * DW) * BN, hi - 1, lane);
     for (int it = 0; it < mine; ++it) {
         // groups so far: STAGES from above and one per iteration before this one; chunk `it` is in group `it` (and the early
         // fetches in group 0): everything but the STAGES - 1 youngest groups must have landed
@@ -281,7 +305,8 @@ __global__ void __launch_bounds__(DW * 32) attn_mma_decode_kernel(const Params p
         const int nxt = it + STAGES;
         if (nxt < mine) {
             bf16* dst = my + (it % STAGES) * 2 * TILE;
-            load_rows_warp<D, BN>(p, table, kvh, lo + (first + nxt * DW) * BN, hi - 1, 0, dst, dst + TILE, lane);
+            copy_rows_warp<D, BN>(p, refill, 0, dst, dst + TILE, lane);
+            if (nxt + 1 < mine) refill = find_rows_warp<BN>(p, table, kvh, lo + (first + (nxt + 1) * DW) * BN, hi - 1, lane);
         }
         cp_async_commit();
     }
@@ -572,6 +597,7 @@ LLMIE_API int llmie_paged_attention_mma(const bf16* q, int q_stride, const bf16*
     p.q = q; p.k_pool = k_pool; p.v_pool = v_pool; p.block_table = block_table; p.token_seq = token_seq; p.positions = positions;
     p.tile_info = tile_info; p.out = out; p.part_o = scratch_o; p.part_ml = scratch_ml; p.counters = counters;
     p.q_stride = q_stride; p.max_blocks = max_blocks; p.nq = nq; p.nkv = nkv; p.page_size = page_size; p.window = window;
+    p.page_shift = (page_size & (page_size - 1)) == 0 ? __builtin_ctz((unsigned)page_size) : -1;
     p.num_splits = num_splits; p.scale_log2 = scale * LOG2E; p.cluster = cluster;
     return d == 64 ? launch<64>(p, num_tiles, decode_mode, s) : launch<128>(p, num_tiles, decode_mode, s);
 }
