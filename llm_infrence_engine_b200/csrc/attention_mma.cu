@@ -214,8 +214,93 @@ __device__ __forceinline__ void attend_chunk(const uint32_t (&qa)[D / 16][4], co
 }
 
 
+// The same for tiles of at most 8 rows (a decoded token's heads of one group), computed TRANSPOSED so that no tensor-core work
+// goes to padding rows: S^T = K Q^T (m16n8k16 with the 16 KEYS as M, the 8 rows as N) and O^T = V^T P^T (16 dims as M).
+// Per lane: scores of keys lane / 4 (+ 8) and rows 2 (lane % 4), + 1; P^T goes from accumulator to B-operand layout by
+// transposing 8 x 8 blocks across the warp (movmatrix). Half the MMAs, exponentials and registers of attend_chunk.
+//   qb[kk][h]   Q^T as B operand: row lane / 4, dims kk * 16 + 2 (lane % 4) + {0, 1} (+ 8 h)
+//   ot[dt][e]   O^T: dim dt * 16 + lane / 4 + 8 (e >> 1), row 2 (lane % 4) + (e & 1)
+//   m[j], l[j]  of row 2 (lane % 4) + j; l holds this lane's keys only until the caller sums it over lanes 4, 8, 16 apart
+__device__ __forceinline__ uint32_t transpose_8x8(uint32_t a) {
+    uint32_t d;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(d) : "r"(a));
+    return d;
+}
+
+template <int D, int BN, bool MASKED>
+__device__ __forceinline__ void attend_chunk_t8(const uint32_t (&qb)[D / 16][2], const bf16* ks, const bf16* vs, float (&ot)[D / 16][4],
+                                                float (&m)[2], float (&l)[2], int key0, int pos, int nrows, int window, float scale_log2,
+                                                int lane) {
+    float st[BN / 16][4];
+#pragma unroll
+    for (int kt = 0; kt < BN / 16; ++kt) {
+        st[kt][0] = st[kt][1] = st[kt][2] = st[kt][3] = 0.f;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+            uint32_t b[4];
+            const int key = kt * 16 + (lane & 7) + ((lane >> 4) << 3);
+            const int col = kk * 16 + (((lane >> 3) & 1) << 3);
+            ldmatrix_x4(b, ks + swz<D>(key, col));  // (keys 0-7, dims 0-7), (0-7, 8-15), (8-15, 0-7), (8-15, 8-15)
+            const uint32_t a[4] = {b[0], b[2], b[1], b[3]};
+            mma_bf16(st[kt], a, qb[kk][0], qb[kk][1]);
+        }
+    }
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int kt = 0; kt < BN / 16; ++kt) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int key = key0 + kt * 16 + (lane >> 2) + ((e >> 1) << 3);
+            const bool ok = !MASKED || (((lane & 3) << 1) + (e & 1) < nrows && key <= pos && (window <= 0 || key > pos - window));
+            const float x = ok ? st[kt][e] * scale_log2 : -INFINITY;
+            st[kt][e] = x;
+            mx[e & 1] = fmaxf(mx[e & 1], x);
+        }
+    }
+    float corr[2], use[2];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+        mx[j] = fmaxf(mx[j], __shfl_xor_sync(0xffffffffu, mx[j], 4));
+        mx[j] = fmaxf(mx[j], __shfl_xor_sync(0xffffffffu, mx[j], 8));
+        mx[j] = fmaxf(mx[j], __shfl_xor_sync(0xffffffffu, mx[j], 16));
+        const float m_new = fmaxf(m[j], mx[j]);
+        use[j] = m_new == -INFINITY ? 0.f : m_new;
+        corr[j] = fast_exp2(m[j] - use[j]);
+        m[j] = m_new;
+        l[j] *= corr[j];
+    }
+#pragma unroll
+    for (int dt = 0; dt < D / 16; ++dt) {
+        ot[dt][0] *= corr[0]; ot[dt][1] *= corr[1];
+        ot[dt][2] *= corr[0]; ot[dt][3] *= corr[1];
+    }
+    uint32_t pb[BN / 16][2];
+#pragma unroll
+    for (int kt = 0; kt < BN / 16; ++kt) {
+        const float p0 = fast_exp2(st[kt][0] - use[0]), p1 = fast_exp2(st[kt][1] - use[1]);
+        const float p2 = fast_exp2(st[kt][2] - use[0]), p3 = fast_exp2(st[kt][3] - use[1]);
+        l[0] += p0 + p2;
+        l[1] += p1 + p3;
+        pb[kt][0] = transpose_8x8(pack_bf16(p0, p1));  // keys 0-7 of the tile: [key][row] -> [row][key]
+        pb[kt][1] = transpose_8x8(pack_bf16(p2, p3));  // keys 8-15
+    }
+#pragma unroll
+    for (int dt = 0; dt < D / 16; ++dt) {
+#pragma unroll
+        for (int kt = 0; kt < BN / 16; ++kt) {
+            uint32_t b[4];
+            const int key = kt * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
+            const int col = dt * 16 + ((lane >> 4) << 3);
+            ldmatrix_x4_trans(b, vs + swz<D>(key, col));  // transposed: (dims 0-7, keys 0-7), (0-7, 8-15), (8-15, 0-7), (8-15, 8-15)
+            const uint32_t a[4] = {b[0], b[2], b[1], b[3]};
+            mma_bf16(ot[dt], a, pb[kt][0], pb[kt][1]);
+        }
+    }
+}
+
 // ---------------------------------------------------------------------------------------------- decode
-template <int D, int BN, int STAGES, int DW>
+// T8: every tile has at most 8 rows and one token (a decode step of a model with up to 8 heads per group): the transposed form.
+template <int D, int BN, int STAGES, int DW, bool T8>
 __global__ void __launch_bounds__(DW * 32) attn_mma_decode_kernel(const Params p) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -260,23 +345,38 @@ __global__ void __launch_bounds__(DW * 32) attn_mma_decode_kernel(const Params p
 
     int row_pos[2];
     bool row_ok[2];
-    uint32_t qa[D / 16][4];
-#pragma unroll
-    for (int r = 0; r < 2; ++r) {
-        const int row = (lane >> 2) + 8 * r;
-        row_ok[r] = row < nrows;
-        row_pos[r] = pos0 + row / G;
-        const bf16* qp = p.q + (size_t)(n0 + (row_ok[r] ? row / G : 0)) * p.q_stride + (size_t)(kvh * G + (row_ok[r] ? row % G : 0)) * D;
+    uint32_t qa[T8 ? 1 : D / 16][4];   // the queries as A operand (rows lane / 4 and + 8), or ...
+    uint32_t qb[T8 ? D / 16 : 1][2];   // ... transposed, as B operand (row lane / 4 only)
+    float o[T8 ? D / 16 : D / 8][4];
+    if constexpr (T8) {
+        const int row = lane >> 2;
+        const bool ok = row < nrows;
+        const bf16* qp = p.q + (size_t)n0 * p.q_stride + (size_t)(kvh * G + (ok ? row : 0)) * D;
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
             const int col = kk * 16 + ((lane & 3) << 1);
-            qa[kk][r] = row_ok[r] ? *reinterpret_cast<const uint32_t*>(qp + col) : 0u;
-            qa[kk][r + 2] = row_ok[r] ? *reinterpret_cast<const uint32_t*>(qp + col + 8) : 0u;
+            qb[kk][0] = ok ? *reinterpret_cast<const uint32_t*>(qp + col) : 0u;
+            qb[kk][1] = ok ? *reinterpret_cast<const uint32_t*>(qp + col + 8) : 0u;
         }
-    }
-    float o[D / 8][4];
 #pragma unroll
-    for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+        for (int i = 0; i < D / 16; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    } else {
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const int row = (lane >> 2) + 8 * r;
+            row_ok[r] = row < nrows;
+            row_pos[r] = pos0 + row / G;
+            const bf16* qp = p.q + (size_t)(n0 + (row_ok[r] ? row / G : 0)) * p.q_stride + (size_t)(kvh * G + (row_ok[r] ? row % G : 0)) * D;
+#pragma unroll
+            for (int kk = 0; kk < D / 16; ++kk) {
+                const int col = kk * 16 + ((lane & 3) << 1);
+                qa[kk][r] = row_ok[r] ? *reinterpret_cast<const uint32_t*>(qp + col) : 0u;
+                qa[kk][r + 2] = row_ok[r] ? *reinterpret_cast<const uint32_t*>(qp + col + 8) : 0u;
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    }
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
 
 #pragma unroll
@@ -297,10 +397,14 @@ __global__ void __launch_bounds__(DW * 32) attn_mma_decode_kernel(const Params p
         const int key0 = lo + (first + it * DW) * BN;
         // a chunk that lies wholly before the first token's position (and inside every window) needs no mask arithmetic;
         // rows beyond the tile then collect numbers nobody reads
-        if (key0 + BN - 1 <= pos0 && (p.window <= 0 || key0 > hi - 1 - p.window))
-            attend_chunk<D, BN, false>(qa, cur, cur + TILE, o, m, l, key0, row_pos, row_ok, p.window, p.scale_log2, lane);
-        else
-            attend_chunk<D, BN, true>(qa, cur, cur + TILE, o, m, l, key0, row_pos, row_ok, p.window, p.scale_log2, lane);
+        const bool interior = key0 + BN - 1 <= pos0 && (p.window <= 0 || key0 > hi - 1 - p.window);
+        if constexpr (T8) {
+            if (interior) attend_chunk_t8<D, BN, false>(qb, cur, cur + TILE, o, m, l, key0, pos0, nrows, p.window, p.scale_log2, lane);
+            else attend_chunk_t8<D, BN, true>(qb, cur, cur + TILE, o, m, l, key0, pos0, nrows, p.window, p.scale_log2, lane);
+        } else {
+            if (interior) attend_chunk<D, BN, false>(qa, cur, cur + TILE, o, m, l, key0, row_pos, row_ok, p.window, p.scale_log2, lane);
+            else attend_chunk<D, BN, true>(qa, cur, cur + TILE, o, m, l, key0, row_pos, row_ok, p.window, p.scale_log2, lane);
+        }
         __syncwarp();  // every lane is done with the slot
         const int nxt = it + STAGES;
         if (nxt < mine) {
@@ -312,11 +416,18 @@ __global__ void __launch_bounds__(DW * 32) attn_mma_decode_kernel(const Params p
     }
     cp_async_wait<0>();
 #pragma unroll
-    for (int r = 0; r < 2; ++r) {
-        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
-        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+    for (int r = 0; r < 2; ++r) {  // a row's sum over the lanes that hold its keys
+        if constexpr (T8) {
+            l[r] += __shfl_xor_sync(0xffffffffu, l[r], 4);
+            l[r] += __shfl_xor_sync(0xffffffffu, l[r], 8);
+            l[r] += __shfl_xor_sync(0xffffffffu, l[r], 16);
+        } else {
+            l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+            l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+        }
     }
     __syncthreads();  // every warp is done with its ring; the space is reused for the merge
+    constexpr int MR = T8 ? 8 : 16;                     // rows that are merged
     constexpr int WS = D + 8;                           // row stride of the warps' outputs: eight rows written at once spread over the banks
     float* wm = reinterpret_cast<float*>(smem_raw);        // [DW][16] each warp's row maxima
     float* wl = wm + DW * 16;                           // [DW][16] row sums
@@ -325,28 +436,41 @@ __global__ void __launch_bounds__(DW * 32) attn_mma_decode_kernel(const Params p
     float* fm = wo + DW * 16 * WS;                      // merged [16], [16], [16][D]
     float* fl = fm + 16;
     float* fo = fl + 16;
+    if constexpr (T8) {
 #pragma unroll
-    for (int r = 0; r < 2; ++r) {
-        const int row = (lane >> 2) + 8 * r;
-        if ((lane & 3) == 0) { wm[warp * 16 + row] = m[r]; wl[warp * 16 + row] = l[r]; }
+        for (int j = 0; j < 2; ++j) {
+            const int row = ((lane & 3) << 1) + j;
+            if ((lane >> 2) == 0) { wm[warp * 16 + row] = m[j]; wl[warp * 16 + row] = l[j]; }
 #pragma unroll
-        for (int dt = 0; dt < D / 8; ++dt) {
-            const int col = dt * 8 + ((lane & 3) << 1);
-            *reinterpret_cast<float2*>(wo + (warp * 16 + row) * WS + col) = make_float2(o[dt][2 * r], o[dt][2 * r + 1]);
+            for (int dt = 0; dt < D / 16; ++dt) {
+                wo[(warp * 16 + row) * WS + dt * 16 + (lane >> 2)] = o[dt][j];
+                wo[(warp * 16 + row) * WS + dt * 16 + (lane >> 2) + 8] = o[dt][2 + j];
+            }
+        }
+    } else {
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const int row = (lane >> 2) + 8 * r;
+            if ((lane & 3) == 0) { wm[warp * 16 + row] = m[r]; wl[warp * 16 + row] = l[r]; }
+#pragma unroll
+            for (int dt = 0; dt < D / 8; ++dt) {
+                const int col = dt * 8 + ((lane & 3) << 1);
+                *reinterpret_cast<float2*>(wo + (warp * 16 + row) * WS + col) = make_float2(o[dt][2 * r], o[dt][2 * r + 1]);
+            }
         }
     }
     __syncthreads();
     // a row's weights once (not once per output element): exp2(warp's maximum - overall maximum); the row's merged maximum and sum
-    for (int i = tid; i < DW * 16; i += DW * 32) {
-        const int w = i / 16, r = i % 16;
+    for (int i = tid; i < DW * MR; i += DW * 32) {
+        const int w = i / MR, r = i % MR;
         float M = -INFINITY;
 #pragma unroll
         for (int w2 = 0; w2 < DW; ++w2) M = fmaxf(M, wm[w2 * 16 + r]);
-        wf[i] = M > -INFINITY ? fast_exp2(wm[i] - M) : 0.f;
+        wf[w * 16 + r] = M > -INFINITY ? fast_exp2(wm[w * 16 + r] - M) : 0.f;
         if (w == 0) fm[r] = M;
     }
     __syncthreads();
-    for (int i = tid; i < 16 * D; i += DW * 32) {
+    for (int i = tid; i < MR * D; i += DW * 32) {
         const int r = i / D, dim = i % D;
         float O = 0.f;
 #pragma unroll
@@ -525,38 +649,45 @@ __global__ void attn_plan_kernel(const int* __restrict__ starts, int num_seqs, i
     for (; t < max_tiles; ++t) { tile_info[2 * t] = 0; tile_info[2 * t + 1] = 0; }
 }
 
+template <int D, bool T8>
+int launch_decode(const Params& p, dim3 grid, cudaStream_t s) {
+    constexpr int BN = D == 64 ? 32 : 16, STAGES = 3, DW = 8;  // eight warps, each with its own ring of 4 KB + 4 KB chunks
+    constexpr size_t ring = (size_t)DW * STAGES * 2 * BN * D * sizeof(bf16);
+    constexpr size_t merge = (size_t)(DW * 16 * (D + 8 + 3) + 16 * (D + 2)) * sizeof(float);
+    constexpr size_t smem = ring > merge ? ring : merge;
+    static bool set = false;
+    if (!set) {
+        cudaError_t e = cudaFuncSetAttribute(attn_mma_decode_kernel<D, BN, STAGES, DW, T8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        set = true;
+    }
+    if (p.cluster && p.num_splits > 1) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = grid;
+        cfg.blockDim = dim3(DW * 32);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = s;
+        cudaLaunchAttribute attr[2];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 1;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = p.num_splits;
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = llmie_pdl_flag ? 2 : 1;
+        return (int)cudaLaunchKernelEx(&cfg, attn_mma_decode_kernel<D, BN, STAGES, DW, T8>, p);
+    }
+    return launch_kernel(attn_mma_decode_kernel<D, BN, STAGES, DW, T8>, grid, dim3(DW * 32), smem, s, p);
+}
+
 template <int D>
 int launch(const Params& p, int num_tiles, int decode_mode, cudaStream_t s) {
     const dim3 grid(num_tiles, p.nkv, p.num_splits);
     if (decode_mode) {
-        constexpr int BN = D == 64 ? 32 : 16, STAGES = 3, DW = 8;  // eight warps, each with its own ring of 4 KB + 4 KB chunks
-        constexpr size_t ring = (size_t)DW * STAGES * 2 * BN * D * sizeof(bf16);
-        constexpr size_t merge = (size_t)(DW * 16 * (D + 8 + 3) + 16 * (D + 2)) * sizeof(float);
-        constexpr size_t smem = ring > merge ? ring : merge;
-        static bool set = false;
-        if (!set) {
-            cudaError_t e = cudaFuncSetAttribute(attn_mma_decode_kernel<D, BN, STAGES, DW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            if (e != cudaSuccess) return (int)e;
-            set = true;
-        }
-        if (p.cluster && p.num_splits > 1) {
-            cudaLaunchConfig_t cfg = {};
-            cfg.gridDim = grid;
-            cfg.blockDim = dim3(DW * 32);
-            cfg.dynamicSmemBytes = smem;
-            cfg.stream = s;
-            cudaLaunchAttribute attr[2];
-            attr[0].id = cudaLaunchAttributeClusterDimension;
-            attr[0].val.clusterDim.x = 1;
-            attr[0].val.clusterDim.y = 1;
-            attr[0].val.clusterDim.z = p.num_splits;
-            attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-            attr[1].val.programmaticStreamSerializationAllowed = 1;
-            cfg.attrs = attr;
-            cfg.numAttrs = llmie_pdl_flag ? 2 : 1;
-            return (int)cudaLaunchKernelEx(&cfg, attn_mma_decode_kernel<D, BN, STAGES, DW>, p);
-        }
-        return launch_kernel(attn_mma_decode_kernel<D, BN, STAGES, DW>, grid, dim3(DW * 32), smem, s, p);
+        // tiles of one token with up to 8 heads per group: the transposed form, which spends nothing on padding rows
+        const bool t8 = p.tile_info == nullptr && p.nq / p.nkv <= 8;
+        return t8 ? launch_decode<D, true>(p, grid, s) : launch_decode<D, false>(p, grid, s);
     } else {
         constexpr size_t tiles = (size_t)(64 * D + 3 * 2 * 64 * D) * sizeof(bf16);
         constexpr size_t merge = (size_t)(64 * (D + 2)) * sizeof(float);
