@@ -190,6 +190,21 @@ def test_greedy_generation_through_entry_point(models, name, dtype):
     assert eng.preemptions >= 0 and all(pool.num_free == pool.capacity for pool in eng.cache.pools)
 
 
+def test_command_line_generates_the_plain_tokens(models):
+    """``python -m llm_infrence_engine_b200`` with graphs and the pipelined engine: greedy tokens of two prompts, float32."""
+    folder, cfg, w, prompts, want = models[("B", "float32")]
+    ps = [random_prompt(cfg["vocab_size"], n, 90 + n) for n in (5, 23)]
+    cmd = [sys.executable, "-m", "llm_infrence_engine_b200", "--model", str(folder), "--dtype", "float32", "--block-size", "8",
+           "--max-len", "64", "--max-seqs", "4", "--max-new-tokens", "12", "--cuda-graphs", "--pipeline"]
+    for p in ps:
+        cmd += ["--prompt-ids", " ".join(map(str, p))]
+    r = subprocess.run(cmd, capture_output=True, text=True, cwd=str(ROOT))
+    assert r.returncode == 0, r.stderr[-2000:]
+    lines = [json.loads(x) for x in r.stdout.splitlines() if x.startswith("{")]
+    assert [x["token_ids"] for x in lines] == [plain_generate(cfg, w, p, 12) for p in ps]
+    assert all(x["finish_reason"] == "length" for x in lines)
+
+
 def test_trace_run_program(models, tmp_path):
     folder, cfg, w, prompts, want = models[("A", "float32")]
     p = prompts["c"]
