@@ -11,13 +11,20 @@ its own and every live request has one block table per group; the page with id 0
   to the pool at once and their entry in the block table becomes the null page.
 
 Pages come back when a request ends, is preempted, or a window has passed them, and are handed
-out again without being cleared: a position beyond a request's length is never read. The
-reference's allocator (src/miniserve/paged.py:52-135) keeps reference counts for prefix sharing;
-this one has single owners and checks for double frees and lost pages instead.
+out again without being cleared: a position beyond a request's length is never read.
+
+Prefix sharing (off unless asked for; one group of unwindowed pages and no fixed-size state only),
+after the reference's allocator (src/miniserve/paged.py:41-49,85-122, paged_engine.py:102-112,133-134):
+a page that is full of tokens gets the hash of those tokens chained to the hash of the page before
+it. A new request first takes over the pages whose hashes match the leading full pages of its
+tokens (always leaving at least one token to compute), so several requests may hold one page: pages
+carry a count of holders. A hashed page whose last holder has gone stays in the pool as a cached
+page, found again by its hash, until the free list is empty and it is the least recently used.
 """
 from __future__ import annotations
 
-from collections import deque
+import hashlib
+from collections import OrderedDict, deque
 from typing import Dict, Hashable, List, Optional, Sequence
 
 from .spec import NULL_PAGE, PagedKVSpec
@@ -28,14 +35,19 @@ class OutOfPages(Exception):
 
 
 class PagePool:
-    """Free list of one group's pages. Page 0 is never handed out."""
+    """One group's pages: a free list, a count of holders per page, and (with prefix sharing) cached pages by hash.
+    Page 0 is never handed out."""
 
     def __init__(self, num_pages: int):
         if num_pages < 2:
             raise ValueError("a pool needs at least 2 pages (page 0 is the null page)")
         self.num_pages = num_pages
         self._free = deque(range(1, num_pages))
-        self._owner: List[Optional[Hashable]] = [None] * num_pages
+        self._holders: List[List[Hashable]] = [[] for _ in range(num_pages)]  # who holds the page (several with prefix sharing)
+        self._hash: List[Optional[bytes]] = [None] * num_pages
+        self._by_hash: Dict[bytes, int] = {}
+        self._cached: "OrderedDict[int, None]" = OrderedDict()  # hashed pages nobody holds, least recently used first
+        self.evictions = 0
 
     @property
     def capacity(self) -> int:
@@ -43,33 +55,60 @@ class PagePool:
 
     @property
     def num_free(self) -> int:
-        return len(self._free)
+        """Pages that ``allocate`` can hand out: free ones and cached ones that nobody holds."""
+        return len(self._free) + len(self._cached)
 
-    def allocate(self, owner: Hashable) -> int:
-        if not self._free:
+    def allocate(self, owner: Hashable = None) -> int:
+        if self._free:
+            page = self._free.popleft()
+        elif self._cached:
+            page, _ = self._cached.popitem(last=False)  # src/miniserve/paged.py:85-96: evict the least recently used
+            del self._by_hash[self._hash[page]]
+            self._hash[page] = None
+            self.evictions += 1
+        else:
             raise OutOfPages()
-        page = self._free.popleft()
-        self._owner[page] = owner
+        self._holders[page] = [owner]
         return page
 
-    def free(self, page: int, owner: Hashable) -> None:
+    def share(self, page: int, owner: Hashable = None) -> None:
+        """One more holder of a page found by its hash."""
+        if not self._holders[page]:
+            del self._cached[page]
+        self._holders[page].append(owner)
+
+    def free(self, page: int, owner: Hashable = None) -> None:
+        """One holder less. The last one sends the page to the cached pages (if it has a hash) or to the free list."""
         if page == NULL_PAGE or not 0 < page < self.num_pages:
             raise ValueError(f"page {page} cannot be freed")
-        if self._owner[page] is None:
+        if not self._holders[page]:
             raise ValueError(f"page {page} freed twice")
-        if self._owner[page] != owner:
-            raise ValueError(f"page {page} belongs to {self._owner[page]!r}, not to {owner!r}")
-        self._owner[page] = None
-        self._free.append(page)
+        if owner not in self._holders[page]:
+            raise ValueError(f"page {page} belongs to {self._holders[page]!r}, not to {owner!r}")
+        self._holders[page].remove(owner)
+        if not self._holders[page]:
+            if self._hash[page] is not None:
+                self._cached[page] = None
+            else:
+                self._free.append(page)
 
-    def owner(self, page: int) -> Optional[Hashable]:
-        return self._owner[page]
+    def holders(self, page: int) -> int:
+        return len(self._holders[page])
+
+    def set_hash(self, page: int, digest: bytes) -> None:
+        """Name a full page by the hash of its tokens. If another page already has the name, this one stays nameless."""
+        if self._hash[page] is None and digest not in self._by_hash:
+            self._hash[page] = digest
+            self._by_hash[digest] = page
+
+    def lookup(self, digest: bytes) -> Optional[int]:
+        return self._by_hash.get(digest)
 
 
 class _Held:
     """What one live request holds."""
 
-    __slots__ = ("slot", "tables", "length", "versions", "released")
+    __slots__ = ("slot", "tables", "length", "versions", "released", "hashes")
 
     def __init__(self, slot: int, num_groups: int, version: int):
         self.slot = slot
@@ -77,13 +116,18 @@ class _Held:
         self.length = 0  # positions covered so far
         self.versions = [version] * num_groups  # changes whenever the group's table changes; never repeats
         self.released = [0] * num_groups        # pages below this index were given back (windowed groups)
+        self.hashes: List[bytes] = []           # chained hashes of the leading full pages (prefix sharing)
 
 
 class CacheManager:
-    def __init__(self, groups: Sequence[PagedKVSpec], num_pages: int, page_size: int, max_seqs: int):
+    def __init__(self, groups: Sequence[PagedKVSpec], num_pages: int, page_size: int, max_seqs: int, prefix_sharing: bool = False):
         if page_size <= 0:
             raise ValueError("page_size must be positive")
         self.groups = list(groups)
+        # pages can only be shared where a request's pages are all it has: one group, no window (a windowed group gives pages
+        # back as it goes), and the caller says that no fixed-size state exists (``prefix_sharing`` is its promise)
+        self.prefix_sharing = bool(prefix_sharing) and len(self.groups) == 1 and self.groups[0].window is None
+        self.shared_tokens = 0  # tokens that requests found in the cache instead of computing them
         self.page_size = page_size
         self.max_seqs = max_seqs
         self.pools = [PagePool(num_pages) for _ in self.groups]
@@ -135,6 +179,53 @@ class CacheManager:
         self._version += 1
         self._held[req] = _Held(slot, len(self.groups), self._version)
         return slot
+
+    # ------------------------------------------------------------------ prefix sharing
+    def _chain(self, before: bytes, tokens: Sequence[int]) -> bytes:
+        h = hashlib.blake2b(before, digest_size=16)
+        h.update(b"".join(int(t).to_bytes(4, "little", signed=True) for t in tokens))
+        return h.digest()
+
+    def share_prefix(self, req: Hashable, tokens: Sequence[int]) -> int:
+        """Right after ``admit``: take over the cached pages that hold the leading full pages of ``tokens``. Returns how
+        many tokens they cover (a multiple of the page size, and less than ``len(tokens)``: one token at least is left to
+        compute, src/miniserve/paged_engine.py:105-110)."""
+        if not self.prefix_sharing:
+            return 0
+        held = self._held[req]
+        if held.tables[0]:
+            raise ValueError("share_prefix comes before the request's first reserve")
+        pool, ps = self.pools[0], self.page_size
+        digest = b""
+        for i in range((len(tokens) - 1) // ps):
+            digest = self._chain(digest, tokens[i * ps:(i + 1) * ps])
+            page = pool.lookup(digest)
+            if page is None:
+                break
+            pool.share(page, req)
+            held.tables[0].append(page)
+            held.hashes.append(digest)
+        n = len(held.tables[0])
+        if n:
+            held.length = n * ps
+            self._bump(held, 0)
+            self.max_blocks_per_seq = max(self.max_blocks_per_seq, n)
+            self.shared_tokens += n * ps
+        return n * ps
+
+    def register_full_pages(self, req: Hashable, tokens: Sequence[int]) -> None:
+        """``tokens`` (from the request's first) are in the cache: name the pages they fill completely, so that later requests
+        with the same leading tokens find them (src/miniserve/paged_engine.py:133-134)."""
+        if not self.prefix_sharing:
+            return
+        held = self._held[req]
+        pool, ps = self.pools[0], self.page_size
+        full = min(len(tokens) // ps, len(held.tables[0]))
+        while len(held.hashes) < full:
+            i = len(held.hashes)
+            digest = self._chain(held.hashes[-1] if held.hashes else b"", tokens[i * ps:(i + 1) * ps])
+            held.hashes.append(digest)
+            pool.set_hash(held.tables[0][i], digest)
 
     def _first_needed_page(self, group: int, context_len: int) -> int:
         """Index of the first page that a query at position >= context_len can still read."""
@@ -234,16 +325,22 @@ class CacheManager:
         assert not set(slots) & set(self._free_slots), "a state slot is both free and held"
         assert len(slots) + len(self._free_slots) == self.max_seqs, "a state slot is lost"
         for g, pool in enumerate(self.pools):
-            seen: Dict[int, Hashable] = {}
+            holders: Dict[int, int] = {}
             for req, held in self._held.items():
-                for page in held.tables[g]:
-                    if page == NULL_PAGE:
-                        continue
-                    assert page not in seen, f"group {g}: page {page} held by {seen[page]!r} and {req!r}"
-                    seen[page] = req
-                    assert pool.owner(page) == req, f"group {g}: page {page} owner mismatch"
-            free = list(pool._free)
+                mine = [page for page in held.tables[g] if page != NULL_PAGE]
+                assert len(set(mine)) == len(mine), f"group {g}: request {req!r} holds a page twice"
+                for page in mine:
+                    holders[page] = holders.get(page, 0) + 1
+            for page, n in holders.items():
+                assert pool.holders(page) == n, f"group {g}: page {page} has {n} holders, the pool counts {pool.holders(page)}"
+                assert n == 1 or self.prefix_sharing, f"group {g}: page {page} is held {n} times"
+            free, cached = list(pool._free), list(pool._cached)
             assert len(set(free)) == len(free), f"group {g}: a page is in the free list twice"
-            assert not set(free) & set(seen), f"group {g}: a page is both free and held"
-            assert NULL_PAGE not in free and NULL_PAGE not in seen
-            assert len(free) + len(seen) == pool.capacity, f"group {g}: {pool.capacity - len(free) - len(seen)} pages lost"
+            assert not set(free) & set(holders) and not set(cached) & set(holders), f"group {g}: a page is both free and held"
+            assert not set(free) & set(cached), f"group {g}: a page is both free and cached"
+            assert NULL_PAGE not in free and NULL_PAGE not in holders and NULL_PAGE not in cached
+            assert all(pool.holders(page) == 0 for page in free + cached), f"group {g}: a free page has holders"
+            assert all(pool._hash[page] is not None and pool._by_hash[pool._hash[page]] == page for page in cached)
+            assert all(pool._hash[page] is None for page in free), f"group {g}: a free page has a name"
+            lost = pool.capacity - len(free) - len(cached) - len(holders)
+            assert lost == 0, f"group {g}: {lost} pages lost"

@@ -24,6 +24,7 @@ class EngineConfig:
     max_num_batched_tokens: int = 2048  # token budget of one step
     cuda_graphs: bool = False        # replay decode-only steps from captured graphs
     pipeline: bool = False           # launch a step before the host has read the tokens of the step before it
+    prefix_cache: bool = False       # requests take over cached pages that hold their leading tokens (one unwindowed group, no state)
     seed: int = 0                    # engine seed for requests that bring none
 
     def validate(self) -> None:

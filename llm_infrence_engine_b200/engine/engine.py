@@ -42,7 +42,8 @@ def build_runner(folder: Union[str, Path], config: EngineConfig, kernels=None):
     load_weights(spec, folder, dtype, config.device)
     groups, of_entry = group_layout(spec.cache_specs())
     num_pages = config.pool_blocks()
-    cache = CacheManager(groups, num_pages, config.block_size, config.max_seqs)
+    stateless = all(e is not None for e in of_entry)  # every cache entry is paged: no fixed-size state to snapshot
+    cache = CacheManager(groups, num_pages, config.block_size, config.max_seqs, prefix_sharing=config.prefix_cache and stateless)
     runner = ModelRunner(spec, kernels, cache, of_entry, dtype, config.device, num_pages, config.block_size, config.max_seqs,
                          config.max_len, config.cuda_graphs)
     return spec, cache, runner
@@ -195,8 +196,10 @@ class Engine:
             self._read(prev)
 
     def stats(self) -> dict:
-        """src/miniserve/paged_engine.py:68-80, without the prefix-cache figures."""
+        """src/miniserve/paged_engine.py:68-80."""
         return {
+            "prefix_cache": self.cache.prefix_sharing,
+            "prefix_tokens_hit": self.cache.shared_tokens,
             "prefill_tokens_computed": self.prefill_tokens_computed,
             "preemptions": self.preemptions,
             "peak_running": self.peak_running,

@@ -141,20 +141,24 @@ class Scheduler:
             r = self.waiting[0]
             if r.in_flight:
                 break  # preempted with a token still on the device: it comes back once that token has been read
-            pending = r.num_tokens
-            count = min(pending, budget)
             self.cache.admit(r.id)
-            if not self.cache.can_reserve(r.id, 0, count, spare=len(self.running)):
+            # with prefix sharing: the leading full pages that the cache already holds are taken over, not computed
+            # (src/miniserve/paged_engine.py:102-112); at least one token is always left
+            have = self.cache.share_prefix(r.id, r.tokens(0, r.num_tokens))
+            pending = r.num_tokens - have
+            count = min(pending, budget)
+            if not self.cache.can_reserve(r.id, have, have + count, spare=len(self.running)):
                 self.cache.free(r.id)
+                self.cache.shared_tokens -= have  # not admitted after all
                 break
-            self.cache.reserve(r.id, 0, count)
+            self.cache.reserve(r.id, have, have + count)
             self.waiting.popleft()
             self._admit_counter += 1
             r.admit_seq = self._admit_counter
             r.state = "running"
-            r.num_computed = 0
+            r.num_computed = have
             self.running.append(r)
-            plan.items.append(Scheduled(r, 0, count, count == pending))
+            plan.items.append(Scheduled(r, have, count, count == pending))
             plan.admitted += 1
             budget -= count
         return plan
@@ -163,3 +167,7 @@ class Scheduler:
         """The step ran: what it computed is in the cache now."""
         for s in plan.items:
             s.req.num_computed = s.start + s.count
+            if self.cache.prefix_sharing and self.cache.holds(s.req.id):
+                # pages that are now full of tokens the host knows become findable (a token still on the device is not known)
+                known = min(s.req.num_computed, len(s.req.prompt_ids) + len(s.req.output_ids))
+                self.cache.register_full_pages(s.req.id, s.req.tokens(0, known))

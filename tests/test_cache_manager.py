@@ -108,3 +108,98 @@ def test_random_orders(seed):
         m.free(r)
     m.check_invariants()
     assert all(p.num_free == p.capacity for p in m.pools) and m.num_free_slots() == 4
+
+
+def test_prefix_sharing_takes_over_full_pages_and_keeps_one_token():
+    """src/miniserve/paged.py:41-49,114-122, paged_engine.py:102-112,133-134: chained hashes of full pages, holders counted,
+    a page without holders stays findable until it is the least recently used and the free list is empty."""
+    m = CacheManager([PagedKVSpec(2, 16)], num_pages=7, page_size=4, max_seqs=3, prefix_sharing=True)
+    a = list(range(100, 111))                      # 11 tokens: pages [100..103], [104..107] full, [108..110] not
+    m.admit("a")
+    assert m.share_prefix("a", a) == 0             # nothing cached yet
+    m.reserve("a", 0, 11)
+    m.register_full_pages("a", a)
+    ta = list(m.block_table("a", 0))
+    m.check_invariants()
+    # the same 8 leading tokens: both full pages are taken over; a different 5th token: only the first
+    m.admit("b")
+    assert m.share_prefix("b", a[:8] + [7, 7]) == 8 and m.block_table("b", 0) == ta[:2]
+    m.admit("c")
+    assert m.share_prefix("c", a[:4] + [9] + a[5:]) == 4 and m.block_table("c", 0) == ta[:1]
+    assert m.pools[0].holders(ta[0]) == 3 and m.pools[0].holders(ta[1]) == 2 and m.shared_tokens == 12
+    m.check_invariants()
+    m.reserve("b", 8, 10)
+    m.reserve("c", 4, 11)
+    m.check_invariants()
+    # exactly the cached tokens again: one token at least is left to compute
+    m.free("c")
+    m.admit("d")
+    assert m.share_prefix("d", a[:8]) == 4
+    m.free("d")
+    # holders go: the two named pages stay cached, the others are free; everything can be handed out
+    m.free("a")
+    m.free("b")
+    m.check_invariants()
+    pool = m.pools[0]
+    assert pool.num_free == pool.capacity and len(pool._cached) == 2
+    m.admit("e")
+    assert m.share_prefix("e", a) == 8             # found again after their holders had gone
+    m.free("e")
+    m.admit("f")
+    m.reserve("f", 0, 24)                           # all six pages: the cached ones are evicted, oldest first
+    assert pool.evictions == 2 and not pool._cached and not pool._by_hash
+    m.check_invariants()
+    m.free("f")
+    m.admit("g")
+    assert m.share_prefix("g", a) == 0
+    m.free("g")
+    m.check_invariants()
+
+
+def test_prefix_sharing_is_refused_where_pages_are_not_all_a_request_has():
+    win = CacheManager([PagedKVSpec(1, 8), PagedKVSpec(1, 8, window=6)], num_pages=9, page_size=4, max_seqs=1, prefix_sharing=True)
+    assert not win.prefix_sharing
+    one = CacheManager([PagedKVSpec(1, 8, window=6)], num_pages=9, page_size=4, max_seqs=1, prefix_sharing=True)
+    assert not one.prefix_sharing
+    one.admit("a")
+    assert one.share_prefix("a", list(range(20))) == 0
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_orders_with_prefix_sharing(seed):
+    """Requests whose tokens share leading pages come and go in random order: no page lost, no holder miscounted, and a
+    taken-over page always holds exactly the tokens its new holder expects."""
+    rng = random.Random(100 + seed)
+    ps = rng.choice([2, 4])
+    m = CacheManager([PagedKVSpec(1, 8)], num_pages=rng.choice([9, 20]), page_size=ps, max_seqs=4, prefix_sharing=True)
+    stems = [[rng.randrange(5) for _ in range(12)] for _ in range(3)]
+    content = {}  # page -> tokens written there (what a device would hold)
+    live = {}
+    for step in range(400):
+        if live and (len(live) == 4 or rng.random() < 0.4):
+            name = rng.choice(list(live))
+            m.free(name)
+            del live[name]
+        else:
+            name = f"r{step}"
+            toks = list(rng.choice(stems)[:rng.randrange(1, 12)]) + [rng.randrange(5) for _ in range(rng.randrange(1, 6))]
+            m.admit(name)
+            have = m.share_prefix(name, toks)
+            assert have % ps == 0 and have < len(toks)
+            for i, page in enumerate(m.block_table(name, 0)):
+                assert content[page] == toks[i * ps:(i + 1) * ps]
+            if not m.can_reserve(name, have, len(toks)):
+                m.free(name)
+                m.check_invariants()
+                continue
+            m.reserve(name, have, len(toks))
+            for i, page in enumerate(m.block_table(name, 0)):
+                if i * ps >= have:
+                    content[page] = toks[i * ps:(i + 1) * ps]
+            m.register_full_pages(name, toks)
+            live[name] = toks
+        m.check_invariants()
+    for name in list(live):
+        m.free(name)
+    m.check_invariants()
+    assert m.pools[0].num_free == m.pools[0].capacity

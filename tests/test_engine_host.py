@@ -83,3 +83,27 @@ def test_engine_sampled_matches_plain(folders):
     res = eng.generate(prompts, max_new_tokens=6, temperature=0.8, top_k=50, top_p=0.95, seed=7)
     for i, (r, p) in enumerate(zip(res, prompts)):
         assert r.token_ids == plain_generate(cfg, w, p, 6, temperature=0.8, top_k=50, top_p=0.95, seed=7 + i)
+
+
+def test_prefix_cache_gives_the_same_tokens_and_computes_less(folders):
+    """Requests that share leading tokens, with and without the prefix cache: same output, fewer prompt tokens computed;
+    also through preemption (a preempted request finds its own pages again) and with pages evicted under pressure."""
+    cfg, w = plain_load(folders["B"])
+    stem = random_prompt(320, 37, 5)
+    prompts = [stem + random_prompt(320, n, 60 + n) for n in (3, 9, 1, 14)] + [random_prompt(320, 21, 77), stem[:20]]
+    out = {}
+    for on in (False, True):
+        eng = Engine(str(folders["B"]), dtype="float32", device="cpu", kernels=TorchKernels(), block_size=8, num_blocks=16,
+                     max_seqs=3, max_len=96, max_num_batched_tokens=32, prefix_cache=on)
+        reqs = [eng.add_request(Request(p, max_new_tokens=10)) for p in prompts]
+        while eng.has_work():
+            eng.step()
+            eng.cache.check_invariants()
+        out[on] = ([r.output_ids for r in reqs], eng.stats())
+        assert all(pool.num_free == pool.capacity for pool in eng.cache.pools) and eng.cache.num_free_slots() == 3
+    assert out[True][0] == out[False][0] == [plain_generate(cfg, w, p, 10) for p in prompts]
+    off, on = out[False][1], out[True][1]
+    assert not off["prefix_cache"] and off["prefix_tokens_hit"] == 0
+    assert on["prefix_cache"] and on["prefix_tokens_hit"] >= 3 * 32
+    assert on["prefill_tokens_computed"] < off["prefill_tokens_computed"]
+    assert on["preemptions"] + off["preemptions"] > 0  # the pool is small enough that both runs had to preempt
