@@ -127,15 +127,16 @@ class Engine:
         useful = 0
         if plan.items:
             entries = []
+            prev_row = {id(r): i for i, r in enumerate(prev[0])} if prev is not None else {}
             for s in plan.items:
                 r = s.req
                 if r.admitted_time is None:
                     r.admitted_time = now
                 want = (s.count - 1,) if s.samples else ()
                 if s.start + s.count > len(r.prompt_ids) + len(r.output_ids):  # its last token is still on the device
-                    if prev is None or s.count != 1 or r not in prev[0]:
+                    if s.count != 1 or id(r) not in prev_row:
                         raise RuntimeError(f"request {r.id} was scheduled past its known tokens")
-                    entries.append(StepEntry(r.id, [0], s.start, want, from_previous=prev[0].index(r)))
+                    entries.append(StepEntry(r.id, [0], s.start, want, from_previous=prev_row[id(r)]))
                 else:
                     entries.append(StepEntry(r.id, r.tokens(s.start, s.start + s.count), s.start, want))
             logits = self.runner.step(entries, previous_tokens=prev[1] if prev is not None else None)

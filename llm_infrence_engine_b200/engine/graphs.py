@@ -30,10 +30,16 @@ from .step import StateBinding, StepContext, StepEntry, step_layout
 
 
 def bucket_sizes(max_batch: int) -> List[int]:
-    """1, 2, 4, ... up to and including ``max_batch`` (src/miniserve/graph_decode.py:23-30)."""
+    """1, 2, 4, 8, 16, then steps of half a power of two (24, 32, 48, 64, ...) up to and including ``max_batch``.
+
+    The reference pads to powers of two (src/miniserve/graph_decode.py:23-30); above 16 a padded row costs real time
+    in the products, so the steps are finer there. A bucket is captured when a batch first needs it.
+    """
     out, b = [], 1
     while b < max_batch:
         out.append(b)
+        if b >= 16 and b + b // 2 < max_batch:
+            out.append(b + b // 2)
         b *= 2
     out.append(max_batch)
     return out

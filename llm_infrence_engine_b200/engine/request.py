@@ -6,7 +6,7 @@ from dataclasses import dataclass, field
 from typing import List, Optional, Tuple
 
 
-@dataclass
+@dataclass(eq=False)  # a request is itself, not its field values: lists of requests are searched by identity
 class Request:
     prompt_ids: List[int]
     max_new_tokens: int = 64
