@@ -5,15 +5,18 @@
 
 namespace {
 
-// `Params` has: out [tokens][nq * D] bfloat16, part_o [tiles][nkv][splits][ROWS][D] and part_ml [tiles][nkv][splits][ROWS][2]
-// float32 scratch, counters [tiles * nkv] (zero between launches), nq, nkv, num_splits.
-// The block's finished rows are in shared memory as (max, sum, output); write them out, or, with
-// several key slices, store the partial and let the last block of the tile merge all slices.
+// `Params` has: out [tokens][nq * D] bfloat16, part_o [partials][ROWS][D] and part_ml [partials][ROWS][2] float32 scratch,
+// counters (zero between launches), nq.
+// The block's finished rows are in shared memory as (max, sum, output); write them out, or, with several key slices
+// (`num_splits` of them for this tile and key/value head, this block's being number `split`), store the partial and let
+// the last block merge all slices. Slice s keeps its partial at index part_base + s * part_stride; `counter` is the
+// counter of this tile and key/value head.
 template <int D, int ROWS, int THREADS, typename Params>
-__device__ __forceinline__ void finish_tile(const Params& p, const float* row_m, const float* row_l, const float* row_o, int tile,
-                                            int kvh, int split, int n0, int nrows, int G, int* flag_smem) {
+__device__ __forceinline__ void finish_tile(const Params& p, const float* row_m, const float* row_l, const float* row_o, int num_splits,
+                                            size_t part_base, size_t part_stride, int counter, int kvh, int split, int n0, int nrows,
+                                            int G, int* flag_smem) {
     const int tid = threadIdx.x;
-    if (p.num_splits == 1) {
+    if (num_splits == 1) {
         for (int i = tid; i < nrows * D; i += THREADS) {
             const int r = i / D, dim = i % D;
             const float L = row_l[r];
@@ -22,9 +25,8 @@ __device__ __forceinline__ void finish_tile(const Params& p, const float* row_m,
         }
         return;
     }
-    const size_t base = ((size_t)tile * p.nkv + kvh) * p.num_splits;
-    float* po = p.part_o + (base + split) * ROWS * D;
-    float* pml = p.part_ml + (base + split) * ROWS * 2;
+    float* po = p.part_o + (part_base + split * part_stride) * ROWS * D;
+    float* pml = p.part_ml + (part_base + split * part_stride) * ROWS * 2;
     for (int i = tid * 4; i < nrows * D; i += THREADS * 4) *reinterpret_cast<float4*>(po + i) = *reinterpret_cast<const float4*>(row_o + i);
     for (int r = tid; r < nrows; r += THREADS) { pml[2 * r] = row_m[r]; pml[2 * r + 1] = row_l[r]; }
     // The block's partial is complete once every thread has passed the barrier; thread 0 then counts the block in with an
@@ -33,8 +35,8 @@ __device__ __forceinline__ void finish_tile(const Params& p, const float* row_m,
     __syncthreads();
     if (tid == 0) {
         int prev;
-        asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;\n" : "=r"(prev) : "l"(p.counters + tile * p.nkv + kvh) : "memory");
-        *flag_smem = prev == p.num_splits - 1;
+        asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;\n" : "=r"(prev) : "l"(p.counters + counter) : "memory");
+        *flag_smem = prev == num_splits - 1;
     }
     __syncthreads();
     if (!*flag_smem) return;
@@ -45,19 +47,19 @@ __device__ __forceinline__ void finish_tile(const Params& p, const float* row_m,
     float* mx = const_cast<float*>(row_m);                  // [nrows] overall maximum
     for (int r = tid; r < nrows; r += THREADS) {
         float M = -INFINITY;
-        for (int s = 0; s < p.num_splits; ++s) M = fmaxf(M, __ldcg(p.part_ml + (base + s) * ROWS * 2 + 2 * r));
+        for (int s = 0; s < num_splits; ++s) M = fmaxf(M, __ldcg(p.part_ml + (part_base + s * part_stride) * ROWS * 2 + 2 * r));
         mx[r] = M;
     }
     __syncthreads();
-    for (int i = tid; i < nrows * p.num_splits; i += THREADS) {
+    for (int i = tid; i < nrows * num_splits; i += THREADS) {
         const int s = i / nrows, r = i % nrows;
         const float M = mx[r];
-        wgt[i] = M > -INFINITY ? exp2f(__ldcg(p.part_ml + (base + s) * ROWS * 2 + 2 * r) - M) : 0.f;
+        wgt[i] = M > -INFINITY ? exp2f(__ldcg(p.part_ml + (part_base + s * part_stride) * ROWS * 2 + 2 * r) - M) : 0.f;
     }
     __syncthreads();
     for (int r = tid; r < nrows; r += THREADS) {
         float L = 0.f;
-        for (int s = 0; s < p.num_splits; ++s) L = fmaf(__ldcg(p.part_ml + (base + s) * ROWS * 2 + 2 * r + 1), wgt[s * nrows + r], L);
+        for (int s = 0; s < num_splits; ++s) L = fmaf(__ldcg(p.part_ml + (part_base + s * part_stride) * ROWS * 2 + 2 * r + 1), wgt[s * nrows + r], L);
         const_cast<float*>(row_l)[r] = L > 0.f ? 1.f / L : 0.f;
     }
     __syncthreads();
@@ -67,8 +69,8 @@ __device__ __forceinline__ void finish_tile(const Params& p, const float* row_m,
         const int r = i / D, dim = i % D;
         float4 O = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll 4
-        for (int s = 0; s < p.num_splits; ++s) {
-            const float4 a = __ldcg(reinterpret_cast<const float4*>(p.part_o + (base + s) * ROWS * D + i));
+        for (int s = 0; s < num_splits; ++s) {
+            const float4 a = __ldcg(reinterpret_cast<const float4*>(p.part_o + (part_base + s * part_stride) * ROWS * D + i));
             const float w = wgt[s * nrows + r];
             O.x = fmaf(a.x, w, O.x); O.y = fmaf(a.y, w, O.y); O.z = fmaf(a.z, w, O.z); O.w = fmaf(a.w, w, O.w);
         }
@@ -79,7 +81,7 @@ __device__ __forceinline__ void finish_tile(const Params& p, const float* row_m,
         packed.y = *reinterpret_cast<const uint32_t*>(&hi);
         *reinterpret_cast<uint2*>(p.out + (size_t)(n0 + r / G) * p.nq * D + (size_t)(kvh * G + r % G) * D + dim) = packed;
     }
-    if (tid == 0) p.counters[tile * p.nkv + kvh] = 0;  // ready for the next launch
+    if (tid == 0) p.counters[counter] = 0;  // ready for the next launch
 }
 
 }  // namespace

@@ -5,20 +5,26 @@
 // The keys go by in chunks of 64:
 //
 //   S  = Q K^T        tcgen05.mma, A = Q tile (shared memory, K-major), B = key chunk (K-major), D = S in tensor
-//                     memory [128 lanes x 64 columns, float32]; two S buffers, so the product for chunk c + 1 runs
-//                     while the threads are busy with chunk c
+//                     memory [128 lanes x 64 columns, float32]; three S buffers, so the scores run up to two chunks
+//                     ahead of the threads and never keep them waiting
 //   P  = softmax step every thread reads ITS row of S with tcgen05.ld (no shuffles: one thread, one row), masks, keeps
 //                     the running maximum and sum in 32-bit, and writes its row of P as bfloat16 into shared memory
 //                     in the swizzled K-major layout an A operand has
-//   O_c = P V         tcgen05.mma, A = P, B = value chunk as it lies in the cache ([key][dim]: MN-major), D = O_c in
-//                     tensor memory; every thread reads its row of O_c and adds it to its 64 running outputs in
-//                     registers, scaled by exp2(old maximum - new maximum). P and O_c have two buffers each: the
-//                     threads go on to the scores of chunk c + 1 and pick up O_c after that
+//   O += P V          tcgen05.mma, A = P, B = value chunk as it lies in the cache ([key][dim]: MN-major), D = O in
+//                     tensor memory, accumulated over all chunks. P is exp2(score - reference) with a reference that
+//                     follows the row's running maximum lazily: only when the maximum has grown by more than 2^8 over
+//                     the reference does the thread scale its row of O (and its sum) down in tensor memory, between
+//                     two P V products. Softmax does not depend on the reference, P stays below 2^8, and after the
+//                     first chunks a row is hardly ever rescaled; O is read once, at the end. P has two buffers: the
+//                     threads go on to the scores of chunk c + 1 while the tensor core works on P V of chunk c
 //
 //   warps 0-3  the 128 row threads
 //   warp 4     producer: looks up the pages of a chunk in the block table and fetches them by TMA (one box per page
 //              and pool, 128-byte swizzle, no multicast) into two rings of STAGES buffers (keys, values) guarded by mbarriers
 //   warp 5     one lane issues the MMAs and commits them to the barriers the other warps wait on
+//
+// A launch follows a plan made once per step on the device (attn_tc_plan_kernel): which pieces of work there are (a tile,
+// or one slice of a long tile's keys, whose partial result the last slice merges), long pieces first.
 //
 // Keys and values arrive exactly as the cache holds them, so a page's slots behind the sequence's last key may
 // hold anything (another request's old values, NaN). Scores there are replaced (not multiplied) by -inf; the
@@ -34,24 +40,25 @@ namespace {
 
 constexpr int D = 64, BM = 128, BN = 64, STAGES = 3, THREADS = 192;  // STAGES: depth of the key ring and of the value ring
 constexpr int Q_BYTES = BM * D * 2, P_BYTES = BM * BN * 2, K_BYTES = BN * D * 2;
-constexpr int TMEM_COLS = 256;  // S0 [0, 64), S1 [64, 128), O0 [128, 192), O1 [192, 256)
+constexpr int S_BUFS = 3;       // score buffers in tensor memory: the scores run up to two chunks ahead of the softmax
+constexpr int TMEM_COLS = 256;  // S0 [0, 64), S1 [64, 128), S2 [128, 192), O [192, 256)
+constexpr float RESCALE_AFTER = 8.f;  // log2: a row's reference lags its running maximum by at most this much
 constexpr float LOG2E = 1.4426950408889634f;
 
 struct TcParams {
     const bf16* q;          // [tokens][q_stride], query heads first
     const int* block_table; // [table rows][max_blocks]
-    const int* token_seq;   // [tokens] row of the block table
-    const int* positions;   // [tokens]
-    const int* tile_info;   // [tiles][2] = (first token, tokens)
+    const int* work;        // [items][8] = (tile, slice, slices of the tile, item of the tile's first slice, first token, tokens,
+                            //               position of the first token, row of the block table); then the item count
     bf16* out;              // [tokens][nq * D]
-    float* part_o;          // [tiles][nkv][splits][BM][D]   scratch for tiles whose keys are cut into slices
-    float* part_ml;         // [tiles][nkv][splits][BM][2]
+    float* part_o;          // [items][nkv][BM][D]   scratch for tiles whose keys are cut into slices
+    float* part_ml;         // [items][nkv][BM][2]
     int* counters;          // [tiles * nkv], zero between launches
-    int num_splits;
+    int max_items;
     int* error_flag;
     int q_stride, max_blocks, nq, nkv, page_size, window;
     int box_rows;           // rows per TMA box: min(page_size, BN)
-    int num_tiles, first_round;  // first_round: blocks that get an SM of their own (the number of SMs, or all blocks if fewer)
+    int num_tiles;
     float scale_log2;       // softmax scale * log2(e)
 };
 
@@ -95,32 +102,27 @@ __global__ void __launch_bounds__(THREADS, 2) attn_tc_prefill_kernel(const __gri
     uint64_t* k_empty = k_full + STAGES;
     uint64_t* v_full = k_empty + STAGES;
     uint64_t* v_empty = v_full + STAGES;
-    uint64_t* s_ready = v_empty + STAGES;  // [2]
-    uint64_t* p_ready = s_ready + 2;     // [2]: the row threads may finish chunk c + 1 before the P V product of chunk c has begun
-    uint64_t* o_ready = p_ready + 2;     // [2]
-    uint64_t* q_ready = o_ready + 2;
+    uint64_t* s_ready = v_empty + STAGES;  // [S_BUFS]
+    uint64_t* p_ready = s_ready + S_BUFS;     // [2]: the row threads may finish chunk c + 1 before the P V product of chunk c has begun
+    uint64_t* o_ready = p_ready + 2;     // completes once per chunk, after its P V product
+    uint64_t* o_done = o_ready + 1;      // completes once, after the last chunk's P V product
+    uint64_t* q_ready = o_done + 1;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(q_ready + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     volatile int* issued = abort_flag + 1;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    // Which (tile, key/value head) this block takes. Later tiles of a prompt see more keys, so the list runs from the last
-    // tile down; all blocks are resident at once (two to an SM), the first `first_round` one to an SM, the others beside
-    // them in the same order of SMs: those take the list from its short end, so that every SM's two blocks add up alike.
-    const int total = gridDim.x, b = blockIdx.x;
-    const int work = b < p.first_round ? b : total - 1 - (b - p.first_round);
-    const int split = work % p.num_splits, item = work / p.num_splits;
-    const int tile = p.num_tiles - 1 - item / p.nkv;
-    const int kvh = item % p.nkv;
+    // Which piece of work this block takes: item blockIdx.x / nkv of the plan (a tile, or one slice of a tile's keys), for
+    // key/value head blockIdx.x % nkv. The plan lists long pieces first; blocks beyond its end have nothing to do.
+    const int item = blockIdx.x / p.nkv, kvh = blockIdx.x % p.nkv;
 
     if (tid == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(k_full + s, 1); mbar_init(k_empty + s, 1); mbar_init(v_full + s, 1); mbar_init(v_empty + s, 1); }
-        mbar_init(s_ready, 1);
-        mbar_init(s_ready + 1, 1);
+        for (int i = 0; i < S_BUFS; ++i) mbar_init(s_ready + i, 1);
         mbar_init(p_ready, BM / 32);  // one arrival per row warp
         mbar_init(p_ready + 1, BM / 32);
         mbar_init(o_ready, 1);
-        mbar_init(o_ready + 1, 1);
+        mbar_init(o_done, 1);
         mbar_init(q_ready, BM / 32);
         *abort_flag = 0;
         issued[0] = issued[1] = 0;  // key chunks, value chunks whose copies were started
@@ -143,62 +145,76 @@ __global__ void __launch_bounds__(THREADS, 2) attn_tc_prefill_kernel(const __gri
     pdl_trigger();
     pdl_wait();  // queries, keys, values and the step's tables all come from kernels before this one
 
-    const int n0 = p.tile_info[2 * tile];
-    const int ntok = p.tile_info[2 * tile + 1];
+    // everything about the piece comes in one trip to memory: the plan has looked up the tile, its position and its request
+    const int4 job = *reinterpret_cast<const int4*>(p.work + 8 * item);
+    const int4 where = *reinterpret_cast<const int4*>(p.work + 8 * item + 4);
+    const bool idle = item >= p.work[8 * p.max_items];
+    const int tile = idle ? 0 : job.x, split = idle ? 0 : job.y, num_splits = idle ? 1 : job.z;
+    const int n0 = idle ? 0 : where.x;
+    const int ntok = idle ? 0 : where.y;
     const int G = p.nq / p.nkv;
     const int nrows = ntok * G;  // <= BM
-    const int pos0 = ntok > 0 ? p.positions[n0] : 0;
+    const int pos0 = ntok > 0 ? where.z : 0;
     const int hi = pos0 + ntok;  // one past the last visible key
     const int lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
     const int lo_al = lo / p.box_rows * p.box_rows;  // chunks start where a TMA box starts
     // this block's slice of the tile's chunks: [chunk0, chunk0 + chunks), empty for the later slices of a short tile
     const int all_chunks = ntok > 0 ? (hi - lo_al + BN - 1) / BN : 0;
-    const int per_split = (all_chunks + p.num_splits - 1) / p.num_splits;
+    const int per_split = (all_chunks + num_splits - 1) / num_splits;
     const int chunk0 = split * per_split;
     const int chunks = max(0, min(all_chunks, chunk0 + per_split) - chunk0);
-    const int* table = p.block_table + (size_t)(ntok > 0 ? p.token_seq[n0] : 0) * p.max_blocks;
+    const int* table = p.block_table + (size_t)(ntok > 0 ? where.w : 0) * p.max_blocks;
 
     if (warp == 4) {
         // ---------------------------------------------------------------- producer
-        const int boxes = BN / p.box_rows;  // per chunk and pool
-        // Where box i of chunk c lies in the pool (a row of the [pages * heads * page_size, D] matrix): lane i finds out.
-        auto box_row = [&](int c) {
-            int row = 0;
-            if (lane < boxes) {
-                const int key = lo_al + (chunk0 + c) * BN + lane * p.box_rows;
-                const int page = key < hi ? table[key / p.page_size] : 0;  // behind the sequence: any page, its keys are masked
-                row = (page * p.nkv + kvh) * p.page_size + key % p.page_size;
-            }
-            return row;
+        const int boxes = BN / p.box_rows;  // per chunk and pool: 1, 2, 4 or 8
+        // Where the boxes lie in the pool (rows of the [pages * heads * page_size, D] matrix). A look-up in the block table is a
+        // trip to memory, and one per step would set the pace of the whole block. So the warp reads the table for 32 / boxes
+        // chunks at once: lane i learns the row of box i % boxes of the (i / boxes)-th chunk of a group of chunks, one group
+        // ahead of its use, and every step takes its rows from the lanes that hold them.
+        const int box_shift = 31 - __clz(boxes), group_shift = 5 - box_shift;  // boxes and the group are powers of two
+        const int group = 1 << group_shift, my_box = lane & (boxes - 1);
+        auto group_rows = [&](int g) {
+            const int cc = (g << group_shift) + (lane >> box_shift);
+            const int key = lo_al + (chunk0 + cc) * BN + my_box * p.box_rows;
+            const int page = (cc < chunks && key < hi) ? table[key / p.page_size] : 0;  // behind the sequence: any page, its keys are masked
+            return (page * p.nkv + kvh) * p.page_size + key % p.page_size;
         };
         // The keys of chunk c are wanted a chunk earlier than its values (for the scores, made ahead of time) and their
         // stage is free earlier too (after the scores of chunk c - STAGES): step c of this loop fetches the keys of chunk c
         // and the values of chunk c - 1. Lanes 0 .. boxes-1 issue one key box each, the next `boxes` lanes one value box
         // each, all at once: issuing a TMA copy occupies a thread for hundreds of cycles, and a chunk of small pages has
-        // many. The block table is read one step ahead of its use.
+        // many.
         bool ok = true;
-        int row_now = box_row(0), row_before = 0;
+        int rows_before = 0, rows_now = group_rows(0), rows_next = group_rows(1);
         for (int c = 0; c <= chunks && ok; ++c) {
-            const int row_next = c + 1 < chunks ? box_row(c + 1) : 0;
+            if (c > 0 && (c & (group - 1)) == 0) {
+                rows_before = rows_now;
+                rows_now = rows_next;
+                rows_next = group_rows((c >> group_shift) + 1);
+            }
             const bool keys = c < chunks, values = c > 0;
             const int kst = c % STAGES, vst = (c + STAGES - 1) % STAGES;  // stage of chunk c, of chunk c - 1
-            if (lane == 0 && keys && c >= STAGES) ok = mbar_wait(k_empty + kst, ((c / STAGES) & 1) ^ 1, abort_flag, p.error_flag, 11);
-            if (lane == boxes && values && c - 1 >= STAGES) ok = mbar_wait(v_empty + vst, (((c - 1) / STAGES) & 1) ^ 1, abort_flag, p.error_flag, 11);
-            ok = __all_sync(0xffffffffu, ok);
+            const int row_k = __shfl_sync(0xffffffffu, rows_now, (((c & (group - 1)) << box_shift) + my_box) & 31);
+            const int cv = c > 0 ? c - 1 : 0;
+            const int row_v = __shfl_sync(0xffffffffu, (cv >> group_shift) == (c >> group_shift) ? rows_now : rows_before,
+                                          (((cv & (group - 1)) << box_shift) + my_box) & 31);
+            if (lane == 0) {
+                // one lane speaks to the barriers: both stages must be free, then both are told what is coming
+                if (keys && c >= STAGES) ok = mbar_wait(k_empty + kst, ((c / STAGES) & 1) ^ 1, abort_flag, p.error_flag, 11);
+                if (ok && values && c - 1 >= STAGES) ok = mbar_wait(v_empty + vst, (((c - 1) / STAGES) & 1) ^ 1, abort_flag, p.error_flag, 11);
+                if (ok && keys) mbar_expect_tx(k_full + kst, K_BYTES);
+                if (ok && values) mbar_expect_tx(v_full + vst, K_BYTES);
+            }
+            ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
             if (!ok) break;
-            if (lane == 0 && keys) mbar_expect_tx(k_full + kst, K_BYTES);
-            if (lane == boxes && values) mbar_expect_tx(v_full + vst, K_BYTES);
-            const int row_v = __shfl_sync(0xffffffffu, row_before, (lane - boxes) & 31);
-            __syncwarp();
             if (lane < boxes) {
-                if (keys) tma_load_2d(k_s + kst * K_BYTES + lane * p.box_rows * 128, &tmap_k, 0, row_now, k_full + kst);
+                if (keys) tma_load_2d(k_s + kst * K_BYTES + lane * p.box_rows * 128, &tmap_k, 0, row_k, k_full + kst);
             } else if (lane < 2 * boxes) {
                 if (values) tma_load_2d(v_s + vst * K_BYTES + (lane - boxes) * p.box_rows * 128, &tmap_v, 0, row_v, v_full + vst);
             }
             __syncwarp();
             if (lane == 0) { if (keys) issued[0] = c + 1; if (values) issued[1] = c; }
-            row_before = row_now;
-            row_now = row_next;
         }
     } else if (warp == 5) {
         // ---------------------------------------------------------------- MMA issuer
@@ -210,32 +226,44 @@ __global__ void __launch_bounds__(THREADS, 2) attn_tc_prefill_kernel(const __gri
             auto issue_s = [&](int c) {
                 const uint64_t k_desc = umma_desc(smem_u32(k_s + (c % STAGES) * K_BYTES));
 #pragma unroll
-                for (int k = 0; k < D / 16; ++k) umma_bf16(tmem + (c & 1) * BN, q_desc + 2 * k, k_desc + 2 * k, idesc_s, k > 0 ? 1u : 0u);
-                umma_commit(s_ready + (c & 1));
+                for (int k = 0; k < D / 16; ++k) umma_bf16(tmem + (c % S_BUFS) * BN, q_desc + 2 * k, k_desc + 2 * k, idesc_s, k > 0 ? 1u : 0u);
+                umma_commit(s_ready + c % S_BUFS);
                 umma_commit(k_empty + c % STAGES);
             };
-            bool ok = mbar_wait(q_ready, 0, abort_flag, p.error_flag, 12) && mbar_wait(k_full, 0, abort_flag, p.error_flag, 13);
-            if (ok) {
-                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                issue_s(0);
-            }
-            int s_next = 1;  // the next chunk whose scores are to be made
-            for (int c = 0; c < chunks && ok; ++c) {
-                if (s_next == c) {
-                    // the keys of this chunk had not come while the chunk before was waited for: now nothing else can go on
-                    ok = mbar_wait(k_full + c % STAGES, (c / STAGES) & 1, abort_flag, p.error_flag, 13);
-                    if (!ok) break;
-                    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                    issue_s(s_next++);
+            // Scores are made as early as their keys and a buffer allow: S(n) goes into the buffer that S(n - S_BUFS) left, and
+            // the rows have read that one by the time they hand over P(n - S_BUFS). After the last chunk comes one commit
+            // without a product: the rows wait for "S(c + 1)" before they overwrite P(c - 2), because a commit completes only
+            // after everything this thread issued before it, and P V of chunk c - 2 is among that.
+            int s_next = 0;
+            auto more_scores = [&](int upto, bool wait) {
+                while (s_next <= upto && s_next <= chunks) {
+                    if (s_next < chunks) {
+                        uint64_t* bar = k_full + s_next % STAGES;
+                        const uint32_t parity = (s_next / STAGES) & 1;
+                        if (wait) {
+                            if (!mbar_wait(bar, parity, abort_flag, p.error_flag, 13)) return false;
+                        } else if (!mbar_try_wait(bar, parity)) {
+                            break;
+                        }
+                        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                        issue_s(s_next);
+                    } else {
+                        umma_commit(s_ready + s_next % S_BUFS);
+                    }
+                    ++s_next;
+                    wait = false;
                 }
-                // Until P of this chunk is there, make the scores of the next chunk as soon as its keys have landed, whichever
-                // comes first. (S buffer (c + 1) & 1 held chunk c - 1, whose rows every thread had read before p_ready of c - 1.)
+                return true;
+            };
+            bool ok = mbar_wait(q_ready, 0, abort_flag, p.error_flag, 12) && more_scores(S_BUFS - 1, true);
+            for (int c = 0; c < chunks && ok; ++c) {
+                // Until P of this chunk is there: the scores of the chunks up to c + 2, as their keys land (the rows have handed
+                // over P(c - 1), so the buffer of S(c - 1) is free). The rows wait for S(c + 1) before they hand over P(c), and
+                // this loop is where it gets made. (Sleeping on one barrier after the other instead of polling all of them was
+                // measured slower.)
                 bool p_there = false;
                 for (uint32_t i = 0; i < SPIN_LIMIT && !p_there; ++i) {
-                    if (s_next == c + 1 && s_next < chunks && mbar_try_wait(k_full + s_next % STAGES, (s_next / STAGES) & 1)) {
-                        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                        issue_s(s_next++);
-                    }
+                    more_scores(c + S_BUFS - 1, false);
                     p_there = mbar_try_wait(p_ready + (c & 1), (c >> 1) & 1) && mbar_try_wait(v_full + c % STAGES, (c / STAGES) & 1);
                     if (*abort_flag) break;
                     if (!p_there && i > 64) __nanosleep(40);
@@ -250,8 +278,9 @@ __global__ void __launch_bounds__(THREADS, 2) attn_tc_prefill_kernel(const __gri
                 const uint64_t p_desc = umma_desc(smem_u32(p_s + (c & 1) * P_BYTES));
 #pragma unroll
                 for (int k = 0; k < BN / 16; ++k)  // 16 keys per step: 32 bytes along a row of P, 2048 bytes down the values
-                    umma_bf16(tmem + 2 * BN + (c & 1) * D, p_desc + 2 * k, umma_desc_mn(v_addr + k * 2048), idesc_o, k > 0 ? 1u : 0u);
-                umma_commit(o_ready + (c & 1));
+                    umma_bf16(tmem + S_BUFS * BN, p_desc + 2 * k, umma_desc_mn(v_addr + k * 2048), idesc_o, (c > 0 || k > 0) ? 1u : 0u);
+                umma_commit(o_ready);
+                if (c == chunks - 1) umma_commit(o_done);
                 umma_commit(v_empty + c % STAGES);
             }
         }
@@ -273,31 +302,18 @@ __global__ void __launch_bounds__(THREADS, 2) attn_tc_prefill_kernel(const __gri
             __syncwarp();
             if (lane == 0) mbar_arrive(q_ready);
         }
-        float o[D];
-#pragma unroll
-        for (int i = 0; i < D; ++i) o[i] = 0.f;
-        float m = -INFINITY, l = 0.f;
+        // m: the row's running maximum (log2 units); ref: what P is taken relative to (-inf until the row has seen a key);
+        // l: the row's sum of P relative to ref
+        float m = -INFINITY, ref = -INFINITY, l = 0.f;
         const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
-        bool ok = true;
-        float corr_before = 0.f;
-        auto take_outputs = [&](int c, float corr) {
-            if (!__all_sync(0xffffffffu, mbar_wait(o_ready + (c & 1), (c >> 1) & 1, abort_flag, p.error_flag, 16))) return false;
-            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-            uint32_t v[D];
-#pragma unroll
-            for (int j = 0; j < D; j += 16) tmem_ld16(lane_base + 2 * BN + (c & 1) * D + j, v + j);
-            asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-#pragma unroll
-            for (int i = 0; i < D; ++i) o[i] = fmaf(o[i], corr, __uint_as_float(v[i]));
-            return true;
-        };
-        for (int c = 0; c < chunks; ++c) {
-            ok = __all_sync(0xffffffffu, mbar_wait(s_ready + (c & 1), (c >> 1) & 1, abort_flag, p.error_flag, 15));
-            if (!ok) break;
+        const uint32_t o_addr = lane_base + S_BUFS * BN;
+        // the scores of chunk c are waited for during chunk c - 1 (see below): only the first ones here
+        bool ok = chunks == 0 || __all_sync(0xffffffffu, mbar_wait(s_ready, 0, abort_flag, p.error_flag, 15));
+        for (int c = 0; c < chunks && ok; ++c) {
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
             uint32_t s[BN];
 #pragma unroll
-            for (int j = 0; j < BN; j += 16) tmem_ld16(lane_base + (c & 1) * BN + j, s + j);
+            for (int j = 0; j < BN; j += 16) tmem_ld16(lane_base + (c % S_BUFS) * BN + j, s + j);
             asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
             const int key0 = lo_al + (chunk0 + c) * BN;
             // A chunk that every row of the tile sees in full needs no mask arithmetic (rows beyond the tile have zero
@@ -319,10 +335,41 @@ __global__ void __launch_bounds__(THREADS, 2) attn_tc_prefill_kernel(const __gri
                 }
             }
             const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-            const float m_new = fmaxf(m, mx * p.scale_log2);
-            const float use = m_new == -INFINITY ? 0.f : m_new;
-            const float corr = fast_exp2(m - use);
-            m = m_new;
+            m = fmaxf(m, mx * p.scale_log2);
+            // The reference follows the maximum only when it lags too far behind: then this row of O and the row's sum are
+            // scaled down. The first keys a row sees set its reference for free (everything so far was zero).
+            float corr = 1.f;
+            bool rescale = false;
+            if (ref == -INFINITY) {
+                ref = m;
+            } else if (m - ref > RESCALE_AFTER) {
+                corr = fast_exp2(ref - m);
+                ref = m;
+                rescale = true;
+            }
+            const float use = ref == -INFINITY ? 0.f : ref;
+            // The scores of the next chunk (after the last chunk: a commit that stands for them) were issued after the P V
+            // product of chunk c - 2, and a commit completes only after everything issued before it. So from here on
+            // that product is over: its P buffer may be overwritten below, and the barrier of the P V products is at most
+            // one phase behind. The scores themselves were made a chunk ago; this wait hardly ever waits.
+            ok = __all_sync(0xffffffffu, mbar_wait(s_ready + (c + 1) % S_BUFS, ((c + 1) / S_BUFS) & 1, abort_flag, p.error_flag, 15));
+            if (!ok) break;
+            if (__any_sync(0xffffffffu, rescale)) {
+                // O holds the products up to chunk c - 1 (there is one: a row's first chunk never gets here). The product
+                // of chunk c waits for this chunk's P, so nothing else touches O meanwhile.
+                ok = __all_sync(0xffffffffu, mbar_wait(o_ready, (c - 1) & 1, abort_flag, p.error_flag, 16));
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                uint32_t v[D];
+#pragma unroll
+                for (int j = 0; j < D; j += 16) tmem_ld16(o_addr + j, v + j);
+                asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+                for (int i = 0; i < D; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * corr);
+#pragma unroll
+                for (int j = 0; j < D; j += 16) tmem_st16(o_addr + j, v + j);
+                asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
+            }
             // all 64 exponentials first, in place and independent of each other (the special-function unit is the narrow
             // place of this loop and must not wait for the sums and stores that follow)
 #pragma unroll
@@ -352,16 +399,24 @@ __global__ void __launch_bounds__(THREADS, 2) attn_tc_prefill_kernel(const __gri
             asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
             __syncwarp();  // every lane's writes (and reads of S) are done and fenced: one arrival speaks for the warp
             if (lane == 0) mbar_arrive(p_ready + (c & 1));
-            // The outputs of the chunk before are picked up now, while the tensor core is busy with this chunk's P V:
-            // o = o * corr(c - 1) + O(c - 1), in the order of the chunks.
-            if (c > 0) {
-                ok = take_outputs(c - 1, corr_before);
-                if (!ok) break;
-            }
-            corr_before = corr;
         }
-        if (ok && chunks > 0) ok = take_outputs(chunks - 1, corr_before);
-        if (ok && p.num_splits == 1) {
+        // the row's outputs, once: everything the tensor core has added up, relative to ref like the sum
+        float o[D];
+#pragma unroll
+        for (int i = 0; i < D; ++i) o[i] = 0.f;
+        if (ok && chunks > 0) {
+            ok = __all_sync(0xffffffffu, mbar_wait(o_done, 0, abort_flag, p.error_flag, 16));
+            if (ok) {
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                uint32_t v[D];
+#pragma unroll
+                for (int j = 0; j < D; j += 16) tmem_ld16(o_addr + j, v + j);
+                asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+                for (int i = 0; i < D; ++i) o[i] = __uint_as_float(v[i]);
+            }
+        }
+        if (ok && num_splits == 1) {
             if (row_ok) {
                 const float inv = l > 0.f ? 1.f / l : 0.f;
                 uint4* dst = reinterpret_cast<uint4*>(p.out + (size_t)(n0 + tok) * p.nq * D + (size_t)(kvh * G + row % G) * D);
@@ -379,7 +434,7 @@ __global__ void __launch_bounds__(THREADS, 2) attn_tc_prefill_kernel(const __gri
             float* fm = reinterpret_cast<float*>(p_s);
             float* fl = fm + BM;
             float* fo = fl + BM;
-            fm[row] = m;
+            fm[row] = ref;  // what the sum and the outputs are relative to
             fl[row] = l;
 #pragma unroll
             for (int i = 0; i < D; i += 4) *reinterpret_cast<float4*>(fo + row * D + i) = make_float4(o[i], o[i + 1], o[i + 2], o[i + 3]);
@@ -402,34 +457,146 @@ __global__ void __launch_bounds__(THREADS, 2) attn_tc_prefill_kernel(const __gri
     }
     __syncthreads();
     if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "n"(TMEM_COLS) : "memory");
-    if (p.num_splits > 1 && !*abort_flag) {
+    if (num_splits > 1 && !*abort_flag) {
         float* fm = reinterpret_cast<float*>(p_s);
         __shared__ int last_flag;
-        finish_tile<D, BM, THREADS>(p, fm, fm + BM, fm + 2 * BM, tile, kvh, split, n0, nrows, G, &last_flag);
+        finish_tile<D, BM, THREADS>(p, fm, fm + BM, fm + 2 * BM, num_splits, (size_t)job.w * p.nkv + kvh, (size_t)p.nkv, tile * p.nkv + kvh, kvh,
+                                    split, n0, nrows, G, &last_flag);
+    }
+}
+
+// The plan of a launch: which tiles' keys are cut into how many slices, and in which order the pieces start.
+//
+// A tile's chunks run one after the other (about a microsecond each), so the longest tile sets the time of the launch while
+// most SMs have long finished: a prompt's last tiles see all its keys, its first ones almost none. `capacity` pieces can be
+// on the device at once (two blocks per SM, divided by the key/value heads that every piece is run for). The plan finds the
+// smallest piece length L >= MIN_SLICE chunks for which cutting every tile into pieces of at most L chunks gives no more
+// than `capacity` pieces. A slice costs about SLICE_COST chunks' time on top of its chunks (its partial result goes through
+// memory and the last slice merges them), so tiles are only cut if L + SLICE_COST is less than the longest tile. The
+// pieces are listed long tiles first, so that whatever does not fit at once starts in the order of its length.
+// With fixed_splits > 0 every tile is cut into that many slices instead (empty ones included).
+constexpr int MIN_SLICE = 8, SLICE_COST = 8, MAX_SLICES = 16, PLAN_THREADS = 256;
+
+__global__ void __launch_bounds__(PLAN_THREADS) attn_tc_plan_kernel(const int* __restrict__ tile_info, int num_tiles, const int* __restrict__ positions,
+                                                                    const int* __restrict__ token_seq, int window, int box_rows, int capacity, int fixed_splits, int max_items,
+                                                                    int* __restrict__ work, int* __restrict__ tmp) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ int red[PLAN_THREADS];
+    __shared__ int piece;
+    const int tid = threadIdx.x;
+    int* chunks = tmp;               // [tiles]
+    int* order = tmp + num_tiles;    // [tiles] tiles by falling length
+    int* first = order + num_tiles;  // [tiles] item of the tile's first slice
+    int longest = 0;
+    for (int t = tid; t < num_tiles; t += PLAN_THREADS) {
+        const int n0 = tile_info[2 * t], ntok = tile_info[2 * t + 1];
+        int c = 0;
+        if (ntok > 0) {
+            const int pos0 = positions[n0], hi = pos0 + ntok;
+            const int lo = window > 0 ? max(0, pos0 - window + 1) : 0;
+            c = (hi - lo / box_rows * box_rows + BN - 1) / BN;
+        }
+        chunks[t] = c;
+        longest = max(longest, c);
+    }
+    red[tid] = longest;
+    __syncthreads();
+    for (int w = PLAN_THREADS / 2; w > 0; w >>= 1) { if (tid < w) red[tid] = max(red[tid], red[tid + w]); __syncthreads(); }
+    longest = red[0];
+    __syncthreads();
+    auto slices_of = [&](int c, int L) { return fixed_splits > 0 ? fixed_splits : max(1, min(MAX_SLICES, (c + L - 1) / L)); };
+    auto pieces = [&](int L) {  // how many pieces a piece length of L gives (the same value in every thread)
+        int n = 0;
+        for (int t = tid; t < num_tiles; t += PLAN_THREADS) n += slices_of(chunks[t], L);
+        red[tid] = n;
+        __syncthreads();
+        for (int w = PLAN_THREADS / 2; w > 0; w >>= 1) { if (tid < w) red[tid] += red[tid + w]; __syncthreads(); }
+        n = red[0];
+        __syncthreads();
+        return n;
+    };
+    int lo_len = MIN_SLICE, hi_len = max(MIN_SLICE, longest);  // pieces(hi_len) is the number of tiles: the least there is
+    if (fixed_splits <= 0 && pieces(hi_len) <= min(capacity, max_items)) {
+        while (lo_len < hi_len) {
+            const int mid = (lo_len + hi_len) / 2;
+            if (pieces(mid) <= min(capacity, max_items)) hi_len = mid; else lo_len = mid + 1;
+        }
+    }
+    if (tid == 0) piece = hi_len + SLICE_COST < longest ? hi_len : max(MIN_SLICE, longest);
+    __syncthreads();
+    const int L = piece;
+    // Order: by falling number of chunks (ties by tile number; later tiles of a prompt are the longer ones). Every thread
+    // ranks its tiles against all others; beyond a few thousand tiles the list stays in reverse tile order.
+    const bool sort = fixed_splits <= 0 && num_tiles <= 2048;
+    for (int t = tid; t < num_tiles; t += PLAN_THREADS) {
+        int rank = num_tiles - 1 - t;
+        if (sort) {
+            rank = 0;
+            const int c = chunks[t];
+            for (int u = 0; u < num_tiles; ++u) rank += chunks[u] > c || (chunks[u] == c && u > t);
+        }
+        order[rank] = t;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        int item = 0;
+        for (int r = 0; r < num_tiles; ++r) {
+            const int t = order[r];
+            first[t] = item;
+            item += slices_of(chunks[t], L);
+        }
+        work[8 * max_items] = min(item, max_items);
+    }
+    __syncthreads();
+    for (int t = tid; t < num_tiles; t += PLAN_THREADS) {
+        const int n = slices_of(chunks[t], L);
+        const int n0 = tile_info[2 * t], ntok = tile_info[2 * t + 1];
+        const int4 where = make_int4(n0, ntok, ntok > 0 ? positions[n0] : 0, ntok > 0 ? token_seq[n0] : 0);
+        for (int k = 0; k < n; ++k) {
+            const int item = first[t] + k;
+            if (item < max_items) {
+                *reinterpret_cast<int4*>(work + 8 * item) = make_int4(t, k, n, first[t]);
+                *reinterpret_cast<int4*>(work + 8 * item + 4) = where;
+            }
+        }
     }
 }
 
 }  // namespace
 
+// The plan for llmie_paged_attention_tc (see attn_tc_plan_kernel): work [8 * max_items + 1] receives the pieces and their number,
+// tmp [3 * num_tiles] is scratch. capacity: pieces that can run at once. max_items >= num_tiles * max(1, fixed_splits).
+LLMIE_API int llmie_attn_tc_plan(const int* tile_info, int num_tiles, const int* positions, const int* token_seq, int window, int page_size,
+                                 int capacity, int fixed_splits, int max_items, int* work, int* tmp, cudaStream_t s) {
+    if (num_tiles <= 0) return 0;
+    if (!tile_info || !positions || !token_seq || !work || !tmp || page_size <= 0 || capacity <= 0 || fixed_splits < 0 || fixed_splits > MAX_SLICES ||
+        max_items < (long long)num_tiles * (fixed_splits > 0 ? fixed_splits : 1) || ((uintptr_t)work & 15))
+        return LLMIE_ERR_BAD_ARGUMENT;
+    return launch_kernel(attn_tc_plan_kernel, dim3(1), dim3(PLAN_THREADS), 0, s, tile_info, num_tiles, positions, token_seq, window,
+                         page_size < BN ? page_size : BN, capacity, fixed_splits, max_items, work, tmp);
+}
+
 // Attention of prompt portions over the paged cache on the tcgen05 tensor cores: head size 64, bfloat16, up to 128 rows
-// (tokens x heads of a group) per tile as listed in tile_info. page_size must be a multiple of 8 that divides 64 or is a
-// multiple of 64. Pools: [pages][nkv][page_size][64]. With num_splits > 1 the keys of every tile are cut into that many slices,
-// one block each, which meet in scratch_o [tiles * nkv * splits * 128 * 64] and scratch_ml [tiles * nkv * splits * 128 * 2]
-// floats; the block that finishes a tile last (counters [tiles * nkv], zero before and after) merges them.
+// (tokens x heads of a group) per tile. page_size must be a multiple of 8 that divides 64 or is a multiple of 64. Pools:
+// [pages][nkv][page_size][64]. `work` is the plan that llmie_attn_tc_plan made for the step's num_tiles tiles, its positions,
+// this window and page size, with the same max_items. The slices of a tile meet in scratch_o [max_items * nkv * 128 * 64]
+// and scratch_ml [max_items * nkv * 128 * 2] floats; the block that finishes a tile last (counters [tiles * nkv], zero before and
+// after) merges them.
 LLMIE_API int llmie_paged_attention_tc(const bf16* q, int q_stride, const bf16* k_pool, const bf16* v_pool, long long pool_pages,
-                                       const int* block_table, int max_blocks, const int* token_seq, const int* positions,
-                                       const int* tile_info, int num_tiles, bf16* out, float* scratch_o, float* scratch_ml, int* counters,
-                                       int nq, int nkv, int d, int page_size, float scale, int window, int num_splits, int* error_flag,
-                                       cudaStream_t s) {
+                                       const int* block_table, int max_blocks, int num_tiles, const int* work, int max_items, bf16* out, float* scratch_o,
+                                       float* scratch_ml, int* counters, int nq, int nkv, int d, int page_size, float scale, int window,
+                                       int* error_flag, cudaStream_t s) {
     if (num_tiles <= 0) return 0;
     if (d != D || nkv <= 0 || nq % nkv || nq / nkv > BM || page_size <= 0 || page_size % 8 || q_stride % 8 ||
-        !(BN % page_size == 0 || page_size % BN == 0) || !tile_info || !error_flag || pool_pages <= 0 || ((uintptr_t)q & 15) ||
-        ((uintptr_t)out & 15) || pool_pages * nkv * page_size > 0x7fffffffLL || num_splits < 1 || num_splits > 16 ||
-        (num_splits > 1 && (!scratch_o || !scratch_ml || !counters)))
+        !(BN % page_size == 0 || page_size % BN == 0) || !error_flag || pool_pages <= 0 || ((uintptr_t)q & 15) ||
+        ((uintptr_t)out & 15) || pool_pages * nkv * page_size > 0x7fffffffLL || !work || ((uintptr_t)work & 15) || max_items < num_tiles ||
+        !scratch_o || !scratch_ml || !counters)
         return LLMIE_ERR_BAD_ARGUMENT;
     TcParams p;
-    p.q = q; p.block_table = block_table; p.token_seq = token_seq; p.positions = positions; p.tile_info = tile_info; p.out = out;
-    p.error_flag = error_flag; p.part_o = scratch_o; p.part_ml = scratch_ml; p.counters = counters; p.num_splits = num_splits; p.q_stride = q_stride; p.max_blocks = max_blocks; p.nq = nq; p.nkv = nkv; p.page_size = page_size;
+    p.q = q; p.block_table = block_table; p.work = work;
+    p.out = out; p.error_flag = error_flag; p.part_o = scratch_o; p.part_ml = scratch_ml; p.counters = counters; p.max_items = max_items;
+    p.q_stride = q_stride; p.max_blocks = max_blocks; p.nq = nq; p.nkv = nkv; p.page_size = page_size; p.num_tiles = num_tiles;
     p.window = window; p.box_rows = page_size < BN ? page_size : BN; p.scale_log2 = scale * LOG2E;
     CUtensorMap mk, mv;
     const int rows = (int)(pool_pages * nkv * page_size);
@@ -444,14 +611,7 @@ LLMIE_API int llmie_paged_attention_tc(const bf16* q, int q_stride, const bf16* 
         if (e != cudaSuccess) return (int)e;
         set = true;
     }
-    static int num_sms = 0;
-    if (!num_sms) {
-        int dev = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return LLMIE_ERR_BAD_ARGUMENT;
-    }
-    const long long blocks = (long long)num_tiles * nkv * num_splits;
+    const long long blocks = (long long)max_items * nkv;
     if (blocks > 0x7fffffffLL) return LLMIE_ERR_BAD_ARGUMENT;
-    p.num_tiles = num_tiles;
-    p.first_round = blocks < num_sms ? (int)blocks : num_sms;
     return launch_kernel(attn_tc_prefill_kernel, dim3((unsigned)blocks), dim3(THREADS), smem, s, mk, mv, p);
 }

@@ -45,9 +45,9 @@ class CudaKernels:
         self.use_cublas = True
         self._attn_scratch: Optional[torch.Tensor] = None
         self._attn_counters: Optional[torch.Tensor] = None
+        self._retired: list = []
         self.use_mma_attention = True
         self.use_tc_attention = True   # prompt portions of head size 64: scores and outputs through tcgen05 and tensor memory
-        self.tc_attention_max_splits = 16
         self.cluster_merge = True      # decode attention: the key slices of a token form a cluster and merge in shared memory
         self.use_tc_gemm = True
         self.tc_max_rows = 128        # batches up to this many rows take the small-batch tensor-core product
@@ -58,7 +58,7 @@ class CudaKernels:
         self._error_flag: Optional[torch.Tensor] = None
         self.num_sms = torch.cuda.get_device_properties(0).multi_processor_count or NUM_SMS_FALLBACK
         for fn in ("llmie_embed", "llmie_feed_tokens", "llmie_rope_tables", "llmie_add_rmsnorm", "llmie_rope_kv_write", "llmie_silu_mul",
-                   "llmie_gemm_simt", "llmie_gemm_tc", "llmie_add_into", "llmie_attn_plan", "llmie_paged_attention_mma", "llmie_paged_attention_tc", "llmie_paged_attention_f32", "llmie_paged_attention_bf16", "llmie_argmax", "llmie_sample"):
+                   "llmie_gemm_simt", "llmie_gemm_tc", "llmie_add_into", "llmie_attn_plan", "llmie_attn_tc_plan", "llmie_paged_attention_mma", "llmie_paged_attention_tc", "llmie_paged_attention_f32", "llmie_paged_attention_bf16", "llmie_argmax", "llmie_sample"):
             getattr(self.lib, fn).restype = ctypes.c_int
         # kernels of a step overlap their set-up with the tail of the kernel before (programmatic dependent launch)
         self.lib.llmie_set_pdl(0 if os.environ.get("LLMIE_PDL", "1") == "0" else 1)
@@ -316,6 +316,8 @@ class CudaKernels:
 
     def _scratch(self, floats: int, device) -> torch.Tensor:
         if self._attn_scratch is None or self._attn_scratch.numel() < floats or self._attn_scratch.device != device:
+            if self._attn_scratch is not None:
+                self._retired.append(self._attn_scratch)  # a captured graph may still write there: never given back
             self._attn_scratch = torch.empty(max(floats, 1 << 20), dtype=torch.float32, device=device)
         return self._attn_scratch
 
@@ -379,29 +381,34 @@ class CudaKernels:
         if not (self.use_tc_attention and head_dim == 64 and batch.max_seq_len > 1 and group <= 128 and page_size % 8 == 0
                 and (64 % page_size == 0 or page_size % 64 == 0) and (num_splits is None or 1 <= num_splits <= 16)):
             return None
-        tiles = sum(-(-n // (128 // group)) for n in batch.seq_lens)
-        blocks, chunks = max(1, tiles * num_kv_heads), -(-span // 64)
-        if num_splits is None:
-            # A tile's chunks run one after the other, about a microsecond each. While the blocks would leave SMs idle, the
-            # keys of every tile are cut into slices that run side by side on SMs of their own and meet in scratch memory
-            # (measured: slices that have to share SMs cost more than they bring).
-            num_splits = max(1, min(self.tc_attention_max_splits, chunks // 8, self.num_sms // blocks))
         tiles, tile_info = self._tiles(batch, 128 // group, qkv.device)
-        scratch_o = scratch_ml = counters = None
-        if num_splits > 1:
-            cells = tiles * num_kv_heads * num_splits * 128
-            buf = self._scratch(cells * (head_dim + 2), qkv.device)
-            scratch_o, scratch_ml = buf, buf[cells * head_dim:]
-            if tiles * num_kv_heads > (1 << 20):
-                return None
-            if self._attn_counters is None or self._attn_counters.device != qkv.device:
-                self._attn_counters = torch.zeros(1 << 20, dtype=torch.int32, device=qkv.device)
-            counters = self._attn_counters
+        if tiles * num_kv_heads > (1 << 20):
+            return None
+        # A tile's chunks run one after the other, about a microsecond each, and a prompt's last tiles have many times the
+        # chunks of its first ones. The plan (made on the device from the step's positions, once per step) cuts the keys of
+        # long tiles into slices, as many pieces as fit on the device at once (two blocks per SM), and starts long pieces first.
+        fixed = int(num_splits or 0)
+        capacity = max(1, 2 * self.num_sms // num_kv_heads)
+        # (tiles of up to 16 chunks are never cut: a slice costs about 8 chunks' time and is at least 8 chunks long)
+        max_items = tiles * fixed if fixed else max(tiles, min(capacity, 16 * tiles)) if span > 16 * 64 else tiles
+        key = ("tcgen05 attention plan", group, num_kv_heads, page_size, int(window), fixed)
+        if key not in batch._tables:
+            work = torch.empty((8 * max_items + 4,), dtype=torch.int32, device=qkv.device)
+            tmp = torch.empty((3 * tiles,), dtype=torch.int32, device=qkv.device)
+            self._check(self.lib.llmie_attn_tc_plan(_ptr(tile_info), tiles, _ptr(positions), _ptr(token_seq), int(window), page_size, capacity, fixed,
+                                                    max_items, _ptr(work), _ptr(tmp), self._stream()), "attention plan (tcgen05)")
+            batch._tables[key] = (work, tmp)
+        work = batch._tables[key][0]
+        cells = max_items * num_kv_heads * 128
+        buf = self._scratch(cells * (head_dim + 2), qkv.device)
+        scratch_o, scratch_ml = buf, buf[cells * head_dim:]
+        if self._attn_counters is None or self._attn_counters.device != qkv.device:
+            self._attn_counters = torch.zeros(1 << 20, dtype=torch.int32, device=qkv.device)
         self._check(self.lib.llmie_paged_attention_tc(
             _ptr(qkv), qkv.shape[1], _ptr(k_pool), _ptr(v_pool), ctypes.c_longlong(k_pool.shape[0]), _ptr(block_table),
-            block_table.shape[1], _ptr(token_seq), _ptr(positions), _ptr(tile_info), tiles, _ptr(out), _ptr(scratch_o), _ptr(scratch_ml),
-            _ptr(counters), num_heads, num_kv_heads, head_dim, page_size, ctypes.c_float(scale), int(window), int(num_splits),
-            _ptr(self._errors(qkv.device)), self._stream()), "paged_attention (tcgen05)")
+            block_table.shape[1], tiles, _ptr(work), max_items, _ptr(out),
+            _ptr(scratch_o), _ptr(scratch_ml), _ptr(self._attn_counters), num_heads, num_kv_heads, head_dim, page_size,
+            ctypes.c_float(scale), int(window), _ptr(self._errors(qkv.device)), self._stream()), "paged_attention (tcgen05)")
         return out
 
     def _attention_mma(self, qkv, k_pool, v_pool, block_table, token_seq, positions, out, num_heads, num_kv_heads, head_dim,

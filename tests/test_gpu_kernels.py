@@ -317,6 +317,33 @@ def test_paged_attention_tcgen05(K, monkeypatch, nq, nkv, ps, lens, qlens, windo
     assert K._attn_counters is None or K._attn_counters.abs().sum().item() == 0  # the slice counters are back at zero
 
 
+@pytest.mark.parametrize("lens,qlens,splits", [([1500], [1500], None), ([1500, 900], [300, 64], None), ([1300], [40], 5)])
+def test_paged_attention_tcgen05_when_the_maximum_keeps_growing(K, lens, qlens, splits):
+    """The tcgen05 kernel takes P relative to a reference that follows a row's running maximum only when it lags by more
+    than 2^8, and then scales the row's outputs down in tensor memory. Here the scores of the even heads climb along the
+    sequence (by about 55 powers of two over 1,500 keys, so a row is rescaled every few chunks), those of the odd heads
+    fall (never rescaled), and both kinds sit in the same warp."""
+    nq, nkv, d, ps = 14, 2, 64, 16
+    qkv, kp, vp, table, tseq, pos = _attention_case(torch.bfloat16, nq, nkv, d, ps, lens, qlens, 0, 31)
+    g = torch.Generator().manual_seed(32)
+    u = torch.randn(d, generator=g)
+    u /= u.norm()
+    for r, L in enumerate(lens):
+        for t in range(L):
+            page, off = int(table[r, t // ps]), t % ps
+            kp[page, :, off] = (kp[page, :, off].float() + u * (t / 40)).to(torch.bfloat16)
+    q = qkv[:, :nq * d].view(-1, nq, d)
+    sign = torch.tensor([8.0 if h % 2 == 0 else -8.0 for h in range(nq)]).view(1, nq, 1)
+    q.copy_((q.float() + sign * u).to(torch.bfloat16))
+    scale = 1.0 / math.sqrt(d)
+    want = REF.paged_attention(qkv, kp, vp, table, tseq, pos, nq, nkv, d, ps, scale, 0, max(lens))
+    for _ in range(2):
+        got = K.paged_attention(qkv.cuda(), kp.cuda(), vp.cuda(), table.cuda(), tseq.cuda(), pos.cuda(), nq, nkv, d, ps, scale, 0,
+                                max(lens), batch=_Batch(qlens), num_splits=splits)
+        K.check_device_errors()
+        close(got, want, 1e-2)
+
+
 @pytest.mark.parametrize("M,N,K_,splits,accumulate", [
     (1, 128, 64, 1, False),
     (8, 1152, 896, 1, False),
