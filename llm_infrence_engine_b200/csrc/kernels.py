@@ -26,6 +26,11 @@ _ERR_BAD_ARGUMENT = 100001
 NUM_SMS_FALLBACK = 148
 
 
+def _raw_stream(device_index: int) -> int:
+    fast = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+    return fast(device_index) if fast is not None else torch.cuda.current_stream(device_index).cuda_stream
+
+
 def _ptr(t: Optional[torch.Tensor]):
     return ctypes.c_void_p(0 if t is None else t.data_ptr())
 
@@ -66,7 +71,8 @@ class CudaKernels:
     # ------------------------------------------------------------------ helpers
     @staticmethod
     def _stream():
-        return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        # the raw handle of the current stream, without building a Stream object (this runs before every launch)
+        return ctypes.c_void_p(_raw_stream(torch.cuda.current_device()))
 
     def _check(self, rc: int, what: str) -> None:
         self.launches += 1
@@ -204,7 +210,7 @@ class CudaKernels:
                 self.linear_tc(x, w, out=add_to, accumulate=True)
             elif bf16 and self.use_cublas and add_to.is_contiguous():
                 self.launches += 1
-                self._pending_add = (add_to, torch.matmul(x, w.t()))  # added by the norm that follows, or by flush()
+                self._pending_add = (add_to, torch.nn.functional.linear(x, w))  # added by the norm that follows, or by flush()
             else:
                 self._check(self.lib.llmie_gemm_simt(_ptr(x), _ptr(w), _ptr(add_to), M, N, K, self._dt(x, "x"), 0, 1, self._stream()),
                             "linear (accumulate)")
@@ -216,7 +222,7 @@ class CudaKernels:
             return self.linear_tc(x, w)
         if self.use_cublas and bf16 and out_dtype == torch.bfloat16:
             self.launches += 1
-            return torch.matmul(x, w.t())
+            return torch.nn.functional.linear(x, w)
         out = torch.empty((M, N), dtype=out_dtype, device=x.device)
         self._check(self.lib.llmie_gemm_simt(_ptr(x), _ptr(w), _ptr(out), M, N, K, self._dt(x, "x"), self._dt(out, "out"), 0,
                                              self._stream()), "linear")

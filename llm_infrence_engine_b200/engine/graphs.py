@@ -65,6 +65,7 @@ class DecodeGraphs:
         self.capture_after = 3   # a capture costs about a hundred eager steps: only shapes that keep coming are worth it
         self.max_shape_tokens = 8192
         self.pool = None
+        self._stream = None
         self.replays = 0
         self.shape_replays = 0
 
@@ -131,26 +132,44 @@ class DecodeGraphs:
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
-            for _ in range(2):
-                ctx._tables.clear()
-                r.forward(ctx, rows)
+            ctx._tables.clear()
+            r.forward(ctx, rows)  # once outside the capture: whatever this shape allocates or sets up for the first time
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
+        ctx._tables.clear()
+        before = r.K.launches
+        graph, logits = self._record(lambda: r.forward(ctx, rows))
+        return _Captured(graph, None, logits, r.K.launches - before)
+
+    def _record(self, fn):
+        """Runs ``fn`` under stream capture; returns ``(graph, what fn returned)``.
+
+        Nothing but the step's own kernels may touch CUDA while the stream is capturing. Python's cyclic collector could: an
+        old runner's graphs, found to be garbage in the middle of the capture, are destroyed with a CUDA call that the capture
+        forbids and that invalidates it. So the collector is off until the capture ends. (The capture is begun and ended by
+        hand: the library's context manager runs a full collection and empties the allocator's cache first, which costs tens
+        of milliseconds in a process with a large heap, many times the capture itself.)"""
         graph = torch.cuda.CUDAGraph()
         if self.pool is None:
             self.pool = torch.cuda.graph_pool_handle()
-        ctx._tables.clear()
-        before = r.K.launches
-        gc.collect()
+        if self._stream is None:
+            self._stream = torch.cuda.Stream()
         was_enabled = gc.isenabled()
         gc.disable()
         try:
-            with torch.cuda.graph(graph, pool=self.pool, capture_error_mode="relaxed"):
-                logits = r.forward(ctx, rows)
+            torch.cuda.synchronize()
+            self._stream.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(self._stream):
+                graph.capture_begin(pool=self.pool, capture_error_mode="relaxed")
+                try:
+                    out = fn()
+                finally:
+                    graph.capture_end()
+            torch.cuda.current_stream().wait_stream(self._stream)
         finally:
             if was_enabled:
                 gc.enable()
-        return _Captured(graph, None, logits, r.K.launches - before)
+        return graph, out
 
     def _layout_len(self, B: int) -> int:
         return step_layout(B, B, B, len(self.runner.cache.groups))["end"][0]
@@ -177,24 +196,14 @@ class DecodeGraphs:
                 r.K.argmax(r.forward(ctx, rows))
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
-        graph = torch.cuda.CUDAGraph()
-        if self.pool is None:
-            self.pool = torch.cuda.graph_pool_handle()
         ctx._tables.clear()
         before = r.K.launches
-        # Nothing but the step's own kernels may touch CUDA while the stream is capturing. Python's cyclic collector could:
-        # an old runner's graphs, found to be garbage in the middle of the capture, are destroyed with a CUDA call that the
-        # capture forbids and that invalidates it. So: collect first, then keep the collector off until the capture ends.
-        gc.collect()
-        was_enabled = gc.isenabled()
-        gc.disable()
-        try:
-            with torch.cuda.graph(graph, pool=self.pool, capture_error_mode="relaxed"):
-                logits = r.forward(ctx, rows)
-                tokens = r.K.argmax(logits)  # greedy rows need nothing more than this; the others are sampled from ``logits``
-        finally:
-            if was_enabled:
-                gc.enable()
+
+        def step():
+            logits = r.forward(ctx, rows)
+            return logits, r.K.argmax(logits)  # greedy rows need nothing more than this; the others are sampled from ``logits``
+
+        graph, (logits, tokens) = self._record(step)
         return _Captured(graph, static_in, logits, r.K.launches - before, tokens)
 
 
