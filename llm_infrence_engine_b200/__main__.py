@@ -28,6 +28,7 @@ def main(argv=None) -> int:
     ap.add_argument("--block-size", type=int, default=16)
     ap.add_argument("--max-batched-tokens", type=int, default=2048, help="token budget of one step")
     ap.add_argument("--cuda-graphs", action="store_true", help="replay decode-only steps (and prompt steps of a recurring shape) from CUDA graphs")
+    ap.add_argument("--warmup", action="store_true", help="with --cuda-graphs: capture the decode graphs of all batch sizes before the first request")
     ap.add_argument("--prefix-cache", action="store_true", help="requests take over cached pages that hold their leading tokens")
     ap.add_argument("--pipeline", action="store_true", help="launch a step before the tokens of the step before it have been read back")
     ap.add_argument("--prompt-ids", action="append", default=[], help="one prompt as space- or comma-separated token ids; repeatable")
@@ -63,6 +64,8 @@ def main(argv=None) -> int:
 
     eng = Engine(a.model, dtype=a.dtype, device=a.device, max_len=a.max_len, max_seqs=a.max_seqs, num_blocks=a.num_blocks,
                  block_size=a.block_size, max_num_batched_tokens=a.max_batched_tokens, cuda_graphs=a.cuda_graphs, pipeline=a.pipeline, prefix_cache=a.prefix_cache)
+    if a.warmup:
+        eng.warmup()
     results = eng.generate(prompts, a.max_new_tokens, ids(a.eos_ids), a.temperature, a.top_k, a.top_p, a.seed)
     for r in results:
         print(json.dumps({"prompt_len": r.prompt_len, "token_ids": r.token_ids, "finish_reason": r.finish_reason,

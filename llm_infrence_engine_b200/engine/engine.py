@@ -77,6 +77,13 @@ class Engine:
     def from_pretrained(cls, model: Union[str, Path], **kw) -> "Engine":
         return cls(model, **kw)
 
+    def warmup(self, batch_sizes: Optional[Sequence[int]] = None) -> List[int]:
+        """With CUDA graphs: capture the decode graphs (of all batch buckets, or of those that hold the given batch sizes)
+        before the first request instead of in the middle of serving; the reference captures when its decoder is built
+        (src/miniserve/graph_decode.py:45-47). Returns the captured buckets; without graphs, nothing."""
+        graphs = self.runner.graphs
+        return graphs.warmup(batch_sizes) if graphs is not None else []
+
     # ------------------------------------------------------------------ the reference's calls
     @property
     def waiting(self):

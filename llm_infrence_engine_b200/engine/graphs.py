@@ -208,6 +208,20 @@ class DecodeGraphs:
 
 
     @torch.inference_mode()
+    def warmup(self, batch_sizes: Optional[Sequence[int]] = None) -> List[int]:
+        """Captures the decode graphs of these batch sizes (all buckets if none are named) now rather than when a batch
+        first needs them, as the reference does when its decoder is built (src/miniserve/graph_decode.py:45-47).
+        Returns the buckets that are captured afterwards."""
+        if not self.usable:
+            return []
+        wanted = self.buckets if batch_sizes is None else sorted({next(b for b in self.buckets if b >= n)
+                                                                  for n in batch_sizes if 0 < n <= self.buckets[-1]})
+        for B in wanted:
+            if B not in self.captured:
+                self.captured[B] = self._capture(B)
+        return sorted(self.captured)
+
+    @torch.inference_mode()
     def run(self, entries: Sequence[StepEntry], previous_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
         r = self.runner
         n = len(entries)

@@ -190,6 +190,26 @@ def test_greedy_generation_through_entry_point(models, name, dtype):
     assert eng.preemptions >= 0 and all(pool.num_free == pool.capacity for pool in eng.cache.pools)
 
 
+def test_warmup_captures_the_decode_graphs_up_front(models):
+    """Engine.warmup() captures the graphs of the batch buckets before the first request (the reference captures when its
+    decoder is built); generation afterwards replays them, captures nothing more for those sizes and gives the plain tokens."""
+    from llm_infrence_engine_b200.engine import Engine
+
+    folder, cfg, w, prompts, want = models[("A", "float32")]
+    eng = Engine(str(folder), dtype="float32", block_size=PAGE_SIZES["A"], num_blocks=40, max_seqs=6, max_len=64,
+                 max_num_batched_tokens=64, cuda_graphs=True)
+    assert eng.warmup([1, 3]) == [1, 4]
+    assert eng.warmup() == eng.runner.graphs.buckets == [1, 2, 4, 6]
+    graphs = dict(eng.runner.graphs.captured)
+    ps = [random_prompt(cfg["vocab_size"], n, 70 + n) for n in (3, 9, 14)]
+    res = eng.generate(ps, max_new_tokens=12)
+    for r, p in zip(res, ps):
+        assert r.token_ids == plain_generate(cfg, w, p, 12)
+    assert eng.runner.graphs.replays > 0 and eng.runner.graphs.captured == graphs
+    no_graphs = Engine(str(folder), dtype="float32", block_size=PAGE_SIZES["A"], num_blocks=40, max_seqs=6, max_len=64)
+    assert no_graphs.warmup() == []
+
+
 def test_command_line_generates_the_plain_tokens(models):
     """``python -m llm_infrence_engine_b200`` with graphs and the pipelined engine: greedy tokens of two prompts, float32."""
     folder, cfg, w, prompts, want = models[("B", "float32")]
