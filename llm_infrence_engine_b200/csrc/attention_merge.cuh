@@ -10,11 +10,12 @@ namespace {
 // The block's finished rows are in shared memory as (max, sum, output); write them out, or, with several key slices
 // (`num_splits` of them for this tile and key/value head, this block's being number `split`), store the partial and let
 // the last block merge all slices. Slice s keeps its partial at index part_base + s * part_stride; `counter` is the
-// counter of this tile and key/value head.
+// counter of this tile and key/value head; `sums` is shared memory for num_splits * nrows floats that nothing else uses
+// (row_o must hold as many).
 template <int D, int ROWS, int THREADS, typename Params>
 __device__ __forceinline__ void finish_tile(const Params& p, const float* row_m, const float* row_l, const float* row_o, int num_splits,
                                             size_t part_base, size_t part_stride, int counter, int kvh, int split, int n0, int nrows,
-                                            int G, int* flag_smem) {
+                                            int G, int* flag_smem, float* sums) {
     const int tid = threadIdx.x;
     if (num_splits == 1) {
         for (int i = tid; i < nrows * D; i += THREADS) {
@@ -40,31 +41,31 @@ __device__ __forceinline__ void finish_tile(const Params& p, const float* row_m,
     }
     __syncthreads();
     if (!*flag_smem) return;
-    // Last block of the tile: first the slices' (max, sum) pairs become per-row weights in shared memory (the
-    // block's own row_m / row_l / row_o are not needed any more), then every output element is one weighted sum
-    // whose loads do not depend on each other.
-    float* wgt = const_cast<float*>(row_o);                 // [num_splits][nrows] weights e^(m_s - M) / L
-    float* mx = const_cast<float*>(row_m);                  // [nrows] overall maximum
-    for (int r = tid; r < nrows; r += THREADS) {
-        float M = -INFINITY;
-        for (int s = 0; s < num_splits; ++s) M = fmaxf(M, __ldcg(p.part_ml + (part_base + s * part_stride) * ROWS * 2 + 2 * r));
-        mx[r] = M;
-    }
-    __syncthreads();
+    // Last block of the tile. One trip to memory brings every slice's (max, sum) pair into shared memory (the block's own
+    // row_m / row_l / row_o are not needed any more); from these each row's thread makes the slices' weights
+    // e^(m_s - M) and 1 / L; then every output element is one weighted sum whose loads do not depend on each other.
+    float* wgt = const_cast<float*>(row_o);                 // [num_splits][nrows] maxima, then weights
     for (int i = tid; i < nrows * num_splits; i += THREADS) {
         const int s = i / nrows, r = i % nrows;
-        const float M = mx[r];
-        wgt[i] = M > -INFINITY ? exp2f(__ldcg(p.part_ml + (part_base + s * part_stride) * ROWS * 2 + 2 * r) - M) : 0.f;
+        const float2 ml = __ldcg(reinterpret_cast<const float2*>(p.part_ml + (part_base + s * part_stride) * ROWS * 2 + 2 * r));
+        wgt[i] = ml.x;
+        sums[i] = ml.y;
     }
     __syncthreads();
     for (int r = tid; r < nrows; r += THREADS) {
+        float M = -INFINITY;
+        for (int s = 0; s < num_splits; ++s) M = fmaxf(M, wgt[s * nrows + r]);
         float L = 0.f;
-        for (int s = 0; s < num_splits; ++s) L = fmaf(__ldcg(p.part_ml + (part_base + s * part_stride) * ROWS * 2 + 2 * r + 1), wgt[s * nrows + r], L);
+        for (int s = 0; s < num_splits; ++s) {
+            const float w = M > -INFINITY ? exp2f(wgt[s * nrows + r] - M) : 0.f;
+            wgt[s * nrows + r] = w;
+            L = fmaf(sums[s * nrows + r], w, L);
+        }
         const_cast<float*>(row_l)[r] = L > 0.f ? 1.f / L : 0.f;
     }
     __syncthreads();
     // four neighbouring outputs of a row per thread and step (16-byte loads that do not depend on each other)
-#pragma unroll 2
+#pragma unroll 4
     for (int i = tid * 4; i < nrows * D; i += THREADS * 4) {
         const int r = i / D, dim = i % D;
         float4 O = make_float4(0.f, 0.f, 0.f, 0.f);

@@ -521,7 +521,7 @@ __global__ void __launch_bounds__(DW * 32) attn_mma_decode_kernel(const Params p
         cluster_sync_all();  // the other blocks' shared memory stays until block 0 has read it
         return;
     }
-    finish_tile<D, 16, DW * 32>(p, fm, fl, fo, p.num_splits, ((size_t)tile * p.nkv + kvh) * p.num_splits, 1, tile * p.nkv + kvh, kvh, split, n0, nrows, G, &flag);
+    finish_tile<D, 16, DW * 32>(p, fm, fl, fo, p.num_splits, ((size_t)tile * p.nkv + kvh) * p.num_splits, 1, tile * p.nkv + kvh, kvh, split, n0, nrows, G, &flag, wo);
 }
 
 // ---------------------------------------------------------------------------------------------- prefill
@@ -631,7 +631,7 @@ __global__ void __launch_bounds__(WARPS * 32) attn_mma_prefill_kernel(const Para
         }
     }
     __syncthreads();
-    finish_tile<D, BM, WARPS * 32>(p, fm, fl, fo, p.num_splits, ((size_t)tile * p.nkv + kvh) * p.num_splits, 1, tile * p.nkv + kvh, kvh, split, n0, nrows, G, &flag);
+    finish_tile<D, BM, WARPS * 32>(p, fm, fl, fo, p.num_splits, ((size_t)tile * p.nkv + kvh) * p.num_splits, 1, tile * p.nkv + kvh, kvh, split, n0, nrows, G, &flag, fo + BM * D);
 }
 
 // tile list of a step: request r brings tokens [starts[r], starts[r + 1]); tiles hold up to `per_tile` tokens of one request

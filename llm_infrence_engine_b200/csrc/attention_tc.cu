@@ -461,7 +461,7 @@ __global__ void __launch_bounds__(THREADS, 2) attn_tc_prefill_kernel(const __gri
         float* fm = reinterpret_cast<float*>(p_s);
         __shared__ int last_flag;
         finish_tile<D, BM, THREADS>(p, fm, fm + BM, fm + 2 * BM, num_splits, (size_t)job.w * p.nkv + kvh, (size_t)p.nkv, tile * p.nkv + kvh, kvh,
-                                    split, n0, nrows, G, &last_flag);
+                                    split, n0, nrows, G, &last_flag, fm + 2 * BM + BM * D);
     }
 }
 
