@@ -65,15 +65,23 @@ __device__ __forceinline__ void finish_tile(const Params& p, const float* row_m,
     }
     __syncthreads();
     // four neighbouring outputs of a row per thread and step (16-byte loads that do not depend on each other)
-#pragma unroll 4
     for (int i = tid * 4; i < nrows * D; i += THREADS * 4) {
         const int r = i / D, dim = i % D;
         float4 O = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 4
-        for (int s = 0; s < num_splits; ++s) {
-            const float4 a = __ldcg(reinterpret_cast<const float4*>(p.part_o + (part_base + s * part_stride) * ROWS * D + i));
-            const float w = wgt[s * nrows + r];
-            O.x = fmaf(a.x, w, O.x); O.y = fmaf(a.y, w, O.y); O.z = fmaf(a.z, w, O.z); O.w = fmaf(a.w, w, O.w);
+        // the slices in groups of GROUP whose loads all leave before the first of them is used: one trip to memory per group
+        constexpr int GROUP = 12;
+        for (int s0 = 0; s0 < num_splits; s0 += GROUP) {
+            float4 a[GROUP];
+#pragma unroll
+            for (int k = 0; k < GROUP; ++k)
+                if (s0 + k < num_splits) a[k] = __ldcg(reinterpret_cast<const float4*>(p.part_o + (part_base + (s0 + k) * part_stride) * ROWS * D + i));
+#pragma unroll
+            for (int k = 0; k < GROUP; ++k) {
+                if (s0 + k < num_splits) {
+                    const float w = wgt[(s0 + k) * nrows + r];
+                    O.x = fmaf(a[k].x, w, O.x); O.y = fmaf(a[k].y, w, O.y); O.z = fmaf(a[k].z, w, O.z); O.w = fmaf(a[k].w, w, O.w);
+                }
+            }
         }
         const float inv = row_l[r];
         const __nv_bfloat162 lo = __floats2bfloat162_rn(O.x * inv, O.y * inv), hi = __floats2bfloat162_rn(O.z * inv, O.w * inv);
