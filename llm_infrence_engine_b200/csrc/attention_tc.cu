@@ -68,6 +68,30 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 
+// Three-input maximum and the packed 32-bit forms of sm_100a (two independent float32 operations per instruction): the
+// softmax step is bound by issue slots, and these halve the slots of its maxima, scalings and sums.
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;\n" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t pair_of(float lo, float hi) {
+    uint64_t v;
+    asm("mov.b64 %0, {%1, %2};\n" : "=l"(v) : "f"(lo), "f"(hi));
+    return v;
+}
+__device__ __forceinline__ void unpair(uint64_t v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;\n" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;\n" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;\n" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<const uint32_t*>(&v);
@@ -323,7 +347,10 @@ __global__ void __launch_bounds__(THREADS, 2) attn_tc_prefill_kernel(const __gri
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
             if (interior) {
 #pragma unroll
-                for (int j = 0; j < BN; ++j) mx4[j & 3] = fmaxf(mx4[j & 3], __uint_as_float(s[j]));
+                for (int j = 0; j < BN; j += 8) {
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) mx4[k] = max3(mx4[k], __uint_as_float(s[j + k]), __uint_as_float(s[j + 4 + k]));
+                }
             } else {
 #pragma unroll
                 for (int j = 0; j < BN; ++j) {
@@ -372,19 +399,30 @@ __global__ void __launch_bounds__(THREADS, 2) attn_tc_prefill_kernel(const __gri
             }
             // all 64 exponentials first, in place and independent of each other (the special-function unit is the narrow
             // place of this loop and must not wait for the sums and stores that follow)
+            const uint64_t scale2 = pair_of(p.scale_log2, p.scale_log2), shift2 = pair_of(-use, -use);
 #pragma unroll
-            for (int j = 0; j < BN; ++j) s[j] = __float_as_uint(fast_exp2(fmaf(__uint_as_float(s[j]), p.scale_log2, -use)));
-            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+            for (int j = 0; j < BN; j += 2) {
+                float x0, x1;
+                unpair(fma2(pair_of(__uint_as_float(s[j]), __uint_as_float(s[j + 1])), scale2, shift2), x0, x1);
+                s[j] = __float_as_uint(fast_exp2(x0));
+                s[j + 1] = __float_as_uint(fast_exp2(x1));
+            }
+            uint64_t sum2[2] = {pair_of(0.f, 0.f), pair_of(0.f, 0.f)};
 #pragma unroll
             for (int j = 0; j < BN; j += 8) {
                 float e[8];
 #pragma unroll
-                for (int i = 0; i < 8; ++i) { e[i] = __uint_as_float(s[j + i]); sum4[i & 3] += e[i]; }
+                for (int i = 0; i < 8; ++i) e[i] = __uint_as_float(s[j + i]);
+                sum2[0] = add2(add2(sum2[0], pair_of(e[0], e[1])), pair_of(e[4], e[5]));
+                sum2[1] = add2(add2(sum2[1], pair_of(e[2], e[3])), pair_of(e[6], e[7]));
                 uint4 packed;
                 packed.x = pack_bf16x2(e[0], e[1]); packed.y = pack_bf16x2(e[2], e[3]);
                 packed.z = pack_bf16x2(e[4], e[5]); packed.w = pack_bf16x2(e[6], e[7]);
                 *reinterpret_cast<uint4*>(p_s + (c & 1) * P_BYTES + row * 128 + (((j >> 3) ^ (row & 7)) << 4)) = packed;
             }
+            float sum4[4];
+            unpair(sum2[0], sum4[0], sum4[1]);
+            unpair(sum2[1], sum4[2], sum4[3]);
             l = l * corr + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
             if (key0 + BN > hi) {
                 // the chunk reaches behind the last key: those value rows may hold anything; they become zeros
