@@ -55,6 +55,7 @@ class CudaKernels:
         self.use_tc_attention = True   # prompt portions of head size 64: scores and outputs through tcgen05 and tensor memory
         self.cluster_merge = True      # decode attention: the key slices of a token form a cluster and merge in shared memory
         self.use_tc_gemm = True
+        self.use_tc_qkv = True         # prompt portions, head size 64: q/k/v product with bias, rotation and cache write in one kernel
         self.tc_max_rows = 128        # batches up to this many rows take the small-batch tensor-core product
         self._acc: Optional[torch.Tensor] = None  # float32 zeros: split-K products add into it, their consumer clears it again
         # A library product that is to be added into the residual stream is kept here until the next kernel that reads
@@ -63,7 +64,7 @@ class CudaKernels:
         self._error_flag: Optional[torch.Tensor] = None
         self.num_sms = torch.cuda.get_device_properties(0).multi_processor_count or NUM_SMS_FALLBACK
         for fn in ("llmie_embed", "llmie_feed_tokens", "llmie_rope_tables", "llmie_add_rmsnorm", "llmie_rope_kv_write", "llmie_silu_mul",
-                   "llmie_gemm_simt", "llmie_gemm_tc", "llmie_add_into", "llmie_attn_plan", "llmie_attn_tc_plan", "llmie_paged_attention_mma", "llmie_paged_attention_tc", "llmie_paged_attention_f32", "llmie_paged_attention_bf16", "llmie_argmax", "llmie_sample"):
+                   "llmie_gemm_simt", "llmie_gemm_tc", "llmie_qkv_rope_tc", "llmie_add_into", "llmie_attn_plan", "llmie_attn_tc_plan", "llmie_paged_attention_mma", "llmie_paged_attention_tc", "llmie_paged_attention_f32", "llmie_paged_attention_bf16", "llmie_argmax", "llmie_sample"):
             getattr(self.lib, fn).restype = ctypes.c_int
         # kernels of a step overlap their set-up with the tail of the kernel before (programmatic dependent launch)
         self.lib.llmie_set_pdl(0 if os.environ.get("LLMIE_PDL", "1") == "0" else 1)
@@ -313,6 +314,43 @@ class CudaKernels:
                                                  _ptr(v_pool), N, num_heads, num_kv_heads, head_dim, page_size, int(bool(write_kv)),
                                                  int(clear), self._dt(qkv, "qkv"), self._dt(out, "out"), self._stream()), "rope_kv_write")
         return out
+
+    def qkv_rope(self, x, w, bias, cos, sin, slot_mapping, k_pool, v_pool, num_heads, num_kv_heads, head_dim, page_size,
+                 write_kv=True, out_dtype=None):
+        """The fused q/k/v projection ``x w^T`` with bias, rotation and cache write; returns the rotated rows.
+
+        Prompt portions in bfloat16 with head size 64 take one tcgen05 kernel that does all of it in its epilogue; everything
+        else is the product followed by ``rope_kv_write``."""
+        out_dtype = out_dtype or x.dtype
+        M, K = x.shape
+        if (self.use_tc_qkv and x.dtype == torch.bfloat16 and out_dtype == torch.bfloat16 and head_dim == 64 and M > self.tc_max_rows
+                and K % 8 == 0 and x.is_contiguous() and w.is_contiguous() and M <= 65535 * 128):
+            self._need(w, "w", torch.bfloat16, 2)
+            heads = num_heads + 2 * num_kv_heads
+            if tuple(w.shape) != (heads * head_dim, K):
+                raise KernelError(f"qkv_rope: w is {list(w.shape)}, the head counts and x need [{heads * head_dim}, {K}]")
+            self._need(cos, "cos", torch.float32, 2)
+            self._need(sin, "sin", torch.float32, 2)
+            if tuple(cos.shape) != (M, head_dim // 2) or tuple(sin.shape) != (M, head_dim // 2):
+                raise KernelError("qkv_rope: cos and sin must be [tokens, head_dim / 2]")
+            if bias is not None:
+                self._need(bias, "bias", torch.float32, 1)
+                if bias.shape[0] != heads * head_dim:
+                    raise KernelError("qkv_rope: bias does not match the projection's width")
+            if write_kv:
+                self._need(slot_mapping, "slot_mapping", torch.int32, 1)
+                for name, pool in (("k_pool", k_pool), ("v_pool", v_pool)):
+                    self._need(pool, name, torch.bfloat16, 4)
+                    if tuple(pool.shape[1:]) != (num_kv_heads, page_size, head_dim):
+                        raise KernelError(f"qkv_rope: {name} is {list(pool.shape)}, expected [pages, {num_kv_heads}, {page_size}, {head_dim}]")
+            out = torch.empty((M, heads * head_dim), dtype=torch.bfloat16, device=x.device)
+            self._check(self.lib.llmie_qkv_rope_tc(_ptr(x), M, K, _ptr(w), _ptr(bias), _ptr(cos), _ptr(sin), _ptr(slot_mapping), _ptr(out),
+                                                   _ptr(k_pool), _ptr(v_pool), num_heads, num_kv_heads, head_dim, page_size,
+                                                   int(bool(write_kv)), _ptr(self._errors(x.device)), self._stream()), "qkv_rope (tcgen05)")
+            return out
+        qkv = self.linear(x, w, transient=True)
+        return self.rope_kv_write(qkv, bias, cos, sin, slot_mapping, k_pool, v_pool, num_heads, num_kv_heads, head_dim, page_size,
+                                  write_kv, out_dtype=out_dtype)
 
     def attention_splits(self, num_tokens: int, num_kv_heads: int, max_context: int) -> int:
         """Slices of the keys per token: enough blocks to fill the device, at least 256 keys each."""

@@ -53,10 +53,9 @@ class PagedAttention(Mixer):
 
     def forward(self, ctx, h, cache, residual):
         K = ctx.K
-        qkv = K.linear(h, self.w_qkv, transient=True)
         cos, sin = ctx.position_tables(self.position)
-        qkv = K.rope_kv_write(qkv, self.b_qkv, cos, sin, ctx.slot_mapping[cache.group], cache.k, cache.v,
-                              self.num_heads, self.num_kv_heads, self.head_dim, ctx.page_size, cache.write, out_dtype=ctx.dtype)
+        qkv = K.qkv_rope(h, self.w_qkv, self.b_qkv, cos, sin, ctx.slot_mapping[cache.group], cache.k, cache.v,
+                         self.num_heads, self.num_kv_heads, self.head_dim, ctx.page_size, cache.write, out_dtype=ctx.dtype)
         attn = K.paged_attention(qkv, cache.k, cache.v, ctx.block_tables[cache.group], ctx.token_seq, ctx.positions,
                                  self.num_heads, self.num_kv_heads, self.head_dim, ctx.page_size, self.scale,
                                  self.window or 0, ctx.max_context, batch=ctx)

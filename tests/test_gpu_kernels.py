@@ -128,6 +128,48 @@ def test_rope_kv_write(K, dtype, nq, nkv, d, ps, bias):
     assert kp_gpu.cpu().permute(0, 2, 1, 3).reshape(pages * ps, -1)[untouched].abs().sum() == 0
 
 
+@pytest.mark.parametrize("N,H,nq,nkv,ps,bias,write", [
+    (2048, 896, 14, 2, 16, True, True),     # the bench's prompt
+    (129, 96, 6, 2, 16, True, True),        # one row more than a tile; an inner size that is no multiple of 64
+    (300, 200, 3, 1, 8, False, True),       # 5 heads: the last tile holds one head only
+    (513, 1536, 12, 2, 32, True, False),    # no cache write (a layer that reads another layer's cache)
+    (200, 72, 1, 1, 16, True, True),        # three heads in one block of columns; two inner blocks, the second ragged
+])
+def test_qkv_rope_tcgen05(K, N, H, nq, nkv, ps, bias, write):
+    """The q/k/v product of prompt portions with bias, rotation and cache write in its epilogue (tcgen05, head size 64)
+    against product, rotation and cache write one after the other in 32-bit. Some tokens have no slot (negative)."""
+    d = 64
+    g = torch.Generator().manual_seed(13)
+    x = torch.randn(N, H, generator=g).to(torch.bfloat16)
+    w = (torch.randn((nq + 2 * nkv) * d, H, generator=g) / math.sqrt(H)).to(torch.bfloat16)
+    b = torch.randn((nq + 2 * nkv) * d, generator=g) if bias else None
+    pos = torch.randint(0, 3000, (N,), generator=g).int()
+    inv = 1.0 / (1e6 ** (torch.arange(0, d, 2).float() / d))
+    cos, sin = REF.rope_tables(pos, inv)
+    pages = -(-N // ps) + 2
+    slots = torch.randperm(pages * ps, generator=g)[:N].int()
+    slots[::7] = -1
+    kp, vp = torch.zeros(pages, nkv, ps, d, dtype=torch.bfloat16), torch.zeros(pages, nkv, ps, d, dtype=torch.bfloat16)
+    want = (x.float() @ w.float().T)
+    kp_ref, vp_ref = kp.float(), vp.float()
+    keep = slots >= 0
+    REF.rope_kv_write(want, b, cos, sin, slots.clamp(min=0), kp_ref, vp_ref, nq, nkv, d, ps, False)
+    if write:
+        page, off = (slots[keep] // ps).long(), (slots[keep] % ps).long()
+        kp_ref[page, :, off] = want.view(N, -1, d)[keep][:, nq:nq + nkv]
+        vp_ref[page, :, off] = want.view(N, -1, d)[keep][:, nq + nkv:]
+    before = K.launches
+    kp_gpu, vp_gpu = kp.cuda(), vp.cuda()
+    for _ in range(2):
+        got = K.qkv_rope(x.cuda(), w.cuda(), None if b is None else b.cuda(), cos.cuda(), sin.cuda(), slots.cuda(), kp_gpu, vp_gpu,
+                         nq, nkv, d, ps, write)
+        K.check_device_errors()
+        close(got, want, 8e-3)
+        close(kp_gpu, kp_ref, 8e-3)
+        close(vp_gpu, vp_ref, 8e-3)
+    assert K.launches - before == 2   # one kernel per call
+
+
 def _attention_case(dtype, nq, nkv, d, ps, lens, qlens, window, seed, spike=False):
     """Requests with ``lens`` cached+new tokens, the last ``qlens`` of each being this step's tokens,
     pages handed out in a shuffled order."""

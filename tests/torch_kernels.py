@@ -51,6 +51,12 @@ class TorchKernels:
             return None
         return y.to(out_dtype or x.dtype)
 
+    def qkv_rope(self, x, w, bias, cos, sin, slot_mapping, k_pool, v_pool, num_heads, num_kv_heads, head_dim, page_size,
+                 write_kv=True, out_dtype=None):
+        qkv = self.linear(x, w, out_dtype=out_dtype)
+        return self.rope_kv_write(qkv, bias, cos, sin, slot_mapping, k_pool, v_pool, num_heads, num_kv_heads, head_dim, page_size,
+                                  write_kv, out_dtype)
+
     def rope_kv_write(self, qkv, bias, cos, sin, slot_mapping, k_pool, v_pool, num_heads, num_kv_heads, head_dim,
                       page_size, write_kv=True, out_dtype=None):
         N = qkv.shape[0]
