@@ -124,6 +124,7 @@ class CacheManager:
         if page_size <= 0:
             raise ValueError("page_size must be positive")
         self.groups = list(groups)
+        self._windowed = any(g.window is not None for g in self.groups)
         # pages can only be shared where a request's pages are all it has: one group, no window (a windowed group gives pages
         # back as it goes), and the caller says that no fixed-size state exists (``prefix_sharing`` is its promise)
         self.prefix_sharing = bool(prefix_sharing) and len(self.groups) == 1 and self.groups[0].window is None
@@ -267,6 +268,15 @@ class CacheManager:
         if new_len < context_len:
             raise ValueError("new_len is less than context_len")
         held = self._held[req]
+        want = -(-new_len // self.page_size)
+        if not self._windowed:
+            for table in held.tables:
+                if len(table) < want:
+                    break
+            else:  # the usual decode step: the last page still has room
+                if new_len > held.length:
+                    held.length = new_len
+                return
         self.release_passed(req, context_len)
         groups = range(len(self.groups))
         for g in groups:
