@@ -107,3 +107,22 @@ def test_prefix_cache_gives_the_same_tokens_and_computes_less(folders):
     assert on["prefix_cache"] and on["prefix_tokens_hit"] >= 3 * 32
     assert on["prefill_tokens_computed"] < off["prefill_tokens_computed"]
     assert on["preemptions"] + off["preemptions"] > 0  # the pool is small enough that both runs had to preempt
+
+
+def test_graph_buckets_and_warmup_without_graphs(folders):
+    """Padded batch sizes of the decode graphs: 1, 2, 4, 8, 16, then in steps of half a power of two, the largest batch last;
+    an engine without graphs has nothing to warm up."""
+    from llm_infrence_engine_b200.engine.graphs import bucket_sizes
+
+    assert bucket_sizes(1) == [1]
+    assert bucket_sizes(6) == [1, 2, 4, 6]
+    assert bucket_sizes(64) == [1, 2, 4, 8, 16, 24, 32, 48, 64]
+    assert bucket_sizes(40) == [1, 2, 4, 8, 16, 24, 32, 40]
+    assert bucket_sizes(100) == [1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 100]
+    for m in range(1, 200):
+        b = bucket_sizes(m)
+        assert b[-1] == m and b == sorted(set(b))
+    folder = folders["A"][0] if isinstance(folders["A"], tuple) else folders["A"]
+    eng = Engine(str(folder), kernels=TorchKernels(), device="cpu", dtype="float32", block_size=PAGE_SIZES["A"], num_blocks=20,
+                 max_seqs=3, max_len=64)
+    assert eng.warmup() == [] and eng.warmup([1, 2]) == []
