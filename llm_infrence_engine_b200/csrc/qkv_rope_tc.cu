@@ -11,7 +11,7 @@
 // and rotation (the library product followed by the rotation kernel rounds it to bfloat16 in between).
 //
 //   warps 0-3  the 128 row threads (epilogue)
-//   warp 4     one lane fetches the tiles
+//   warp 4     fetches the tiles, up to four boxes at a time from four lanes
 //   warp 5     one lane issues the MMAs
 //
 // Every wait on an mbarrier is bounded: after SPIN_LIMIT polls the block records an error, the roles leave their loops,
@@ -81,29 +81,39 @@ __global__ void __launch_bounds__(THREADS, 1) qkv_rope_tc_kernel(const __grid_co
 
     pdl_trigger();
     if (warp == 4) {
-        if (lane == 0) {
-            // the weights do not depend on the kernel before: their first tiles are on their way before the wait
-            bool ok = true;
-            const int early = nkb < STAGES ? nkb : STAGES;
-            for (int kb = 0; kb < early; ++kb) {
-                mbar_expect_tx(full + kb, A_BYTES + B_BYTES);
-                tma_load_2d(b_s + kb * B_BYTES, &tmap_w, kb * BK, n0, full + kb);
-            }
-            *issued = early;
-            pdl_wait();
-            for (int kb = 0; kb < nkb && ok; ++kb) {
-                const int st = kb % STAGES;
-                if (kb >= STAGES) {
-                    ok = mbar_wait(empty + st, ((kb / STAGES) & 1) ^ 1, abort_flag, p.error_flag, 21);
-                    if (!ok) break;
-                    mbar_expect_tx(full + st, A_BYTES + B_BYTES);
-                    tma_load_2d(b_s + st * B_BYTES, &tmap_w, kb * BK, n0, full + st);
+        // Issuing a TMA copy occupies its thread for hundreds of cycles whatever the box's size, so the boxes of a step are
+        // issued by different lanes side by side. The weights do not depend on the kernel before: the first STAGES tiles
+        // of them are on their way before the dependency wait, the tokens' tiles follow after it.
+        const int early = nkb < STAGES ? nkb : STAGES;
+        if (lane == 0)
+            for (int kb = 0; kb < early; ++kb) mbar_expect_tx(full + kb, A_BYTES + B_BYTES);
+        __syncwarp();
+        if (lane < early) tma_load_2d(b_s + lane * B_BYTES, &tmap_w, lane * BK, n0, full + lane);
+        pdl_wait();
+        if (lane < early) tma_load_2d(a_s + lane * A_BYTES, &tmap_x, lane * BK, m0, full + lane);
+        __syncwarp();
+        if (lane == 0) *issued = early;
+        // from then on two steps of the ring at a time: lane 0 waits for both stages and announces the bytes, lanes 0 .. 3
+        // issue the two token tiles and the two weight tiles
+        bool ok = true;
+        for (int kb0 = STAGES; kb0 < nkb; kb0 += 2) {
+            const int n = nkb - kb0 < 2 ? nkb - kb0 : 2;
+            if (lane == 0) {
+                for (int i = 0; i < n && ok; ++i) {
+                    const int st = (kb0 + i) % STAGES;
+                    ok = mbar_wait(empty + st, (((kb0 + i) / STAGES) & 1) ^ 1, abort_flag, p.error_flag, 21);
+                    if (ok) mbar_expect_tx(full + st, A_BYTES + B_BYTES);
                 }
-                tma_load_2d(a_s + st * A_BYTES, &tmap_x, kb * BK, m0, full + st);
-                *issued = kb + 1;
             }
-        } else {
-            pdl_wait();
+            ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+            if (!ok) break;
+            if (lane < 2 * n) {
+                const int kb = kb0 + (lane >> 1), st = kb % STAGES;
+                if (lane & 1) tma_load_2d(b_s + st * B_BYTES, &tmap_w, kb * BK, n0, full + st);
+                else tma_load_2d(a_s + st * A_BYTES, &tmap_x, kb * BK, m0, full + st);
+            }
+            __syncwarp();
+            if (lane == 0) *issued = kb0 + n;
         }
     } else if (warp == 5) {
         pdl_wait();
