@@ -18,8 +18,8 @@ after the reference's allocator (src/miniserve/paged.py:41-49,85-122, paged_engi
 a page that is full of tokens gets the hash of those tokens chained to the hash of the page before
 it. A new request first takes over the pages whose hashes match the leading full pages of its
 tokens (always leaving at least one token to compute), so several requests may hold one page: pages
-carry a count of holders. A hashed page whose last holder has gone stays in the pool as a cached
-page, found again by its hash, until the free list is empty and it is the least recently used.
+carry a count of holders. A named page whose last holder has gone stays findable by its name until
+every nameless idle page is in use and it is the one that was let go of longest ago.
 """
 from __future__ import annotations
 
@@ -35,19 +35,23 @@ class OutOfPages(Exception):
 
 
 class PagePool:
-    """One group's pages: a free list, a count of holders per page, and (with prefix sharing) cached pages by hash.
-    Page 0 is never handed out."""
+    """One group's pages. Page 0 is never handed out.
+
+    A page is either in use (it has users: one request, or several with prefix sharing) or idle. The idle pages stand
+    in ONE queue in the order in which they will be handed out: a page that carries no name goes to the head when its
+    last user lets go (it is worth nothing, and was touched most recently), a named page (a full page of known tokens,
+    findable by ``find``) goes to the tail. So names survive as long as any nameless page is left, and then the name
+    that was let go of longest ago is given up first."""
 
     def __init__(self, num_pages: int):
         if num_pages < 2:
             raise ValueError("a pool needs at least 2 pages (page 0 is the null page)")
         self.num_pages = num_pages
-        self._free = deque(range(1, num_pages))
-        self._holders: List[List[Hashable]] = [[] for _ in range(num_pages)]  # who holds the page (several with prefix sharing)
-        self._hash: List[Optional[bytes]] = [None] * num_pages
-        self._by_hash: Dict[bytes, int] = {}
-        self._cached: "OrderedDict[int, None]" = OrderedDict()  # hashed pages nobody holds, least recently used first
-        self.evictions = 0
+        self._idle: "OrderedDict[int, None]" = OrderedDict((page, None) for page in range(1, num_pages))
+        self._users: List[List[Hashable]] = [[] for _ in range(num_pages)]
+        self._name_of: Dict[int, bytes] = {}
+        self._page_named: Dict[bytes, int] = {}
+        self.names_given_up = 0   # named pages that had to be handed out again because no nameless page was idle
 
     @property
     def capacity(self) -> int:
@@ -55,54 +59,59 @@ class PagePool:
 
     @property
     def num_free(self) -> int:
-        """Pages that ``allocate`` can hand out: free ones and cached ones that nobody holds."""
-        return len(self._free) + len(self._cached)
+        """Pages that ``allocate`` can hand out: every idle page, named or not."""
+        return len(self._idle)
 
     def allocate(self, owner: Hashable = None) -> int:
-        if self._free:
-            page = self._free.popleft()
-        elif self._cached:
-            page, _ = self._cached.popitem(last=False)  # src/miniserve/paged.py:85-96: evict the least recently used
-            del self._by_hash[self._hash[page]]
-            self._hash[page] = None
-            self.evictions += 1
-        else:
+        if not self._idle:
             raise OutOfPages()
-        self._holders[page] = [owner]
+        page, _ = self._idle.popitem(last=False)
+        name = self._name_of.pop(page, None)
+        if name is not None:  # the head of the queue is a named page only when every idle page is named
+            del self._page_named[name]
+            self.names_given_up += 1
+        self._users[page] = [owner]
         return page
 
     def share(self, page: int, owner: Hashable = None) -> None:
-        """One more holder of a page found by its hash."""
-        if not self._holders[page]:
-            del self._cached[page]
-        self._holders[page].append(owner)
+        """One more user of a page that ``find`` returned; an idle page leaves the queue."""
+        if not self._users[page]:
+            del self._idle[page]
+        self._users[page].append(owner)
 
     def free(self, page: int, owner: Hashable = None) -> None:
-        """One holder less. The last one sends the page to the cached pages (if it has a hash) or to the free list."""
+        """One user less; the last one makes the page idle."""
         if page == NULL_PAGE or not 0 < page < self.num_pages:
             raise ValueError(f"page {page} cannot be freed")
-        if not self._holders[page]:
+        users = self._users[page]
+        if not users:
             raise ValueError(f"page {page} freed twice")
-        if owner not in self._holders[page]:
-            raise ValueError(f"page {page} belongs to {self._holders[page]!r}, not to {owner!r}")
-        self._holders[page].remove(owner)
-        if not self._holders[page]:
-            if self._hash[page] is not None:
-                self._cached[page] = None
-            else:
-                self._free.append(page)
+        if owner not in users:
+            raise ValueError(f"page {page} belongs to {users!r}, not to {owner!r}")
+        users.remove(owner)
+        if not users:
+            self._idle[page] = None                          # tail: behind every other idle page
+            if page not in self._name_of:
+                self._idle.move_to_end(page, last=False)     # nameless: to the head, the next to be handed out
 
     def holders(self, page: int) -> int:
-        return len(self._holders[page])
+        return len(self._users[page])
 
-    def set_hash(self, page: int, digest: bytes) -> None:
+    def set_name(self, page: int, name: bytes) -> None:
         """Name a full page by the hash of its tokens. If another page already has the name, this one stays nameless."""
-        if self._hash[page] is None and digest not in self._by_hash:
-            self._hash[page] = digest
-            self._by_hash[digest] = page
+        if page not in self._name_of and name not in self._page_named:
+            self._name_of[page] = name
+            self._page_named[name] = page
 
-    def lookup(self, digest: bytes) -> Optional[int]:
-        return self._by_hash.get(digest)
+    def find(self, name: bytes) -> Optional[int]:
+        return self._page_named.get(name)
+
+    def idle_pages(self) -> List[int]:
+        """The idle pages in the order in which they would be handed out."""
+        return list(self._idle)
+
+    def name_of(self, page: int) -> Optional[bytes]:
+        return self._name_of.get(page)
 
 
 class _Held:
@@ -200,7 +209,7 @@ class CacheManager:
         digest = b""
         for i in range((len(tokens) - 1) // ps):
             digest = self._chain(digest, tokens[i * ps:(i + 1) * ps])
-            page = pool.lookup(digest)
+            page = pool.find(digest)
             if page is None:
                 break
             pool.share(page, req)
@@ -226,7 +235,7 @@ class CacheManager:
             i = len(held.hashes)
             digest = self._chain(held.hashes[-1] if held.hashes else b"", tokens[i * ps:(i + 1) * ps])
             held.hashes.append(digest)
-            pool.set_hash(held.tables[0][i], digest)
+            pool.set_name(held.tables[0][i], digest)
 
     def _first_needed_page(self, group: int, context_len: int) -> int:
         """Index of the first page that a query at position >= context_len can still read."""
@@ -344,13 +353,13 @@ class CacheManager:
             for page, n in holders.items():
                 assert pool.holders(page) == n, f"group {g}: page {page} has {n} holders, the pool counts {pool.holders(page)}"
                 assert n == 1 or self.prefix_sharing, f"group {g}: page {page} is held {n} times"
-            free, cached = list(pool._free), list(pool._cached)
-            assert len(set(free)) == len(free), f"group {g}: a page is in the free list twice"
-            assert not set(free) & set(holders) and not set(cached) & set(holders), f"group {g}: a page is both free and held"
-            assert not set(free) & set(cached), f"group {g}: a page is both free and cached"
-            assert NULL_PAGE not in free and NULL_PAGE not in holders and NULL_PAGE not in cached
-            assert all(pool.holders(page) == 0 for page in free + cached), f"group {g}: a free page has holders"
-            assert all(pool._hash[page] is not None and pool._by_hash[pool._hash[page]] == page for page in cached)
-            assert all(pool._hash[page] is None for page in free), f"group {g}: a free page has a name"
-            lost = pool.capacity - len(free) - len(cached) - len(holders)
+            idle = pool.idle_pages()
+            assert len(set(idle)) == len(idle), f"group {g}: a page is idle twice"
+            assert not set(idle) & set(holders), f"group {g}: a page is both idle and held"
+            assert NULL_PAGE not in idle and NULL_PAGE not in holders
+            assert all(pool.holders(page) == 0 for page in idle), f"group {g}: an idle page has users"
+            named = [pool.name_of(page) is not None for page in idle]
+            assert named == sorted(named), f"group {g}: a named page would be handed out before a nameless one"
+            assert all(pool.find(pool.name_of(page)) == page for page in range(1, pool.num_pages) if pool.name_of(page) is not None)
+            lost = pool.capacity - len(idle) - len(holders)
             assert lost == 0, f"group {g}: {lost} pages lost"

@@ -32,6 +32,29 @@ def _need(d: Mapping[str, Any], key: str, kind):
     return v
 
 
+def _refuse_unread_arithmetic(d: Mapping[str, Any]) -> None:
+    """Keys that change the model's arithmetic and that this engine does not carry out: a checkpoint that sets one of
+    them would give wrong logits without a word (the reference reads none of them, src/miniserve/model.py:42-58, and
+    is silent). A key that is absent, null or at its neutral value is fine."""
+    nested = d.get("rope_parameters") if isinstance(d.get("rope_parameters"), Mapping) else {}
+    scaling = d.get("rope_scaling")
+    if scaling is None and nested.get("rope_type") not in (None, "default"):
+        scaling = {k: v for k, v in nested.items() if k != "rope_theta"}
+    if isinstance(scaling, Mapping) and (scaling.get("rope_type") or scaling.get("type")) == "default":
+        scaling = None
+    if scaling is not None:
+        raise ConfigError(f"config.json: 'rope_scaling' is {scaling!r}; scaled rotary positions are not built here "
+                          "(only plain rotary positions with 'rope_theta')")
+    prf = d.get("partial_rotary_factor", nested.get("partial_rotary_factor"))
+    if prf is not None and float(prf) != 1.0:
+        raise ConfigError(f"config.json: 'partial_rotary_factor' is {prf!r}; only whole heads are rotated here (1.0)")
+    drop = d.get("attention_dropout")
+    if drop is not None and float(drop) != 0.0:
+        raise ConfigError(f"config.json: 'attention_dropout' is {drop!r}; an inference engine has none (0.0)")
+    if d.get("mlp_bias"):
+        raise ConfigError("config.json: 'mlp_bias' is true; the feed-forward of Qwen2 has no biases")
+
+
 @dataclass(frozen=True)
 class Qwen2Config:
     """The dense Qwen2 decoder: GQA attention with QKV bias, rotary positions, RMSNorm, SwiGLU."""
@@ -59,6 +82,7 @@ class Qwen2Config:
     # ------------------------------------------------------------------ reading
     @classmethod
     def from_dict(cls, d: Mapping[str, Any]) -> "Qwen2Config":
+        _refuse_unread_arithmetic(d)
         heads = _need(d, "num_attention_heads", int)
         hidden = _need(d, "hidden_size", int)
         rope = d.get("rope_theta")

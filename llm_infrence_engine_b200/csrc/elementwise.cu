@@ -12,19 +12,6 @@ LLMIE_API int llmie_set_pdl(int on) {
 }
 
 // ------------------------------------------------------------------------------------------------
-// A kernel that does nothing but take its place in the stream's dependency chain: what a kernel boundary costs
-// on this device (with and without programmatic dependent launch) is measured with chains of these.
-__global__ void noop_kernel(int* sink) {
-    pdl_trigger();
-    pdl_wait();
-    if (sink && threadIdx.x == 0 && blockIdx.x == 0xffffffffu) *sink = 0;
-}
-
-LLMIE_API int llmie_noop(int blocks, int threads, int* sink, cudaStream_t s) {
-    return launch_kernel(noop_kernel, dim3(blocks), dim3(threads), 0, s, sink);
-}
-
-// ------------------------------------------------------------------------------------------------
 // x[n, :] = table[ids[n], :]  widened to float (the residual stream)
 template <typename T>
 __global__ void embed_kernel(const int* __restrict__ ids, const T* __restrict__ table, float* __restrict__ out, int H) {

@@ -62,7 +62,8 @@ class CudaKernels:
         # the stream: that kernel is usually the norm, which adds and normalises in one pass (see ``flush``).
         self._pending_add: Optional[tuple] = None
         self._error_flag: Optional[torch.Tensor] = None
-        self.num_sms = torch.cuda.get_device_properties(0).multi_processor_count or NUM_SMS_FALLBACK
+        self._retired_acc: list = []   # accumulation buffers that were outgrown: captured graphs may still add into and clear them
+        self._sms: dict = {}
         for fn in ("llmie_embed", "llmie_feed_tokens", "llmie_rope_tables", "llmie_add_rmsnorm", "llmie_rope_kv_write", "llmie_silu_mul",
                    "llmie_gemm_simt", "llmie_gemm_tc", "llmie_qkv_rope_tc", "llmie_add_into", "llmie_attn_plan", "llmie_attn_tc_plan", "llmie_paged_attention_mma", "llmie_paged_attention_tc", "llmie_paged_attention_f32", "llmie_paged_attention_bf16", "llmie_argmax", "llmie_sample"):
             getattr(self.lib, fn).restype = ctypes.c_int
@@ -70,6 +71,25 @@ class CudaKernels:
         self.lib.llmie_set_pdl(0 if os.environ.get("LLMIE_PDL", "1") == "0" else 1)
 
     # ------------------------------------------------------------------ helpers
+    @property
+    def num_sms(self) -> int:
+        """Multiprocessors of the device the kernels launch on (torch's current device)."""
+        dev = torch.cuda.current_device()
+        if dev not in self._sms:
+            self._sms[dev] = torch.cuda.get_device_properties(dev).multi_processor_count or NUM_SMS_FALLBACK
+        return self._sms[dev]
+
+    def abandon_step(self) -> None:
+        """After an exception in the middle of a step: nothing of it may reach the next one. An addition that was put off
+        is dropped, and the accumulation buffers, which every product assumes to be zero, are cleared."""
+        self._pending_add = None
+        for t in [self._acc, *self._retired_acc]:
+            if t is not None:
+                try:
+                    t.zero_()
+                except RuntimeError:
+                    pass   # the device itself has failed: nothing more can be done here
+
     @staticmethod
     def _stream():
         # the raw handle of the current stream, without building a Stream object (this runs before every launch)
@@ -184,8 +204,16 @@ class CudaKernels:
 
     def _transient(self, M: int, N: int, device) -> torch.Tensor:
         if self._acc is None or self._acc.numel() < M * N or self._acc.device != device:
+            if self._acc is not None:
+                self._retired_acc.append(self._acc)  # a captured graph may still add into it and clear it: never given back
             self._acc = torch.zeros(max(M * N, 1 << 20), dtype=torch.float32, device=device)
         return self._acc[: M * N].view(M, N)
+
+    def reserve_transient(self, widest: int, device) -> None:
+        """Make the accumulation buffer large enough for the small-batch products of a model whose widest projection has
+        ``widest`` outputs (a runner does this before anything is captured, so that the buffer need not grow later; if it
+        grows all the same, the outgrown buffer is kept for the graphs that hold its address)."""
+        self._transient(self.tc_max_rows, widest, torch.device(device))
 
     def linear(self, x, w, out_dtype=None, add_to=None, transient=False):
         """``x w^T`` for ``x [rows, K]`` and ``w [outputs, K]``.
@@ -273,14 +301,22 @@ class CudaKernels:
             self._error_flag = torch.zeros(1, dtype=torch.int32, device=device)
         return self._error_flag
 
+    def error_flag(self, device) -> torch.Tensor:
+        """The device word that a kernel sets when it gives up on a bounded wait (0: nothing happened). Whoever reads a
+        step's results back reads this word with them and hands it to ``raise_for_error_code``."""
+        return self._errors(torch.device(device))
+
+    def raise_for_error_code(self, code: int) -> None:
+        if code:
+            if self._error_flag is not None:
+                self._error_flag.zero_()
+            raise KernelError(f"a block of a tcgen05 kernel gave up waiting on a barrier (code {code}: 1-4 matrix product, "
+                              "11-16 attention); its output is not valid, and neither is what later steps made of it")
+
     def check_device_errors(self) -> None:
         """Raise if a kernel gave up on a bounded wait since the last check (reads one integer back)."""
         if self._error_flag is not None:
-            code = int(self._error_flag.item())
-            if code:
-                self._error_flag.zero_()
-                raise KernelError(f"a block of a tcgen05 kernel gave up waiting on a barrier (code {code}: 1-4 matrix product, "
-                                  "11-16 attention); its output is not valid")
+            self.raise_for_error_code(int(self._error_flag.item()))
 
     def rope_kv_write(self, qkv, bias, cos, sin, slot_mapping, k_pool, v_pool, num_heads, num_kv_heads, head_dim, page_size,
                       write_kv=True, out_dtype=None):

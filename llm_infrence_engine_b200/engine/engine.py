@@ -72,6 +72,7 @@ class Engine:
         self._inflight = None        # (requests, their tokens on the device, pinned copy, event) of the step that was launched last
         self._token_ring: list = []
         self._token_next = 0
+        self._prev_read = False
 
     @classmethod
     def from_pretrained(cls, model: Union[str, Path], **kw) -> "Engine":
@@ -117,6 +118,13 @@ class Engine:
     def run_until_idle(self) -> None:
         while self.has_work():
             self.step()
+        self._final_check()
+
+    def _final_check(self) -> None:
+        """A step without sampled rows (a prompt portion) hands nothing back with which the error word could ride."""
+        check = getattr(self.runner.K, "check_device_errors", None)
+        if check is not None and self.runner.device.type == "cuda":
+            check()
 
     def step(self) -> StepRecord:
         """One step of the engine. With ``EngineConfig.pipeline`` the tokens a step chooses stay on the device: the next
@@ -125,6 +133,17 @@ class Engine:
         whose token turns out to be a stop token has by then been given one more row, whose result is dropped."""
         t0 = self.clock()
         prev, self._inflight = self._inflight, None
+        try:
+            return self._step(prev, t0)
+        except BaseException:
+            # The step did not happen: the scheduler was not advanced, so the same tokens are planned again next time
+            # (pages that were reserved stay with their requests). The tokens of the step before are still unread.
+            if prev is not None and self._inflight is None and not self._prev_read:
+                self._inflight = prev
+            raise
+
+    def _step(self, prev, t0: float) -> StepRecord:
+        self._prev_read = False
         plan = self.scheduler.schedule()
         now = self.clock()
         for r in plan.aborted:
@@ -153,18 +172,25 @@ class Engine:
                 params = [SamplingParams(r.temperature, r.top_k, r.top_p, self._seed(r)) for r in rows]
                 greedy = self.runner.greedy_tokens if len(rows) == len(plan.items) else None
                 chosen = self.sampler.sample_device(logits, params, [len(r.output_ids) + r.in_flight for r in rows], greedy)
+                flag = self._error_word()
                 if self._pipeline:
                     pinned, event = self._token_buffer()
                     pinned[:len(rows)].copy_(chosen, non_blocking=True)
+                    if flag is not None:   # the kernels' error word rides with the tokens: reading it costs no wait of its own
+                        pinned[-1:].copy_(flag, non_blocking=True)
                     event.record()
                     for r in rows:
                         r.in_flight += 1
                     self._inflight = (rows, chosen, pinned, event)
                 else:
-                    for r, tok in zip(rows, chosen.tolist()):
+                    values = (chosen if flag is None else torch.cat([chosen, flag])).tolist()
+                    if flag is not None:
+                        self.runner.K.raise_for_error_code(values.pop())
+                    for r, tok in zip(rows, values):
                         self._emit(r, int(tok))
                         useful += 1
         if prev is not None:
+            self._prev_read = True
             useful += self._read(prev)
         decode = sum(1 for s in plan.items if s.count == 1 and s.start > 0)
         n_tok = plan.num_tokens
@@ -176,10 +202,16 @@ class Engine:
         self.steps.append(rec)
         return rec
 
+    def _error_word(self):
+        """The device word in which a kernel reports that it gave up on a bounded wait (None if these kernels have none)."""
+        get = getattr(self.runner.K, "error_flag", None)
+        return get(self.runner.device) if get is not None and self.runner.device.type == "cuda" else None
+
     def _token_buffer(self):
-        """A pinned buffer for one step's chosen tokens and the event of its copy, from a ring of three."""
+        """A pinned buffer for one step's chosen tokens (and, last, the kernels' error word) and the event of its copy,
+        from a ring of three."""
         if not self._token_ring:
-            self._token_ring = [(torch.empty(max(self.config.max_seqs, 1), dtype=torch.int32, pin_memory=True), torch.cuda.Event())
+            self._token_ring = [(torch.zeros(max(self.config.max_seqs, 1) + 1, dtype=torch.int32, pin_memory=True), torch.cuda.Event())
                                 for _ in range(3)]
         self._token_next = (self._token_next + 1) % len(self._token_ring)
         return self._token_ring[self._token_next]
@@ -188,6 +220,10 @@ class Engine:
         """Wait for a launched step's tokens and hand them to their requests; returns how many were kept."""
         rows, _, pinned, event = inflight
         event.synchronize()
+        code = int(pinned[-1])
+        if code:
+            pinned[-1] = 0
+            self.runner.K.raise_for_error_code(code)  # these tokens, and the cache entries behind them, are not to be trusted
         kept = 0
         for r, tok in zip(rows, pinned[:len(rows)].tolist()):
             r.in_flight -= 1
@@ -260,6 +296,7 @@ class Engine:
         while any(r.state != "finished" for r in reqs):
             self.step()
         self.drain()
+        self._final_check()
         total = self.clock() - t0
         out = []
         for r in reqs:

@@ -129,6 +129,11 @@ class ModelRunner:
         self._staging: List[list] = []  # ring of [pinned buffer, event of the copy that last read it]
         self._next_staging = 0
         self.last_h2d_bytes = 0  # bytes of step inputs copied to the device by the last step
+        if hasattr(kernels, "reserve_transient") and self.device.type == "cuda" and dtype == torch.bfloat16:
+            widest = max((p.shape[0] for part in spec.parts() for p in part.params().values() if p.kind == "matrix"
+                          and part is not spec.embedding and part is not spec.head), default=0)
+            if widest:
+                kernels.reserve_transient(widest, self.device)
         self.greedy_tokens = None
         self.graphs = None
         if cuda_graphs:
@@ -370,6 +375,17 @@ class ModelRunner:
         return self.forward(ctx, logit_rows)
 
     def forward(self, ctx: StepContext, logit_rows: torch.Tensor) -> Optional[torch.Tensor]:
+        """The model on the step's batch. If anything raises in the middle, the kernels object is told to drop what the
+        unfinished step left with it (``abandon_step``), so that the next step, of whatever request or runner, starts clean."""
+        try:
+            return self._forward(ctx, logit_rows)
+        except BaseException:
+            abandon = getattr(self.K, "abandon_step", None)
+            if abandon is not None:
+                abandon()
+            raise
+
+    def _forward(self, ctx: StepContext, logit_rows: torch.Tensor) -> Optional[torch.Tensor]:
         spec = self.spec
         residual = spec.embedding.forward(ctx)
         for call in spec.schedule:

@@ -43,6 +43,10 @@ class OutputHead(Part):
         """Checkpoint names that may be present without being read."""
         return (self.name,) if self.tied_to is not None else ()
 
+    def aliases(self) -> Dict[str, str]:
+        """Ignored checkpoint name -> the tensor that stands in for it; the loader warns when the two differ."""
+        return {self.name: self.tied_to.name} if self.tied_to is not None else {}
+
     def matrix(self) -> torch.Tensor:
         return self.tied_to.table if self.tied_to is not None else self.weight
 

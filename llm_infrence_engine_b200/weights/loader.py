@@ -12,6 +12,7 @@ together are joined along their output rows here, once.
 """
 from __future__ import annotations
 
+import warnings
 from pathlib import Path
 from typing import Dict, List, Tuple
 
@@ -90,6 +91,16 @@ def load_weights(spec: ModelSpec, folder: str | Path, dtype: torch.dtype, device
                 wrong_dtype.append((name, got_dtype, "a floating type"))
         if missing or unexpected or wrong_shape or wrong_dtype:
             raise WeightsError(folder, sorted(missing), sorted(unexpected), wrong_shape, wrong_dtype)
+
+        # A tensor that is present but stands aside for another (the output head of a tied checkpoint) should be that
+        # other tensor; the reference re-ties without looking (src/miniserve/loader.py:46-47). Here a difference is said.
+        for part in spec.parts():
+            for aside, used in getattr(part, "aliases", lambda: {})().items():
+                if aside in where and used in where:
+                    a, b = where[aside].tensor(aside), where[used].tensor(used)
+                    if a.shape != b.shape or not torch.equal(a, b):
+                        warnings.warn(f"{folder}: '{aside}' differs from '{used}', which the configuration ties it to; "
+                                      f"'{aside}' is not used", stacklevel=2)
 
         total = 0
         for part in spec.parts():

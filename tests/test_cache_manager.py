@@ -141,13 +141,14 @@ def test_prefix_sharing_takes_over_full_pages_and_keeps_one_token():
     m.free("b")
     m.check_invariants()
     pool = m.pools[0]
-    assert pool.num_free == pool.capacity and len(pool._cached) == 2
+    assert pool.num_free == pool.capacity and sum(pool.name_of(p) is not None for p in pool.idle_pages()) == 2
+    assert [pool.name_of(p) is not None for p in pool.idle_pages()] == [False] * 4 + [True] * 2   # named pages are handed out last
     m.admit("e")
     assert m.share_prefix("e", a) == 8             # found again after their holders had gone
     m.free("e")
     m.admit("f")
     m.reserve("f", 0, 24)                           # all six pages: the cached ones are evicted, oldest first
-    assert pool.evictions == 2 and not pool._cached and not pool._by_hash
+    assert pool.names_given_up == 2 and not pool.idle_pages() and all(pool.name_of(p) is None for p in range(1, 7))
     m.check_invariants()
     m.free("f")
     m.admit("g")

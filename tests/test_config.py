@@ -35,10 +35,22 @@ def test_defaults_follow_the_reference():
     ({"use_sliding_window": True, "sliding_window": None}, "sliding_window"),
     ({"rms_norm_eps": 0.0}, "rms_norm_eps"),
     ({"vocab_size": "many"}, "vocab_size"),
+    ({"rope_scaling": {"type": "yarn", "factor": 4.0, "original_max_position_embeddings": 32768}}, "rope_scaling"),
+    ({"rope_parameters": {"rope_theta": 1e6, "rope_type": "linear", "factor": 2.0}}, "rope_scaling"),
+    ({"partial_rotary_factor": 0.5}, "partial_rotary_factor"),
+    ({"attention_dropout": 0.1}, "attention_dropout"),
+    ({"mlp_bias": True}, "mlp_bias"),
 ])
 def test_rejects_what_makes_no_sense(change, match):
     with pytest.raises(ConfigError, match=match):
         Qwen2Config.from_dict(dict(TINY_A, **change))
+
+
+def test_neutral_values_of_unread_keys_pass():
+    """Absent, null or neutral: nothing to refuse (real Qwen2 checkpoints carry ``attention_dropout: 0.0``)."""
+    c = Qwen2Config.from_dict(dict(TINY_A, rope_scaling=None, attention_dropout=0.0, partial_rotary_factor=1.0, mlp_bias=False,
+                                   rope_parameters={"rope_theta": 1e4, "rope_type": "default"}))
+    assert c.rope_theta == TINY_A["rope_theta"]
 
 
 def test_missing_key_is_named():

@@ -126,3 +126,45 @@ def test_graph_buckets_and_warmup_without_graphs(folders):
     eng = Engine(str(folder), kernels=TorchKernels(), device="cpu", dtype="float32", block_size=PAGE_SIZES["A"], num_blocks=20,
                  max_seqs=3, max_len=64)
     assert eng.warmup() == [] and eng.warmup([1, 2]) == []
+
+
+def test_a_step_that_raises_loses_nothing(folders):
+    """An exception in the middle of the step function (a simulated allocation failure inside the third layer call of one
+    step) reaches the caller of ``Engine.step``; the engine is still usable: the caller cancels one request, the others go
+    on and produce exactly the plain tokens, and in the end every page and slot is back. (The reference's analogue is its
+    server's crash test, tests/test_server.py:173-189: it fails the requests and flips health; this engine can go on.)"""
+    cfg, w = plain_load(folders["B"])
+    prompts = [random_prompt(320, n, 30 + n) for n in (9, 21, 5)]
+
+    class Failing(TorchKernels):
+        def __init__(self):
+            super().__init__()
+            self.calls, self.fail_at = 0, None
+
+        def paged_attention(self, *a, **kw):
+            self.calls += 1
+            if self.calls == self.fail_at:
+                raise MemoryError("simulated: out of memory inside the step")
+            return super().paged_attention(*a, **kw)
+
+    K = Failing()
+    eng = Engine(str(folders["B"]), dtype="float32", device="cpu", kernels=K, block_size=8, num_blocks=20, max_seqs=3,
+                 max_len=64, max_num_batched_tokens=16)
+    reqs = [eng.add_request(Request(p, max_new_tokens=10)) for p in prompts]
+    for _ in range(4):
+        eng.step()
+    before = [list(r.output_ids) for r in reqs]
+    computed = [r.num_computed for r in reqs]
+    K.fail_at = K.calls + 2   # the second layer of the next step: the first layer's keys are already written
+    with pytest.raises(MemoryError):
+        eng.step()
+    assert [list(r.output_ids) for r in reqs] == before and [r.num_computed for r in reqs] == computed
+    eng.cache.check_invariants()
+    eng.cancel(reqs[1])
+    while eng.has_work():
+        eng.step()
+        eng.cache.check_invariants()
+    assert reqs[1].finish_reason == "abort" and reqs[1].output_ids == before[1]
+    for i in (0, 2):
+        assert reqs[i].output_ids == plain_generate(cfg, w, prompts[i], 10) and reqs[i].finish_reason == "length"
+    assert all(pool.num_free == pool.capacity for pool in eng.cache.pools) and eng.cache.num_free_slots() == 3

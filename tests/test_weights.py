@@ -82,7 +82,17 @@ def test_tied_checkpoint_may_carry_the_head_name(tmp_path):
     f.close()
     t["lm_head.weight"] = t["model.embed_tokens.weight"].clone()
     write_safetensors(folder / "model.safetensors", t)
-    load_weights(build_model_spec(TINY_A), folder, torch.float32, "cpu")  # no error: the name is known and not needed
+    import warnings
+
+    with warnings.catch_warnings():
+        warnings.simplefilter("error")   # equal to the table: no error, no warning; the name is known and not needed
+        load_weights(build_model_spec(TINY_A), folder, torch.float32, "cpu")
+    t["lm_head.weight"][3, 5] += 1.0
+    write_safetensors(folder / "model.safetensors", t)
+    spec = build_model_spec(TINY_A)
+    with pytest.warns(UserWarning, match="lm_head.weight.*differs.*model.embed_tokens.weight"):
+        load_weights(spec, folder, torch.float32, "cpu")
+    assert spec.head.matrix() is spec.embedding.table   # the table is what is used, as the configuration says
 
 
 def test_no_file(tmp_path):
