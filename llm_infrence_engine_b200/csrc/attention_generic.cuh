@@ -25,7 +25,7 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attn_kernel(
     const T* __restrict__ q, int q_stride, const T* __restrict__ k_pool, const T* __restrict__ v_pool,
     const int* __restrict__ block_table, int max_blocks, const int* __restrict__ token_seq, const int* __restrict__ positions,
     T* __restrict__ out, float* __restrict__ part_acc, float* __restrict__ part_ml, int nq, int nkv, int d, int page_size,
-    float scale, int window, int num_splits) {
+    float scale, int window, int num_splits, int slice_keys) {
     constexpr int DMAX = DPL * 32;
     __shared__ float qs[GC][DMAX];
     __shared__ float ps[WARPS][GC][32];
@@ -44,10 +44,20 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attn_kernel(
     const int p = positions[n];
     const int lo = window > 0 ? max(0, p - window + 1) : 0;
     const int hi = p + 1;
-    int per = (hi - lo + num_splits - 1) / num_splits;
-    per = (per + 31) & ~31;
-    const int start = lo + split * per;
-    const int end = min(hi, start + per);
+    // Two ways of cutting the keys into slices. `slice_keys` > 0: slice s holds the keys [s * slice_keys, (s + 1) * slice_keys)
+    // of the request, whatever else is in the batch and however many slices are launched (slices beyond the token's
+    // position are empty), so a token's arithmetic, and with it every bit of its result, depends on its own position
+    // alone. Otherwise the token's visible keys are cut into `num_splits` equal runs.
+    int start, end;
+    if (slice_keys > 0) {
+        start = split * slice_keys;
+        end = min(hi, start + slice_keys);
+    } else {
+        int per = (hi - lo + num_splits - 1) / num_splits;
+        per = (per + 31) & ~31;
+        start = lo + split * per;
+        end = min(hi, start + per);
+    }
     const int* table = block_table + (size_t)token_seq[n] * max_blocks;
 
     for (int i = threadIdx.x; i < GC * DMAX; i += blockDim.x) {
@@ -69,8 +79,9 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attn_kernel(
 
     constexpr int VN = Vec16<T>::N;
     for (int base = start + warp * 32; base < end; base += WARPS * 32) {
+        if (base + 32 <= lo) continue;  // (absolute slices only) every key of the chunk lies before the window
         const int key = base + lane;
-        const bool valid = key < end;
+        const bool valid = key < end && key >= lo;
         int row = 0;
         float s[GC];
 #pragma unroll
@@ -105,7 +116,7 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attn_kernel(
 #pragma unroll
             for (int i = 0; i < DPL; ++i) acc[g][i] *= corr[g];
         const int count = min(32, end - base);
-        for (int j = 0; j < count; ++j) {
+        for (int j = max(0, lo - base); j < count; ++j) {
             const int rj = __shfl_sync(0xffffffffu, row, j);
             const T* vr = v_pool + (size_t)rj * d;
             float vv[DPL];
@@ -177,11 +188,11 @@ __global__ void attn_combine_kernel(const float* __restrict__ part_acc, const fl
 template <typename T, int DPL>
 int launch_gc(int GC, dim3 grid, cudaStream_t s, const T* q, int q_stride, const T* k_pool, const T* v_pool,
               const int* block_table, int max_blocks, const int* token_seq, const int* positions, T* out, float* part_acc,
-              float* part_ml, int nq, int nkv, int d, int page_size, float scale, int window, int num_splits) {
+              float* part_ml, int nq, int nkv, int d, int page_size, float scale, int window, int num_splits, int slice_keys) {
 #define LLMIE_ATTN_LAUNCH(GCV)                                                                                              \
     paged_attn_kernel<T, DPL, GCV><<<grid, WARPS * 32, 0, s>>>(q, q_stride, k_pool, v_pool, block_table, max_blocks,          \
                                                                token_seq, positions, out, part_acc, part_ml, nq, nkv, d,     \
-                                                               page_size, scale, window, num_splits)
+                                                               page_size, scale, window, num_splits, slice_keys)
     switch (GC) {
         case 1: LLMIE_ATTN_LAUNCH(1); break;
         case 2: LLMIE_ATTN_LAUNCH(2); break;
@@ -200,9 +211,9 @@ inline size_t scratch_floats(int N, int nq, int d, int num_splits) {
 template <typename T>
 int paged_attention(const T* q, int q_stride, const T* k_pool, const T* v_pool, const int* block_table, int max_blocks,
                     const int* token_seq, const int* positions, T* out, float* scratch, int N, int nq, int nkv, int d,
-                    int page_size, float scale, int window, int num_splits, cudaStream_t s) {
+                    int page_size, float scale, int window, int num_splits, int slice_keys, cudaStream_t s) {
     if (N <= 0) return 0;
-    if (nkv <= 0 || nq % nkv || d <= 0 || d > 256 || d % Vec16<T>::N || page_size <= 0 || num_splits < 1 ||
+    if (nkv <= 0 || nq % nkv || d <= 0 || d > 256 || d % Vec16<T>::N || page_size <= 0 || num_splits < 1 || slice_keys < 0 || slice_keys % 32 ||
         (num_splits > 1 && !scratch) || q_stride % Vec16<T>::N)
         return LLMIE_ERR_BAD_ARGUMENT;
     const int G = nq / nkv;
@@ -213,10 +224,10 @@ int paged_attention(const T* q, int q_stride, const T* k_pool, const T* v_pool, 
     float* part_acc = scratch;
     float* part_ml = scratch ? scratch + (size_t)N * nq * num_splits * d : nullptr;
     int rc;
-    if (d <= 32) rc = launch_gc<T, 1>(GC, grid, s, q, q_stride, k_pool, v_pool, block_table, max_blocks, token_seq, positions, out, part_acc, part_ml, nq, nkv, d, page_size, scale, window, num_splits);
-    else if (d <= 64) rc = launch_gc<T, 2>(GC, grid, s, q, q_stride, k_pool, v_pool, block_table, max_blocks, token_seq, positions, out, part_acc, part_ml, nq, nkv, d, page_size, scale, window, num_splits);
-    else if (d <= 128) rc = launch_gc<T, 4>(GC, grid, s, q, q_stride, k_pool, v_pool, block_table, max_blocks, token_seq, positions, out, part_acc, part_ml, nq, nkv, d, page_size, scale, window, num_splits);
-    else rc = launch_gc<T, 8>(GC, grid, s, q, q_stride, k_pool, v_pool, block_table, max_blocks, token_seq, positions, out, part_acc, part_ml, nq, nkv, d, page_size, scale, window, num_splits);
+    if (d <= 32) rc = launch_gc<T, 1>(GC, grid, s, q, q_stride, k_pool, v_pool, block_table, max_blocks, token_seq, positions, out, part_acc, part_ml, nq, nkv, d, page_size, scale, window, num_splits, slice_keys);
+    else if (d <= 64) rc = launch_gc<T, 2>(GC, grid, s, q, q_stride, k_pool, v_pool, block_table, max_blocks, token_seq, positions, out, part_acc, part_ml, nq, nkv, d, page_size, scale, window, num_splits, slice_keys);
+    else if (d <= 128) rc = launch_gc<T, 4>(GC, grid, s, q, q_stride, k_pool, v_pool, block_table, max_blocks, token_seq, positions, out, part_acc, part_ml, nq, nkv, d, page_size, scale, window, num_splits, slice_keys);
+    else rc = launch_gc<T, 8>(GC, grid, s, q, q_stride, k_pool, v_pool, block_table, max_blocks, token_seq, positions, out, part_acc, part_ml, nq, nkv, d, page_size, scale, window, num_splits, slice_keys);
     if (rc) return rc;
     if (num_splits > 1) {
         attn_combine_kernel<T><<<N * nq, 64, 0, s>>>(part_acc, part_ml, out, d, num_splits);

@@ -49,10 +49,10 @@ LLMIE_API int llmie_paged_attention_noalloc(const void* q, int q_stride, const v
     if (dtype == DT_F32)
         return attn_generic::paged_attention<float>((const float*)q, q_stride, (const float*)k_pool, (const float*)v_pool, block_table,
                                                     max_blocks, token_seq, positions, (float*)out, scratch, num_tokens, num_heads,
-                                                    num_kv_heads, head_dim, page_size, scale, window, num_splits, stream);
+                                                    num_kv_heads, head_dim, page_size, scale, window, num_splits, 0, stream);
     return attn_generic::paged_attention<bf16>((const bf16*)q, q_stride, (const bf16*)k_pool, (const bf16*)v_pool, block_table,
                                                max_blocks, token_seq, positions, (bf16*)out, scratch, num_tokens, num_heads,
-                                               num_kv_heads, head_dim, page_size, scale, window, num_splits, stream);
+                                               num_kv_heads, head_dim, page_size, scale, window, num_splits, 0, stream);
 }
 
 LLMIE_API const char* llmie_noalloc_error_string(int code) {

@@ -57,6 +57,7 @@ class CudaKernels:
         self.use_tc_gemm = True
         self.use_tc_qkv = True         # prompt portions, head size 64: q/k/v product with bias, rotation and cache write in one kernel
         self.tc_max_rows = 128        # batches up to this many rows take the small-batch tensor-core product
+        self.slice_keys = 1024         # generic attention: keys per slice, at fixed places of a request (a multiple of 32)
         self._acc: Optional[torch.Tensor] = None  # float32 zeros: split-K products add into it, their consumer clears it again
         # A library product that is to be added into the residual stream is kept here until the next kernel that reads
         # the stream: that kernel is usually the norm, which adds and normalises in one pass (see ``flush``).
@@ -64,6 +65,7 @@ class CudaKernels:
         self._error_flag: Optional[torch.Tensor] = None
         self._retired_acc: list = []   # accumulation buffers that were outgrown: captured graphs may still add into and clear them
         self._sms: dict = {}
+        self.last_attention_plan = (1, False)   # (key slices, merged as a cluster) of the last tensor-core attention launch
         for fn in ("llmie_embed", "llmie_feed_tokens", "llmie_rope_tables", "llmie_add_rmsnorm", "llmie_rope_kv_write", "llmie_silu_mul",
                    "llmie_gemm_simt", "llmie_gemm_tc", "llmie_qkv_rope_tc", "llmie_add_into", "llmie_attn_plan", "llmie_attn_tc_plan", "llmie_paged_attention_mma", "llmie_paged_attention_tc", "llmie_paged_attention_f32", "llmie_paged_attention_bf16", "llmie_argmax", "llmie_sample"):
             getattr(self.lib, fn).restype = ctypes.c_int
@@ -286,8 +288,7 @@ class CudaKernels:
             out = torch.empty((M, N), dtype=torch.float32, device=w.device)
         if out.dtype != torch.float32 or out.dim() != 2 or tuple(out.shape) != (M, N) or out.stride(1) != 1:
             raise KernelError("linear_tc: out must be float32 [rows of x, rows of w] with unit column stride")
-        if self._error_flag is None:
-            self._error_flag = torch.zeros(1, dtype=torch.int32, device=w.device)
+        self._errors(w.device)
         if k_splits is None:
             k_splits = self.tc_splits(M, N, K) if accumulate else 1
         self._need(x, "x", torch.bfloat16, 2)
@@ -298,7 +299,8 @@ class CudaKernels:
 
     def _errors(self, device) -> torch.Tensor:
         if self._error_flag is None:
-            self._error_flag = torch.zeros(1, dtype=torch.int32, device=device)
+            with torch.inference_mode(False):  # an ordinary tensor: it is cleared later from code that runs outside inference mode
+                self._error_flag = torch.zeros(1, dtype=torch.int32, device=device)
         return self._error_flag
 
     def error_flag(self, device) -> torch.Tensor:
@@ -388,11 +390,11 @@ class CudaKernels:
         return self.rope_kv_write(qkv, bias, cos, sin, slot_mapping, k_pool, v_pool, num_heads, num_kv_heads, head_dim, page_size,
                                   write_kv, out_dtype=out_dtype)
 
-    def attention_splits(self, num_tokens: int, num_kv_heads: int, max_context: int) -> int:
-        """Slices of the keys per token: enough blocks to fill the device, at least 256 keys each."""
-        blocks = max(1, num_tokens * num_kv_heads)
-        want = -(-4 * self.num_sms // blocks)
-        return max(1, min(want, -(-max_context // 256), 64))
+    def attention_slices(self, max_context: int) -> int:
+        """Key slices that the generic attention kernel is launched with: slice s of a request always holds its keys
+        ``[s * slice_keys, (s + 1) * slice_keys)``, so how a token's keys are cut depends on its own position only, never on
+        the batch it is in; a slice beyond a token's position is empty and adds nothing (exactly nothing) to the merge."""
+        return max(1, -(-max_context // self.slice_keys))
 
     def _scratch(self, floats: int, device) -> torch.Tensor:
         if self._attn_scratch is None or self._attn_scratch.numel() < floats or self._attn_scratch.device != device:
@@ -433,12 +435,16 @@ class CudaKernels:
                 and group <= (16 if batch.max_seq_len == 1 else 64)):
             return self._attention_mma(qkv, k_pool, v_pool, block_table, token_seq, positions, out, num_heads, num_kv_heads,
                                        head_dim, page_size, scale, window, span, batch, num_splits)
-        splits = num_splits or self.attention_splits(N, num_kv_heads, span)
+        # ``num_splits`` given: that many equal runs of each token's visible keys (tests of the kernel). Otherwise slices at
+        # fixed places of the request, which makes the 32-bit path bit-identical however a request is cut into steps
+        # and whatever else is in the batch.
+        slice_keys = 0 if num_splits else self.slice_keys
+        splits = num_splits or self.attention_slices(max_context)
         scratch = self._scratch(N * num_heads * splits * (head_dim + 2), qkv.device) if splits > 1 else None
         fn = self.lib.llmie_paged_attention_f32 if dt == 0 else self.lib.llmie_paged_attention_bf16
         self._check(fn(_ptr(qkv), qkv.shape[1], _ptr(k_pool), _ptr(v_pool), _ptr(block_table), block_table.shape[1],
                        _ptr(token_seq), _ptr(positions), _ptr(out), _ptr(scratch), N, num_heads, num_kv_heads, head_dim, page_size,
-                       ctypes.c_float(scale), int(window), splits, self._stream()), "paged_attention")
+                       ctypes.c_float(scale), int(window), splits, slice_keys, self._stream()), "paged_attention")
         if splits > 1:
             self.launches += 1
         return out
@@ -516,6 +522,7 @@ class CudaKernels:
         # memory); more slices than that go through scratch and a counter: clusters of eight blocks of this size do not
         # all fit on the device at once and were measured slower.
         cluster = int(decode and self.cluster_merge and 1 < num_splits <= (4 if explicit is None else 8))
+        self.last_attention_plan = (num_splits, bool(cluster))
         if num_splits > 1 and not cluster:
             cells = tiles * num_kv_heads * num_splits * rows
             buf = self._scratch(cells * (head_dim + 2), qkv.device)

@@ -28,12 +28,13 @@ ROUND_TO = 64     # every request's token count is rounded up to this when the p
 
 
 class TraceReplayer:
-    def __init__(self, model: str, dtype: str, max_tokens: int, device: str = "cuda:0", kernels=None, block_size: int = 16):
+    def __init__(self, model: str, dtype: str, max_tokens: int, device: str = "cuda:0", kernels=None, block_size: int = 16,
+                 cuda_graphs: bool = False):
         if ROUND_TO % block_size:
             raise ValueError(f"block_size must divide {ROUND_TO}")
         pages = -(-max_tokens // block_size) + 1  # + the null page
         cfg = EngineConfig(dtype=dtype, device=device, block_size=block_size, num_blocks=pages, max_seqs=MAX_LIVE,
-                           max_len=max(max_tokens, 1), max_num_batched_tokens=max(max_tokens, 1))
+                           max_len=max(max_tokens, 1), max_num_batched_tokens=max(max_tokens, 1), cuda_graphs=cuda_graphs)
         self.spec, self.cache, self.runner = build_runner(model, cfg, kernels)
         self.lengths: Dict[str, int] = {}
 

@@ -91,3 +91,29 @@ def write_safetensors(path: str | Path, tensors: Dict[str, torch.Tensor]) -> Non
         f.write(head)
         for raw in blobs:
             f.write(raw)
+
+
+def write_safetensors_stream(path: str | Path, metas, produce) -> None:
+    """The same file as ``write_safetensors``, one tensor at a time: ``metas`` lists ``(name, dtype, shape)`` in file order,
+    ``produce(name)`` returns that tensor when its turn comes. Nothing but the tensor being written is held in memory,
+    which lets folders of many gigabytes be written."""
+    header, offset = {}, 0
+    for name, dtype, shape in metas:
+        if dtype not in _NAMES:
+            raise ValueError(f"tensor '{name}' has dtype {dtype}, which cannot be written")
+        n = torch.empty((), dtype=dtype).element_size()
+        for d in shape:
+            n *= int(d)
+        header[name] = {"dtype": _NAMES[dtype], "shape": [int(d) for d in shape], "data_offsets": [offset, offset + n]}
+        offset += n
+    head = json.dumps(header, separators=(",", ":")).encode()
+    head += b" " * (-len(head) % 8)
+    with open(path, "wb") as f:
+        f.write(struct.pack("<Q", len(head)))
+        f.write(head)
+        for name, dtype, shape in metas:
+            t = produce(name).detach().cpu().contiguous()
+            if t.dtype != dtype or tuple(t.shape) != tuple(shape):
+                raise ValueError(f"tensor '{name}' came as {t.dtype} {list(t.shape)}, announced as {dtype} {list(shape)}")
+            if t.numel():
+                f.write(memoryview(t.view(torch.uint8).numpy().reshape(-1)))

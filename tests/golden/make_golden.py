@@ -27,7 +27,7 @@ sys.path.insert(0, str(HERE.parent.parent))
 from plain_qwen2 import plain_forward, plain_generate, plain_load, plain_logits_to_probs  # noqa: E402
 from tiny_configs import CONFIGS, SEEDS  # noqa: E402
 
-PROMPT_LENS = {"A": [1, 7, 19, 33], "B": [3, 12, 40]}
+PROMPT_LENS = {"A": [1, 7, 19, 33], "B": [3, 12, 40, 64, 97]}
 
 
 def prompts_for(name: str, vocab: int):

@@ -11,6 +11,13 @@ CPU and stores the small outputs; ``tests/test_plain.py`` checks them on every r
 Two things here have no counterpart in the reference and rest on the formulas alone: the sliding
 window of ``plain_attention`` (``window``), and the counter-based random numbers of
 ``plain_uniform`` that the sampler draws with.
+
+``store`` (default: nothing) is applied wherever the engine under test keeps an activation in its
+compute dtype: the normed rows, the rotated queries and keys, the values, the softmax weights, the
+attention's output, the gated activation, and the two results that are added to the residual stream
+(which itself, like the logits, stays 32-bit). With ``store=bf16_store`` the plain model shows how much
+bfloat16 storage alone moves the logits of a given model, which is what the bfloat16 tests measure
+the engine against.
 """
 from __future__ import annotations
 
@@ -60,12 +67,21 @@ def plain_load(folder: str | Path, dtype: torch.dtype = torch.float32) -> tuple[
 
 
 # ----------------------------------------------------------------------------- parts
-def plain_rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+def keep(x: torch.Tensor) -> torch.Tensor:
+    return x
+
+
+def bf16_store(x: torch.Tensor) -> torch.Tensor:
+    """What a value becomes when it is written as bfloat16 and read again."""
+    return x.to(torch.bfloat16).to(x.dtype)
+
+
+def plain_rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, store=keep) -> torch.Tensor:
     """model.py:69-73: reduce in 32-bit, cast back, then multiply by the weight."""
     dtype = x.dtype
     h = x.float()
     h = h * torch.rsqrt(h.pow(2).mean(-1, keepdim=True) + eps)
-    return weight * h.to(dtype)
+    return store(weight * store(h.to(dtype)))
 
 
 def plain_rope_tables(positions: torch.Tensor, head_dim: int, theta: float, dtype: torch.dtype):
@@ -83,7 +99,7 @@ def plain_apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> t
     return x * cos + rot * sin
 
 
-def plain_attention(x, w: dict, prefix: str, c: dict, cos, sin, window=None) -> torch.Tensor:
+def plain_attention(x, w: dict, prefix: str, c: dict, cos, sin, window=None, store=keep) -> torch.Tensor:
     """model.py:121-152 for one sequence x [T, hidden], no cache: causal softmax(q k^T / sqrt(d)) v.
 
     ``window`` (not in the reference): position i sees keys j with i - window < j <= i.
@@ -99,8 +115,9 @@ def plain_attention(x, w: dict, prefix: str, c: dict, cos, sin, window=None) -> 
     q = lin("q_proj").view(T, nq, d).transpose(0, 1)  # model.py:123
     k = lin("k_proj").view(T, nkv, d).transpose(0, 1)  # model.py:124
     v = lin("v_proj").view(T, nkv, d).transpose(0, 1)  # model.py:125
-    q = plain_apply_rope(q, cos, sin)  # model.py:127
-    k = plain_apply_rope(k, cos, sin)  # model.py:128
+    q = store(plain_apply_rope(q, cos, sin))  # model.py:127
+    k = store(plain_apply_rope(k, cos, sin))  # model.py:128
+    v = store(v)
     rep = nq // nkv
     k = k.repeat_interleave(rep, dim=0)  # model.py:137-139: query head h reads kv head h // rep
     v = v.repeat_interleave(rep, dim=0)
@@ -111,29 +128,29 @@ def plain_attention(x, w: dict, prefix: str, c: dict, cos, sin, window=None) -> 
     if window is not None:
         allowed = allowed & (j > i - window)
     scores = scores.masked_fill(~allowed, float("-inf"))
-    p = torch.softmax(scores, dim=-1)
-    out = (p @ v.float()).to(x.dtype)
+    p = store(torch.softmax(scores, dim=-1))
+    out = store((p @ v.float()).to(x.dtype))
     out = out.transpose(0, 1).reshape(T, nq * d)  # model.py:151
-    return out @ w[f"{prefix}.o_proj.weight"].T  # model.py:152, no bias
+    return store(out @ w[f"{prefix}.o_proj.weight"].T)  # model.py:152, no bias
 
 
-def plain_mlp(x, w: dict, prefix: str) -> torch.Tensor:
+def plain_mlp(x, w: dict, prefix: str, store=keep) -> torch.Tensor:
     """model.py:164-165: down(silu(gate(x)) * up(x)), no biases."""
     g = x @ w[f"{prefix}.gate_proj.weight"].T
     u = x @ w[f"{prefix}.up_proj.weight"].T
-    return (torch.nn.functional.silu(g) * u) @ w[f"{prefix}.down_proj.weight"].T
+    return store(store(torch.nn.functional.silu(g) * u) @ w[f"{prefix}.down_proj.weight"].T)
 
 
-def plain_block(x, w: dict, i: int, c: dict, cos, sin) -> torch.Tensor:
+def plain_block(x, w: dict, i: int, c: dict, cos, sin, store=keep) -> torch.Tensor:
     """model.py:184-185: pre-norm residual, twice."""
     p = f"model.layers.{i}"
-    h = plain_rmsnorm(x, w[f"{p}.input_layernorm.weight"], c["eps"])
-    x = x + plain_attention(h, w, f"{p}.self_attn", c, cos, sin, c["window"][i])
-    h = plain_rmsnorm(x, w[f"{p}.post_attention_layernorm.weight"], c["eps"])
-    return x + plain_mlp(h, w, f"{p}.mlp")
+    h = plain_rmsnorm(x, w[f"{p}.input_layernorm.weight"], c["eps"], store)
+    x = x + plain_attention(h, w, f"{p}.self_attn", c, cos, sin, c["window"][i], store)
+    h = plain_rmsnorm(x, w[f"{p}.post_attention_layernorm.weight"], c["eps"], store)
+    return x + plain_mlp(h, w, f"{p}.mlp", store)
 
 
-def plain_forward(cfg: dict, w: dict, token_ids, layer_order=None) -> torch.Tensor:
+def plain_forward(cfg: dict, w: dict, token_ids, layer_order=None, store=keep) -> torch.Tensor:
     """model.py:222-237 for one sequence: logits [T, vocab] in 32-bit for every position.
 
     ``layer_order`` (not in the reference) runs the layers in another order than 0..L-1.
@@ -143,8 +160,8 @@ def plain_forward(cfg: dict, w: dict, token_ids, layer_order=None) -> torch.Tens
     x = w["model.embed_tokens.weight"][ids]  # model.py:229
     cos, sin = plain_rope_tables(torch.arange(len(ids)), c["head_dim"], c["theta"], x.dtype)  # model.py:228-230
     for i in (range(c["layers"]) if layer_order is None else layer_order):  # model.py:231-232
-        x = plain_block(x, w, i, c, cos, sin)
-    x = plain_rmsnorm(x, w["model.norm.weight"], c["eps"])  # model.py:237
+        x = plain_block(x, w, i, c, cos, sin, store)
+    x = plain_rmsnorm(x, w["model.norm.weight"], c["eps"], store)  # model.py:237
     head = w["model.embed_tokens.weight"] if c["tied"] else w["lm_head.weight"]  # model.py:204-206
     return (x @ head.T).float()
 

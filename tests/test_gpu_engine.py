@@ -10,7 +10,7 @@ import pytest
 import torch
 
 from helpers import cut, make_model_folder, random_prompt
-from plain_qwen2 import plain_forward, plain_generate, plain_load
+from plain_qwen2 import bf16_store, plain_forward, plain_generate, plain_load
 from tiny_configs import CONFIGS, PAGE_SIZES
 
 pytestmark = pytest.mark.gpu
@@ -20,9 +20,22 @@ MODES = [("float32", "float32"), ("bfloat16", "bfloat16")]
 LENS = {"a": 150, "b": 97, "c": 64, "d": 41, "e": 130}
 
 
-def tolerance(dtype: str, ref: torch.Tensor) -> float:
-    """float32: rounding of a different summation order. bfloat16: 8 bits of mantissa on every stored activation."""
-    return (2e-5 if dtype == "float32" else 3e-2) * max(1.0, ref.abs().max().item())
+NOISE = {}   # per configuration: how far bfloat16 storage alone moves the plain model's logits (largest over the test prompts)
+
+
+def storage_noise(cfg, w, prompts, exact) -> float:
+    """max |plain model that rounds to bfloat16 wherever the engine stores an activation - exact plain model|."""
+    return max((plain_forward(cfg, w, p, store=bf16_store) - exact[k]).abs().max().item() for k, p in prompts.items())
+
+
+def tolerance(dtype: str, ref: torch.Tensor, name: str) -> float:
+    """float32: 1e-5 of the logits' scale; only the order of summation differs from the plain model (measured: 2e-7 to
+    5e-7 at the tiny sizes, 3e-6 at widths of 896 and 1536). bfloat16: twice what bfloat16 storage alone does to the
+    plain model's logits of this configuration (the engine was measured at 0.9 to 1.4 times that; a flat bound would
+    have to be ten times looser for the tiny models than what their rounding explains)."""
+    if dtype == "float32":
+        return 1e-5 * max(1.0, ref.abs().max().item())
+    return 2.0 * NOISE[name]
 
 
 @pytest.fixture(scope="module")
@@ -36,23 +49,25 @@ def models(tmp_path_factory):
             cfg, w = plain_load(folder)  # bfloat16 files are widened exactly: both sides hold the same numbers
             prompts = {k: random_prompt(cfg["vocab_size"], n, 7 + i) for i, (k, n) in enumerate(LENS.items())}
             want = {k: plain_forward(cfg, w, p) for k, p in prompts.items()}
+            if dtype == "bfloat16":
+                NOISE[name] = storage_noise(cfg, w, prompts, want)
             out[(name, dtype)] = (folder, cfg, w, prompts, want)
     return out
 
 
-def replayer(folder, name, dtype, max_tokens):
+def replayer(folder, name, dtype, max_tokens, cuda_graphs=False):
     from llm_infrence_engine_b200.engine import TraceReplayer
 
-    return TraceReplayer(str(folder), dtype, max_tokens, block_size=PAGE_SIZES[name])
+    return TraceReplayer(str(folder), dtype, max_tokens, block_size=PAGE_SIZES[name], cuda_graphs=cuda_graphs)
 
 
-def check(got, want, dtype, what):
+def check(got, want, dtype, what, name):
     err = (got - want).abs().max().item()
-    assert err <= tolerance(dtype, want), f"{what}: max |dlogits| {err:.3g} > {tolerance(dtype, want):.3g}"
+    assert err <= tolerance(dtype, want, name), f"{what}: max |dlogits| {err:.3g} > {tolerance(dtype, want, name):.3g}"
 
 
-def first_bad(got, want, dtype):
-    bad = ((got - want).abs().max(-1).values > tolerance(dtype, want)).nonzero().flatten()
+def first_bad(got, want, dtype, name):
+    bad = ((got - want).abs().max(-1).values > tolerance(dtype, want, name)).nonzero().flatten()
     return int(bad[0]) if len(bad) else None
 
 
@@ -63,7 +78,7 @@ def test_whole(models, name, dtype):
     rp = replayer(folder, name, dtype, 192)
     for i, (k, p) in enumerate(prompts.items()):
         got = rp.step({"step": i, "entries": [{"id": k, "tokens": p, "want": list(range(len(p)))}], "end": [k]})
-        assert first_bad(got, want[k], dtype) is None, f"{k}: first wrong position {first_bad(got, want[k], dtype)}"
+        assert first_bad(got, want[k], dtype, name) is None, f"{k}: first wrong position {first_bad(got, want[k], dtype, name)}"
         rp.cache.check_invariants()
 
 
@@ -79,7 +94,7 @@ def test_last_32_one_by_one(models, name, dtype):
         for i in range(head, n):
             got.append(rp.step({"step": i, "entries": [{"id": k, "tokens": [p[i]], "want": [0]}], "end": [k] if i == n - 1 else []}))
         got = torch.cat(got)
-        assert first_bad(got, want[k], dtype) is None, f"{k}: first wrong position {first_bad(got, want[k], dtype)} (decoding starts at {head})"
+        assert first_bad(got, want[k], dtype, name) is None, f"{k}: first wrong position {first_bad(got, want[k], dtype, name)} (decoding starts at {head})"
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -96,7 +111,7 @@ def test_portions_of_changing_size(models, name, dtype):
                 got.append(rp.step({"step": i, "entries": [{"id": k, "tokens": p[lo:hi], "want": list(range(hi - lo))}],
                                     "end": [k] if hi == len(p) else []}))
             got = torch.cat(got)
-            bad = first_bad(got, want[k], dtype)
+            bad = first_bad(got, want[k], dtype, name)
             assert bad is None, f"{k} cut {sizes}: first wrong position {bad}; portions {parts}"
 
 
@@ -151,9 +166,59 @@ def test_mixed_on_few_pages(models, name, dtype):
     rp = replayer(folder, name, dtype, 448 + 128)
     got = run_mixed(rp, prompts)
     for k in prompts:
-        bad = first_bad(got[k], want[k], dtype)
+        bad = first_bad(got[k], want[k], dtype, name)
         assert bad is None, f"request {k}: first wrong position {bad}"
     assert all(p.num_free == p.capacity for p in rp.cache.pools)
+
+
+@pytest.mark.parametrize("slice_keys", [32, 1024])
+@pytest.mark.parametrize("graphs", [False, True])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+def test_float32_is_bit_identical_however_the_work_is_cut(models, monkeypatch, name, graphs, slice_keys):
+    """In 32-bit every logit has the same bits whether its request ran whole, with its last 32 tokens one by one, in
+    portions of changing size, or mixed with other requests on pages that were used before; launched kernel by kernel or
+    replayed from graphs (whose launch shapes are planned for the longest request the pool allows). What makes this so:
+    the products and the norm treat every row by itself in one fixed order, and the attention cuts a request's keys at
+    fixed places (here every 32 keys, so that several slices are in play, and at the default)."""
+    from llm_infrence_engine_b200.csrc import get_kernels
+
+    monkeypatch.setattr(get_kernels(), "slice_keys", slice_keys)
+    folder, cfg, w, prompts, want = models[(name, "float32")]
+
+    def fresh(max_tokens):
+        rp = replayer(folder, name, "float32", max_tokens, cuda_graphs=graphs)
+        if graphs:
+            rp.runner.graphs.capture_after = 2
+        return rp
+
+    rp = fresh(192)
+    whole = {k: rp.step({"step": i, "entries": [{"id": k, "tokens": p, "want": list(range(len(p)))}], "end": [k]})
+             for i, (k, p) in enumerate(prompts.items())}
+    for k in prompts:
+        assert first_bad(whole[k], want[k], "float32", name) is None
+    rp = fresh(192)
+    for k, p in prompts.items():
+        n = len(p)
+        got = [rp.step({"step": 0, "entries": [{"id": k, "tokens": p[:n - 32], "want": list(range(n - 32))}], "end": []})]
+        for i in range(n - 32, n):
+            got.append(rp.step({"step": i, "entries": [{"id": k, "tokens": [p[i]], "want": [0]}], "end": [k] if i == n - 1 else []}))
+        got = torch.cat(got)
+        diff = (got != whole[k]).any(-1).nonzero().flatten()
+        assert len(diff) == 0, f"{k}: last 32 one by one differ from whole first at position {int(diff[0])}"
+    if graphs:
+        assert rp.runner.graphs.replays > 0
+    rp = fresh(192)
+    for sizes in ([16, 5, 2, 9], [2, 2, 33, 3, 64]):
+        for k in ("a", "e"):
+            p = prompts[k]
+            got = torch.cat([rp.step({"step": i, "entries": [{"id": k, "tokens": p[lo:hi], "want": list(range(hi - lo))}],
+                                      "end": [k] if hi == len(p) else []}) for i, (lo, hi) in enumerate(cut(len(p), sizes))])
+            diff = (got != whole[k]).any(-1).nonzero().flatten()
+            assert len(diff) == 0, f"{k} cut {sizes}: differs from whole first at position {int(diff[0])}"
+    got = run_mixed(fresh(448 + 128), prompts)
+    for k in prompts:
+        diff = (got[k] != whole[k]).any(-1).nonzero().flatten()
+        assert len(diff) == 0, f"mixed, request {k}: differs from whole first at position {int(diff[0])}"
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -163,9 +228,9 @@ def test_long_decoding_and_first_tokens(models, dtype):
     p = prompts["a"]
     got = [rp.step({"step": i, "entries": [{"id": "x", "tokens": [t], "want": [0]}], "end": []}) for i, t in enumerate(p)]
     got = torch.cat(got)
-    bad = first_bad(got, want["a"], dtype)
+    bad = first_bad(got, want["a"], dtype, "B")
     assert bad is None, f"decoding from the first token on: first wrong position {bad}"
-    check(got[:3], want["a"][:3], dtype, "the first three tokens")
+    check(got[:3], want["a"][:3], dtype, "the first three tokens", "B")
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -187,7 +252,7 @@ def test_greedy_generation_through_entry_point(models, name, dtype):
         total += 16
     # bfloat16 may leave the plain sequence at a near tie; most tokens before that agree (the reference reports 95.8 %)
     assert agree >= 0.6 * total, f"only {agree} of {total} greedy tokens agree"
-    assert eng.preemptions >= 0 and all(pool.num_free == pool.capacity for pool in eng.cache.pools)
+    assert all(pool.num_free == pool.capacity for pool in eng.cache.pools)
 
 
 def test_warmup_captures_the_decode_graphs_up_front(models):
@@ -244,8 +309,8 @@ def test_trace_run_program(models, tmp_path):
     s0 = torch.from_numpy(np.fromfile(out / "0.f32", dtype="<f4").reshape(-1, v))
     s2 = torch.from_numpy(np.fromfile(out / "2.f32", dtype="<f4").reshape(-1, v))
     assert not (out / "1.f32").exists()
-    check(s0, want["c"][[0, 29]], "float32", "step 0")
-    check(s2, torch.stack([want["c"][len(p) - 1], want["c"][4]]), "float32", "step 2")
+    check(s0, want["c"][[0, 29]], "float32", "step 0", "A")
+    check(s2, torch.stack([want["c"][len(p) - 1], want["c"][4]]), "float32", "step 2", "A")
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -279,7 +344,7 @@ def test_decode_from_cuda_graphs_matches_eager(models, dtype):
             assert runner.graphs.replays == 27 + 4 and sorted(runner.graphs.captured) == [2, 4]
     assert torch.equal(out[True], out[False])
     ref = torch.stack([want[k][i] for i in range(33, 60) for k in ("a", "b", "c")] + [want[k][i] for i in range(60, 64) for k in ("a", "c")])
-    check(out[True], ref, dtype, "graph decode vs plain")
+    check(out[True], ref, dtype, "graph decode vs plain", "A")
 
 
 HALF_B = dict(CONFIGS["A"], vocab_size=151936, hidden_size=896, intermediate_size=4864, num_hidden_layers=2, num_attention_heads=14,
@@ -301,14 +366,15 @@ def test_head_size_128(tmp_path, dtype):
     cfg, w = plain_load(folder)
     p = random_prompt(32003, 140, 3)
     want = plain_forward(cfg, w, p)
+    NOISE["wide"] = storage_noise(cfg, w, {"p": p}, {"p": want})
     rp = TraceReplayer(str(folder), dtype, 192)
     got = rp.step({"step": 0, "entries": [{"id": "a", "tokens": p, "want": list(range(140))}], "end": ["a"]})
-    assert first_bad(got, want, dtype) is None, f"whole: first wrong position {first_bad(got, want, dtype)}"
+    assert first_bad(got, want, dtype, "wide") is None, f"whole: first wrong position {first_bad(got, want, dtype, 'wide')}"
     outs = [rp.step({"step": 0, "entries": [{"id": "b", "tokens": p[:100], "want": list(range(100))}], "end": []})]
     for i in range(100, 140):
         outs.append(rp.step({"step": i, "entries": [{"id": "b", "tokens": [p[i]], "want": [0]}], "end": ["b"] if i == 139 else []}))
     got = torch.cat(outs)
-    assert first_bad(got, want, dtype) is None, f"decoded: first wrong position {first_bad(got, want, dtype)}"
+    assert first_bad(got, want, dtype, "wide") is None, f"decoded: first wrong position {first_bad(got, want, dtype, 'wide')}"
     rp.runner.K.check_device_errors()
 
 
@@ -324,6 +390,7 @@ def test_layer_sizes_of_the_half_billion_model(tmp_path, dtype):
     cfg, w = plain_load(folder)
     pa, pb = random_prompt(151936, 150, 1), random_prompt(151936, 70, 2)
     want_a, want_b = plain_forward(cfg, w, pa), plain_forward(cfg, w, pb)
+    NOISE["half_b"] = storage_noise(cfg, w, {"a": pa, "b": pb}, {"a": want_a, "b": want_b})
     from llm_infrence_engine_b200.engine import TraceReplayer
 
     rp = TraceReplayer(str(folder), dtype, 320)
@@ -331,7 +398,7 @@ def test_layer_sizes_of_the_half_billion_model(tmp_path, dtype):
         b.k.fill_(float("nan"))
         b.v.fill_(float("nan"))
     got = rp.step({"step": 0, "entries": [{"id": "a", "tokens": pa, "want": list(range(150))}], "end": ["a"]})
-    assert first_bad(got, want_a, dtype) is None, f"whole: first wrong position {first_bad(got, want_a, dtype)}"
+    assert first_bad(got, want_a, dtype, "half_b") is None, f"whole: first wrong position {first_bad(got, want_a, dtype, 'half_b')}"
     # a in portions (one of two tokens) while b decodes token by token beside it, then a decodes too
     outs = {"a": [], "b": []}
     cuts_a = [(0, 64), (64, 66), (66, 130)] + [(i, i + 1) for i in range(130, 150)]
@@ -349,7 +416,7 @@ def test_layer_sizes_of_the_half_billion_model(tmp_path, dtype):
             o += len(e["tokens"])
     for k, want in (("a", want_a), ("b", want_b)):
         got = torch.cat(outs[k])
-        assert first_bad(got, want, dtype) is None, f"{k}: first wrong position {first_bad(got, want, dtype)}"
+        assert first_bad(got, want, dtype, "half_b") is None, f"{k}: first wrong position {first_bad(got, want, dtype, 'half_b')}"
     rp.runner.K.check_device_errors()
     # the same decoding through captured graphs
     ec = EngineConfig(dtype=dtype, block_size=16, num_blocks=40, max_seqs=4, max_len=160, max_num_batched_tokens=256, cuda_graphs=True)
@@ -365,19 +432,19 @@ def test_layer_sizes_of_the_half_billion_model(tmp_path, dtype):
         out = runner.step([StepEntry("a", [pa[i]], i, (0,)), StepEntry("b", [pb[i]], i, (0,))]).float().cpu()
         got_a.append(out[0]); got_b.append(out[1])
     assert runner.graphs.replays == 30
-    check(torch.stack(got_a), want_a[40:70], dtype, "graphs, request a")
-    check(torch.stack(got_b), want_b[40:70], dtype, "graphs, request b")
+    check(torch.stack(got_a), want_a[40:70], dtype, "graphs, request a", "half_b")
+    check(torch.stack(got_b), want_b[40:70], dtype, "graphs, request b", "half_b")
     runner.K.check_device_errors()
 
 
-def _sharp_folder(tmp_path, name, factor=8.0):
+def _sharp_folder(tmp_path, name, factor=8.0, store="float32", config=None):
     """Tiny model whose query and key projections are scaled up: the softmax becomes nearly one-hot, so a key that is
     skipped, misplaced, read from a wrong page or let in across a window's edge changes the logits by far more than rounding.
     The factor is 8 (scores x 64): at 25 the plain implementation itself moves by 7e-5 when its weights are disturbed by
     one part in 10^7, which is beyond the comparison's 2e-5; at 8 it moves by 1e-6."""
     from llm_infrence_engine_b200.weights import SafetensorsFile, write_random_model, write_safetensors
 
-    folder = write_random_model(CONFIGS[name], tmp_path / f"sharp_{name}", 11, "float32")
+    folder = write_random_model(config or CONFIGS[name], tmp_path / f"sharp_{name}", 11, store)
     f = SafetensorsFile(folder / "model.safetensors")
     t = {n: f.tensor(n) for n in f.names()}
     f.close()
@@ -399,12 +466,49 @@ def test_sharp_attention_shows_a_wrong_key(tmp_path, name):
     assert (want - plain_forward(cfg, {k: (v / 8.0 if k.endswith(("q_proj.weight", "k_proj.weight")) else v) for k, v in base.items()}, p)).abs().max() > 1e-2
     rp = replayer(folder, name, "float32", 192)
     got = rp.step({"step": 0, "entries": [{"id": "w", "tokens": p, "want": list(range(150))}], "end": ["w"]})
-    assert first_bad(got, want, "float32") is None, f"whole: first wrong position {first_bad(got, want, 'float32')}"
+    assert first_bad(got, want, "float32", name) is None, f"whole: first wrong position {first_bad(got, want, 'float32', name)}"
     outs = []
     for i, (lo, hi) in enumerate(cut(150, [7, 16, 1, 33, 2, 15, 1, 1, 17])):
         outs.append(rp.step({"step": i, "entries": [{"id": "c", "tokens": p[lo:hi], "want": list(range(hi - lo))}], "end": ["c"] if hi == 150 else []}))
     got = torch.cat(outs)
-    assert first_bad(got, want, "float32") is None, f"portions: first wrong position {first_bad(got, want, 'float32')}"
+    assert first_bad(got, want, "float32", name) is None, f"portions: first wrong position {first_bad(got, want, 'float32', name)}"
+
+
+@pytest.mark.parametrize("which", ["D", "half_b"])
+def test_sharp_attention_in_bfloat16(tmp_path, which):
+    """The same in bfloat16, where the tensor-core kernels run (heads of 64): the tcgen05 attention and the fused q/k/v
+    kernel for prompt portions, the small-batch products and the decode attention with its key slices, eagerly (two slices
+    merged as a cluster once the context passes 1,024) and from graphs planned for 8,192 tokens (sixteen slices merged
+    through scratch memory). The bound is twice what bfloat16 storage does to the plain model with these sharp weights;
+    the unscaled model is many bounds away, so a key that is lost or misplaced cannot hide."""
+    from llm_infrence_engine_b200.engine import TraceReplayer
+
+    n = 1200 if which == "D" else 150
+    folder = _sharp_folder(tmp_path, which, 4.0, "bfloat16", None if which == "D" else HALF_B)
+    cfg, w = plain_load(folder)
+    p = random_prompt(cfg["vocab_size"], n, 23)
+    want = plain_forward(cfg, w, p)
+    key = f"sharp_{which}"
+    NOISE[key] = storage_noise(cfg, w, {"p": p}, {"p": want})
+    blunt = plain_forward(cfg, {k: (v / 4.0 if k.endswith(("q_proj.weight", "k_proj.weight")) else v) for k, v in w.items()}, p)
+    assert (want - blunt).abs().max() > 10 * tolerance("bfloat16", want, key)
+    for graphs in (False, True):
+        rp = TraceReplayer(str(folder), "bfloat16", 8192 if graphs else 1280, cuda_graphs=graphs)
+        if not graphs:
+            got = rp.step({"step": 0, "entries": [{"id": "w", "tokens": p, "want": list(range(n))}], "end": ["w"]})
+            bad = first_bad(got, want, "bfloat16", key)
+            assert bad is None, f"whole: first wrong position {bad}"
+        outs = []
+        head = n - 40
+        for i, (lo, hi) in enumerate(cut(head, [300, 128, 2, 513, 17] if which == "D" else [64, 2, 33])):
+            outs.append(rp.step({"step": i, "entries": [{"id": "c", "tokens": p[lo:hi], "want": list(range(hi - lo))}], "end": []}))
+        for i in range(head, n):
+            outs.append(rp.step({"step": i, "entries": [{"id": "c", "tokens": [p[i]], "want": [0]}], "end": ["c"] if i == n - 1 else []}))
+        bad = first_bad(torch.cat(outs), want, "bfloat16", key)
+        assert bad is None, f"graphs {graphs}: portions, then decoding from {head}: first wrong position {bad}"
+        if graphs:
+            assert rp.runner.graphs.replays == 40 and rp.runner.K.last_attention_plan[0] > 8
+        rp.runner.K.check_device_errors()
 
 
 @pytest.mark.parametrize("seed", [0, 1, 2])
@@ -447,7 +551,7 @@ def test_random_traces(models, dtype, seed):
         rp.cache.check_invariants()
         step += 1
     for k in keys:
-        bad = first_bad(torch.cat(got[k]), want[k], dtype)
+        bad = first_bad(torch.cat(got[k]), want[k], dtype, name)
         assert bad is None, f"seed {seed}, request {k}: first wrong position {bad}"
     assert all(p.num_free == p.capacity for p in rp.cache.pools)
 
@@ -465,7 +569,7 @@ def test_nothing_reads_what_was_never_written(models, name, dtype):
     got = run_mixed(rp, prompts)
     for k in prompts:
         assert not torch.isnan(got[k]).any(), f"request {k}: NaN at position {int(torch.isnan(got[k]).any(-1).nonzero()[0])}"
-        assert first_bad(got[k], want[k], dtype) is None
+        assert first_bad(got[k], want[k], dtype, name) is None
 
 
 def test_stop_tokens_and_ignore_eos(models):
@@ -516,9 +620,9 @@ def test_recurring_step_shapes_from_cuda_graphs(models, dtype):
         assert runner.step([portion("b", 5, False)]) is None
     out = runner.step([portion("b", 18, True)]).float().cpu()   # seen once only: eager
     assert runner.graphs.shape_replays == 4 + 3 + 2 and len(runner.graphs.shapes) == 3
-    check(torch.cat(got["a"]), want["a"][:112], dtype, "request a")
-    check(torch.cat(got["b"]), want["b"][:64], dtype, "request b, first 64")
-    check(out, want["b"][79:97], dtype, "request b after the unwanted portions")
+    check(torch.cat(got["a"]), want["a"][:112], dtype, "request a", "C")
+    check(torch.cat(got["b"]), want["b"][:64], dtype, "request b, first 64", "C")
+    check(out, want["b"][79:97], dtype, "request b after the unwanted portions", "C")
 
 
 @pytest.mark.parametrize("graphs", [False, True])
@@ -581,3 +685,156 @@ def test_prefix_cache_on_the_gpu(models, dtype, graphs, pipeline):
     else:
         same = sum(a == b for x, y in zip(out[True][0], out[False][0]) for a, b in zip(x, y))
         assert same >= 0.8 * 12 * len(ps)  # bfloat16: a taken-over page was computed in another batch; near ties may flip
+
+
+def test_engine_raises_when_a_kernel_reported_an_error(models):
+    """A kernel that gives up on a bounded wait sets a word on the device; the engine reads that word together with every
+    step's tokens and raises instead of handing out tokens made from invalid output. (The word is set from the host here:
+    nothing on the device is made to fail.)"""
+    from llm_infrence_engine_b200.csrc.kernels import KernelError
+    from llm_infrence_engine_b200.engine import Engine
+
+    folder, cfg, w, prompts, want = models[("D", "bfloat16")]
+    for pipeline, graphs in ((False, False), (True, True)):
+        eng = Engine(str(folder), dtype="bfloat16", block_size=16, num_blocks=20, max_seqs=2, max_len=64, cuda_graphs=graphs, pipeline=pipeline)
+        K = eng.runner.K
+        assert len(eng.generate(prompts["d"][:9], max_new_tokens=3).token_ids) == 3
+        K.error_flag("cuda:0").fill_(12)
+        with pytest.raises(KernelError, match="code 12"):
+            eng.generate(prompts["d"][:9], max_new_tokens=3)
+        assert int(K.error_flag("cuda:0").item()) == 0   # reported once, then cleared
+
+
+def test_graphs_survive_a_growing_accumulation_buffer(models):
+    """Captured decode graphs hold the address of the buffer that split-K products add into. When a later, larger product
+    makes the kernels object take a larger buffer, the old one must stay alive and zero for the graphs that still use it."""
+    from llm_infrence_engine_b200.config import EngineConfig
+    from llm_infrence_engine_b200.engine import StepEntry, build_runner
+
+    folder, cfg, w, prompts, want = models[("D", "bfloat16")]
+    ec = EngineConfig(dtype="bfloat16", block_size=16, num_blocks=40, max_seqs=4, max_len=160, max_num_batched_tokens=256, cuda_graphs=True)
+    spec, cache, runner = build_runner(folder, ec)
+    K = runner.K
+    keys = ["a", "b"]
+    for k in keys:
+        cache.admit(k)
+        cache.reserve(k, 0, 40)
+    runner.step([StepEntry(k, prompts[k][:40], 0, ()) for k in keys])
+    got = []
+
+    def decode(i):
+        for k in keys:
+            cache.reserve(k, i, i + 1)
+        got.append(runner.step([StepEntry(k, [prompts[k][i]], i, (0,)) for k in keys]).float().cpu())
+
+    for i in range(40, 44):
+        decode(i)
+    old = K._acc
+    x = torch.randn(120, 96, device="cuda").to(torch.bfloat16)
+    wide = torch.randn(old.numel() // 120 + 128, 96, device="cuda").to(torch.bfloat16)
+    y = K.linear(x, wide, transient=True)          # a product too large for the buffer: a new one is taken
+    assert K._acc is not old and any(t is old for t in K._retired_acc) and K._is_transient(y)
+    K._acc.zero_()                                 # nothing consumed it here: leave it as every product expects it
+    junk = [torch.full((old.numel(),), 7.0, device="cuda") for _ in range(4)]   # would land in the old buffer's place had it been freed
+    for i in range(44, 60):
+        decode(i)
+    assert runner.graphs.replays == 20 and old.abs().sum().item() == 0
+    ref = torch.stack([want[k][i] for i in range(40, 60) for k in keys])
+    check(torch.cat(got), ref, "bfloat16", "graph decode around a grown accumulation buffer", "D")
+    del junk
+
+
+@pytest.mark.parametrize("prefix", [False, True])
+def test_preemption_in_bfloat16(models, prefix):
+    """A pool so small that requests are preempted and recomputed, in bfloat16 through graphs and the pipelined engine,
+    with and without the prefix cache: every request still gets its tokens (those of a run with a large pool, up to near
+    ties that recomputation in another batch may flip), and every page and slot comes back."""
+    from llm_infrence_engine_b200.engine import Engine, Request
+
+    folder, cfg, w, prompts, want = models[("D", "bfloat16")]
+    vocab = cfg["vocab_size"]
+    stem = random_prompt(vocab, 20, 5)
+    ps = [stem + random_prompt(vocab, n, 80 + n) for n in (1, 7, 3, 5, 2, 9)]
+
+    def run(num_blocks):
+        eng = Engine(str(folder), dtype="bfloat16", block_size=16, num_blocks=num_blocks, max_seqs=4, max_len=96,
+                     max_num_batched_tokens=48, cuda_graphs=True, pipeline=True, prefix_cache=prefix)
+        reqs = [eng.add_request(Request(p, max_new_tokens=40)) for p in ps]
+        steps = 0
+        while eng.has_work():
+            eng.step()
+            eng.cache.check_invariants()
+            steps += 1
+            assert steps < 3000
+        assert all(pool.num_free == pool.capacity for pool in eng.cache.pools) and eng.cache.num_free_slots() == 4
+        assert all(len(r.output_ids) == 40 and r.finish_reason == "length" for r in reqs)
+        return [r.output_ids for r in reqs], eng.preemptions
+
+    roomy, none = run(40)
+    tight, some = run(11)
+    assert none == 0 and some > 0
+    same = sum(next((i for i, (a, b) in enumerate(zip(x, y)) if a != b), 40) for x, y in zip(roomy, tight))
+    assert same >= 0.7 * 40 * len(ps), f"only {same} of {40 * len(ps)} tokens agree before the first difference"
+    assert [x[0] for x in roomy] == [x[0] for x in tight]
+
+
+@pytest.mark.parametrize("graphs", [False, True])
+def test_more_decode_rows_than_the_small_batch_kernels_take(models, graphs):
+    """140 requests decode together in bfloat16: more rows than the small-batch tensor-core product accepts (128), so the
+    products of a decode step go to the library and q/k/v takes the kernel of prompt portions with one token per request."""
+    from llm_infrence_engine_b200.engine import Engine, Request
+
+    folder, cfg, w, prompts, want = models[("D", "bfloat16")]
+    vocab = cfg["vocab_size"]
+    ps = [random_prompt(vocab, 3 + i % 9, 300 + i) for i in range(140)]
+    eng = Engine(str(folder), dtype="bfloat16", block_size=16, num_blocks=160 * 2 + 1, max_seqs=160, max_len=32,
+                 max_num_batched_tokens=2048, cuda_graphs=graphs, pipeline=graphs)
+    reqs = [eng.add_request(Request(p, max_new_tokens=6)) for p in ps]
+    eng.run_until_idle()
+    assert max(rec.decode_batch for rec in eng.steps) > 128
+    agree = 0
+    for r, p in zip(reqs, ps):
+        ref = plain_generate(cfg, w, p, 6)
+        agree += next((i for i, (a, b) in enumerate(zip(r.output_ids, ref)) if a != b), 6)
+    assert agree >= 0.85 * 6 * len(ps), f"only {agree} of {6 * len(ps)} tokens agree with the plain model"
+    assert all(pool.num_free == pool.capacity for pool in eng.cache.pools)
+    eng.runner.K.check_device_errors()
+
+
+@pytest.mark.parametrize("which", ["D", "half_b"])
+def test_decode_graphs_planned_for_a_long_context(models, tmp_path, which):
+    """A decode graph fixes its launch shapes for the longest request the engine allows. With ``max_len`` 8192 the
+    attention of a captured step is planned with many key slices (merged through scratch memory and a counter), while the
+    requests here are short: most slices are empty. Logits against the plain model, step after step, replayed twice over."""
+    from llm_infrence_engine_b200.config import EngineConfig
+    from llm_infrence_engine_b200.engine import StepEntry, build_runner
+    from llm_infrence_engine_b200.weights import write_random_model
+
+    if which == "D":
+        folder, cfg, w, prompts, want = models[("D", "bfloat16")]
+        pa, pb = prompts["a"], prompts["b"]
+        want_a, want_b = want["a"], want["b"]
+    else:
+        folder = write_random_model(HALF_B, tmp_path / "half_b", 4, "bfloat16")
+        cfg, w = plain_load(folder)
+        pa, pb = random_prompt(151936, 90, 1), random_prompt(151936, 90, 2)
+        want_a, want_b = plain_forward(cfg, w, pa), plain_forward(cfg, w, pb)
+        NOISE["half_b"] = storage_noise(cfg, w, {"a": pa, "b": pb}, {"a": want_a, "b": want_b})
+    ec = EngineConfig(dtype="bfloat16", block_size=16, num_blocks=40, max_seqs=4, max_len=8192, max_num_batched_tokens=256, cuda_graphs=True)
+    spec, cache, runner = build_runner(folder, ec)
+    for k in ("a", "b"):
+        cache.admit(k)
+        cache.reserve(k, 0, 40)
+    runner.step([StepEntry("a", pa[:40], 0, ()), StepEntry("b", pb[:40], 0, ())])
+    got_a, got_b = [], []
+    for i in range(40, 90):
+        for k in ("a", "b"):
+            cache.reserve(k, i, i + 1)
+        out = runner.step([StepEntry("a", [pa[i]], i, (0,)), StepEntry("b", [pb[i]], i, (0,))]).float().cpu()
+        got_a.append(out[0]); got_b.append(out[1])
+    assert runner.graphs.replays == 50
+    slices, as_cluster = runner.K.last_attention_plan    # of the captured step: nothing was launched from the host since
+    assert slices > 8 and not as_cluster
+    check(torch.stack(got_a), want_a[40:90], "bfloat16", "request a", which)
+    check(torch.stack(got_b), want_b[40:90], "bfloat16", "request b", which)
+    runner.K.check_device_errors()

@@ -318,6 +318,37 @@ def test_paged_attention_tensor_cores(K, nq, nkv, d, ps, lens, qlens, window, sp
         close(got, want, 1e-2)
 
 
+@pytest.mark.parametrize("cluster", [True, False])
+@pytest.mark.parametrize("nq,nkv,d,ps,lens,splits", [
+    (14, 2, 64, 16, [8192] * 8, None),            # the headline decode step: the planner's own choice (9 slices on 148 SMs)
+    (14, 2, 64, 16, [8192] * 7 + [40], 9),        # one request far shorter than the others: its later slices are empty
+    (14, 2, 64, 16, [5000, 3000, 17], 13),        # more slices than the merge loads in one group of 12
+    (14, 2, 64, 16, [8200, 100], 33),
+    (14, 2, 64, 16, [8200, 1], 64),               # the most slices the kernel takes; a request of one token
+    (14, 2, 64, 16, [8192] * 8, 4),               # few enough to merge as a cluster when that is on
+    (12, 2, 128, 16, [8192] * 4, None),           # head size 128: chunks of 16 keys, more slices
+    (12, 2, 128, 16, [4100, 900], 13),
+    (28, 4, 128, 32, [6000, 64], 8),
+    (16, 1, 64, 64, [3000, 3000, 2000], 25),      # 16 heads on one key/value head, pages of 64
+])
+def test_decode_attention_with_many_key_slices(K, monkeypatch, cluster, nq, nkv, d, ps, lens, splits):
+    """Decoded tokens at long contexts: the keys of a token are cut into slices that run as blocks of their own and are
+    merged either as a thread-block cluster through shared memory (few slices) or through scratch memory, a counter and
+    the last block to finish (many slices; what serving at a long context runs). Twice in a row: the counters must be
+    back at zero. With a far key that must not be lost."""
+    monkeypatch.setattr(K, "cluster_merge", cluster)
+    qlens = [1] * len(lens)
+    for spike in (False, True):
+        qkv, kp, vp, table, tseq, pos = _attention_case(torch.bfloat16, nq, nkv, d, ps, lens, qlens, 0, 17, spike)
+        scale = 1.0 / math.sqrt(d)
+        want = REF.paged_attention(qkv, kp, vp, table, tseq, pos, nq, nkv, d, ps, scale, 0, max(lens))
+        dev = [t.cuda() for t in (qkv, kp, vp, table, tseq, pos)]
+        for _ in range(2):
+            got = K.paged_attention(*dev, nq, nkv, d, ps, scale, 0, max(lens), batch=_Batch(qlens), num_splits=splits)
+            close(got, want, 1e-2)
+    assert K._attn_counters is None or K._attn_counters.abs().sum().item() == 0
+
+
 @pytest.mark.parametrize("nq,nkv,ps,lens,qlens,window", [
     (14, 2, 16, [2048], [2048], 0),                       # the bench's prompt: 18 tokens x 7 heads per tile
     (14, 2, 16, [3000], [40], 0),                         # a short portion far into a long request: few tiles, their keys in slices
