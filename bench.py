@@ -295,14 +295,31 @@ def reference_arm(a) -> int:
 
 
 def check_decode_step(runner, entries, graph_logits, graph_tokens, torch) -> dict:
-    """Outside the timed region: is what the captured step computes right? The same entries are run again (a) eagerly,
-    kernel by kernel, with the same kernels: logits must agree up to the order of the split-K additions; and (b) eagerly with
-    the attention done by the generic kernel (another kernel altogether: one thread per key, 32-bit arithmetic, slices at
-    fixed places) instead of the tensor-core kernel with its slices and merges: logits must agree within bfloat16 rounding.
-    The tokens of the graph must be the argmax of (a) wherever the two best logits are further apart than the difference."""
+    """Outside the timed region: is what the captured step computes right?
+
+    (a) The attention of this very shape (these block tables, contexts and pools, the planner's own number of key slices
+    and way of merging them) against another kernel altogether: the generic one (one thread per key, 32-bit arithmetic,
+    slices at fixed places), on random queries. Bound: 1e-2 of the largest output, the bound of the kernels' own tests.
+    (b) The whole step again eagerly, kernel by kernel, and with the generic attention. The logits of two runs of the
+    same bfloat16 step are not bit-equal: split-K partial sums meet by atomic additions in whatever order they arrive, the
+    last bits of a sum decide how some activations round to bfloat16, and a deep model with random weights carries such
+    a flip through to the logits (two replays of one graph were measured 1e-2 of the logits' scale apart at 24 layers, 1e-3
+    at 2, and exactly equal with split-K off). So (b) is a coarse bound, 4e-2 of the scale, and the graph's tokens must be
+    the eager argmax wherever the two best logits are clearly apart."""
     K = runner.K
     ctx, rows = runner.make_context(entries)
     eager = runner.forward(ctx, rows).float()
+    slices = int(K.last_attention_plan[0])
+    mixer = runner.spec.layers[runner.spec.schedule[0].layer].mixer
+    bind = runner.bindings[runner.spec.schedule[0].cache]
+    g = torch.Generator(device="cuda").manual_seed(3)
+    width = (mixer.num_heads + 2 * mixer.num_kv_heads) * mixer.head_dim
+    qkv = torch.randn((ctx.num_tokens, width), generator=g, device="cuda").to(torch.bfloat16)
+    args = (qkv, bind.k, bind.v, ctx.block_tables[bind.group], ctx.token_seq, ctx.positions, mixer.num_heads, mixer.num_kv_heads,
+            mixer.head_dim, ctx.page_size, mixer.scale, mixer.window or 0, ctx.max_context)
+    fast = K.paged_attention(*args, batch=ctx).float()
+    plain = K.paged_attention(*args).float()   # without the step's description the generic kernel runs
+    d_attn = float((fast - plain).abs().max()) / max(float(plain.abs().max()), 1e-30)
     ctx._tables.clear()
     was = K.use_mma_attention
     K.use_mma_attention = False
@@ -316,9 +333,11 @@ def check_decode_step(runner, entries, graph_logits, graph_tokens, torch) -> dic
     top2 = eager.topk(2, dim=-1).values
     clear = (top2[:, 0] - top2[:, 1]) > 4 * float((graph_logits - eager).abs().max())
     same = graph_tokens.long() == eager.argmax(-1)
-    ok = bool(d_eager <= 1e-3 and d_generic <= 2e-2 and bool((same | ~clear).all()) and torch.isfinite(graph_logits).all())
-    return {"checked": ok, "graph_vs_eager": round(d_eager, 7), "vs_generic_attention": round(d_generic, 5),
-            "tokens_equal": int(same.sum()), "rows": int(same.numel()), "attention_slices": int(K.last_attention_plan[0])}
+    ok = bool(d_attn <= 1e-2 and d_eager <= 4e-2 and d_generic <= 4e-2 and bool((same | ~clear).all())
+              and bool(torch.isfinite(graph_logits).all()))
+    return {"checked": ok, "attention_vs_generic_kernel": round(d_attn, 5), "graph_vs_eager": round(d_eager, 5),
+            "vs_generic_attention": round(d_generic, 5), "tokens_equal": int(same.sum()), "rows": int(same.numel()),
+            "attention_slices": slices}
 
 
 def decode_point(folder: Path, batch: int, steps: int, warmup: int, torch, graphs: bool = True, sampler=None) -> dict:

@@ -43,6 +43,17 @@ struct Params {
     int page_shift;         // log2(page_size), or -1 if that is no power of two
     int cluster;            // 1: the slices of a tile are one thread-block cluster and merge through distributed shared memory
     float scale_log2;       // softmax scale * log2(e)
+    // Decode steps may hand over the fused q/k/v projection as it leaves a split-K product: float32 sums that still lack the
+    // bias and the rotation (`q` is then unused). The kernel finishes the queries in its own registers, and the one warp whose
+    // keys include the token's own position finishes that key and value, puts them into its chunk and into the cache.
+    const float* qkv_acc;   // [tokens][acc_stride]: query heads, key heads, value heads; or null
+    const float* bias;      // [(nq + 2 nkv) * D] or null
+    const float* cos_t;     // [tokens][D / 2]
+    const float* sin_t;
+    const int* slots;       // [tokens] cache slot (page * page_size + offset) of the token's own key and value; null: already cached
+    bf16* k_pool_w;         // the pools again, to write into
+    bf16* v_pool_w;
+    int acc_stride;
 };
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
@@ -348,15 +359,85 @@ __global__ void __launch_bounds__(DW * 32) attn_mma_decode_kernel(const Params p
     uint32_t qa[T8 ? 1 : D / 16][4];   // the queries as A operand (rows lane / 4 and + 8), or ...
     uint32_t qb[T8 ? D / 16 : 1][2];   // ... transposed, as B operand (row lane / 4 only)
     float o[T8 ? D / 16 : D / 8][4];
+    // (from the projection's sums) the token's own key and value, finished by the warp that owns its position: pairs
+    // (j, j + D / 2) for j = lane, lane + 32, ...
+    constexpr int NP = D / 64;
+    int own_it = -1;
+    uint32_t own_k[NP], own_v[NP];   // (element j, element j + D / 2) as two bfloat16
     if constexpr (T8) {
         const int row = lane >> 2;
         const bool ok = row < nrows;
-        const bf16* qp = p.q + (size_t)n0 * p.q_stride + (size_t)(kvh * G + (ok ? row : 0)) * D;
+        if (p.qkv_acc) {
+            const int head = kvh * G + (ok ? row : 0);
+            const float* src = p.qkv_acc + (size_t)n0 * p.acc_stride + (size_t)head * D;
+            const float* ct = p.cos_t + (size_t)n0 * (D / 2);
+            const float* sn = p.sin_t + (size_t)n0 * (D / 2);
+            float x[D / 16][4];
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-            const int col = kk * 16 + ((lane & 3) << 1);
-            qb[kk][0] = ok ? *reinterpret_cast<const uint32_t*>(qp + col) : 0u;
-            qb[kk][1] = ok ? *reinterpret_cast<const uint32_t*>(qp + col + 8) : 0u;
+            for (int kk = 0; kk < D / 16; ++kk) {
+                const int col = kk * 16 + ((lane & 3) << 1);
+                const float2 a = __ldcg(reinterpret_cast<const float2*>(src + col)), c = __ldcg(reinterpret_cast<const float2*>(src + col + 8));
+                x[kk][0] = a.x; x[kk][1] = a.y; x[kk][2] = c.x; x[kk][3] = c.y;
+                if (p.bias) {
+                    const float2 ba = *reinterpret_cast<const float2*>(p.bias + (size_t)head * D + col);
+                    const float2 bc = *reinterpret_cast<const float2*>(p.bias + (size_t)head * D + col + 8);
+                    x[kk][0] += ba.x; x[kk][1] += ba.y; x[kk][2] += bc.x; x[kk][3] += bc.y;
+                }
+            }
+#pragma unroll
+            for (int kk = 0; kk < D / 32; ++kk) {   // dims of the first half and their partners D / 2 further on, both in this lane
+                const int col = kk * 16 + ((lane & 3) << 1);
+                const float2 c0 = *reinterpret_cast<const float2*>(ct + col), c1 = *reinterpret_cast<const float2*>(ct + col + 8);
+                const float2 s0 = *reinterpret_cast<const float2*>(sn + col), s1 = *reinterpret_cast<const float2*>(sn + col + 8);
+                const float cs[4] = {c0.x, c0.y, c1.x, c1.y}, ss[4] = {s0.x, s0.y, s1.x, s1.y};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float x1 = x[kk][e], x2 = x[kk + D / 32][e];
+                    x[kk][e] = x1 * cs[e] - x2 * ss[e];
+                    x[kk + D / 32][e] = x2 * cs[e] + x1 * ss[e];
+                }
+            }
+#pragma unroll
+            for (int kk = 0; kk < D / 16; ++kk) {
+                qb[kk][0] = ok ? pack_bf16(x[kk][0], x[kk][1]) : 0u;
+                qb[kk][1] = ok ? pack_bf16(x[kk][2], x[kk][3]) : 0u;
+            }
+            if (p.slots) {
+                const int c_p = (pos0 - lo) / BN;   // the chunk that holds the token's own position
+                if (c_p >= c_begin && c_p < c_end && (c_p - c_begin) % DW == warp) own_it = (c_p - first) / DW;
+            }
+            if (own_it >= 0) {
+                const float* ks_ = p.qkv_acc + (size_t)n0 * p.acc_stride + (size_t)(p.nq + kvh) * D;
+                const float* vs_ = p.qkv_acc + (size_t)n0 * p.acc_stride + (size_t)(p.nq + p.nkv + kvh) * D;
+                const float* kb = p.bias ? p.bias + (size_t)(p.nq + kvh) * D : nullptr;
+                const float* vb = p.bias ? p.bias + (size_t)(p.nq + p.nkv + kvh) * D : nullptr;
+                const int slot = p.slots[n0];
+                const int page = slot >= 0 ? slot / p.page_size : 0, off = slot >= 0 ? slot - page * p.page_size : 0;
+                const size_t dst = (((size_t)page * p.nkv + kvh) * p.page_size + off) * D;
+#pragma unroll
+                for (int i = 0; i < NP; ++i) {
+                    const int j = lane + 32 * i;
+                    float k1 = __ldcg(ks_ + j), k2 = __ldcg(ks_ + j + D / 2), v1 = __ldcg(vs_ + j), v2 = __ldcg(vs_ + j + D / 2);
+                    if (p.bias) { k1 += kb[j]; k2 += kb[j + D / 2]; v1 += vb[j]; v2 += vb[j + D / 2]; }
+                    const float c = ct[j], sv = sn[j];
+                    const __nv_bfloat16 r1 = __float2bfloat16_rn(k1 * c - k2 * sv), r2 = __float2bfloat16_rn(k2 * c + k1 * sv);
+                    const __nv_bfloat16 w1 = __float2bfloat16_rn(v1), w2 = __float2bfloat16_rn(v2);
+                    own_k[i] = (uint32_t)__bfloat16_as_ushort(r1) | ((uint32_t)__bfloat16_as_ushort(r2) << 16);
+                    own_v[i] = (uint32_t)__bfloat16_as_ushort(w1) | ((uint32_t)__bfloat16_as_ushort(w2) << 16);
+                    if (slot >= 0) {
+                        p.k_pool_w[dst + j] = r1; p.k_pool_w[dst + j + D / 2] = r2;
+                        p.v_pool_w[dst + j] = w1; p.v_pool_w[dst + j + D / 2] = w2;
+                    }
+                }
+            }
+        } else {
+            const bf16* qp = p.q + (size_t)n0 * p.q_stride + (size_t)(kvh * G + (ok ? row : 0)) * D;
+#pragma unroll
+            for (int kk = 0; kk < D / 16; ++kk) {
+                const int col = kk * 16 + ((lane & 3) << 1);
+                qb[kk][0] = ok ? *reinterpret_cast<const uint32_t*>(qp + col) : 0u;
+                qb[kk][1] = ok ? *reinterpret_cast<const uint32_t*>(qp + col + 8) : 0u;
+            }
         }
 #pragma unroll
         for (int i = 0; i < D / 16; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
@@ -393,8 +474,25 @@ __global__ void __launch_bounds__(DW * 32) attn_mma_decode_kernel(const Params p
         // fetches in group 0): everything but the STAGES - 1 youngest groups must have landed
         cp_async_wait<STAGES - 1>();
         __syncwarp();
-        const bf16* cur = my + (it % STAGES) * 2 * TILE;
+        bf16* cur = my + (it % STAGES) * 2 * TILE;
         const int key0 = lo + (first + it * DW) * BN;
+        if (it == own_it) {
+            // The token's own position lies in this chunk, and the cache did not hold its key and value when the chunk was
+            // fetched: the row (and the rows behind it, which were fetched from the same place and which the mask hides, but
+            // whose values would still be multiplied by zero) gets what this warp has just made.
+#pragma unroll 1
+            for (int r = pos0 - key0; r < BN; ++r) {
+#pragma unroll
+                for (int i = 0; i < NP; ++i) {
+                    const int j = lane + 32 * i;
+                    cur[swz<D>(r, j)] = __ushort_as_bfloat16((unsigned short)(own_k[i] & 0xffffu));
+                    cur[swz<D>(r, j + D / 2)] = __ushort_as_bfloat16((unsigned short)(own_k[i] >> 16));
+                    cur[TILE + swz<D>(r, j)] = __ushort_as_bfloat16((unsigned short)(own_v[i] & 0xffffu));
+                    cur[TILE + swz<D>(r, j + D / 2)] = __ushort_as_bfloat16((unsigned short)(own_v[i] >> 16));
+                }
+            }
+            __syncwarp();
+        }
         // a chunk that lies wholly before the first token's position (and inside every window) needs no mask arithmetic;
         // rows beyond the tile then collect numbers nobody reads
         const bool interior = key0 + BN - 1 <= pos0 && (p.window <= 0 || key0 > hi - 1 - p.window);
@@ -713,11 +811,15 @@ LLMIE_API int llmie_attn_plan(const int* seq_starts, int num_seqs, int tokens_pe
 // decode_mode 1: every tile has at most 16 rows (tokens * group). 0: at most 64 rows.
 // scratch_o / scratch_ml / counters are needed for num_splits > 1 (counters zeroed once; the kernel leaves them zero), unless
 // `cluster` is set (decode mode, at most 8 slices): the slices then form one thread-block cluster and merge in shared memory.
-LLMIE_API int llmie_paged_attention_mma(const bf16* q, int q_stride, const bf16* k_pool, const bf16* v_pool, const int* block_table,
-                                        int max_blocks, const int* token_seq, const int* positions, const int* tile_info, int num_tiles,
-                                        bf16* out, float* scratch_o, float* scratch_ml, int* counters, int nq, int nkv, int d,
-                                        int page_size, float scale, int window, int num_splits, int decode_mode, int cluster, cudaStream_t s) {
+static int run_mma(const bf16* q, int q_stride, const bf16* k_pool, const bf16* v_pool, const int* block_table,
+                   int max_blocks, const int* token_seq, const int* positions, const int* tile_info, int num_tiles,
+                   bf16* out, float* scratch_o, float* scratch_ml, int* counters, int nq, int nkv, int d,
+                   int page_size, float scale, int window, int num_splits, int decode_mode, int cluster, const float* qkv_acc,
+                   int acc_stride, const float* bias, const float* cos_t, const float* sin_t, const int* slots, cudaStream_t s) {
     if (num_tiles <= 0) return 0;
+    if (qkv_acc && (!decode_mode || tile_info || nq / (nkv > 0 ? nkv : 1) > 8 || !cos_t || !sin_t || acc_stride < (nq + 2 * nkv) * d ||
+                    (acc_stride & 1) || ((uintptr_t)qkv_acc & 7) || ((uintptr_t)bias & 7) || ((uintptr_t)cos_t & 7) || ((uintptr_t)sin_t & 7)))
+        return LLMIE_ERR_BAD_ARGUMENT;
     if (cluster && (!decode_mode || num_splits > 8)) return LLMIE_ERR_BAD_ARGUMENT;
     if ((d != 64 && d != 128) || nkv <= 0 || nq % nkv || page_size <= 0 || num_splits < 1 || q_stride % 8 || nkv > 65535 ||
         num_splits > 64 || (num_splits > 1 && !cluster && (!scratch_o || !scratch_ml || !counters)))
@@ -730,5 +832,30 @@ LLMIE_API int llmie_paged_attention_mma(const bf16* q, int q_stride, const bf16*
     p.q_stride = q_stride; p.max_blocks = max_blocks; p.nq = nq; p.nkv = nkv; p.page_size = page_size; p.window = window;
     p.page_shift = (page_size & (page_size - 1)) == 0 ? __builtin_ctz((unsigned)page_size) : -1;
     p.num_splits = num_splits; p.scale_log2 = scale * LOG2E; p.cluster = cluster;
+    p.qkv_acc = qkv_acc; p.acc_stride = acc_stride; p.bias = bias; p.cos_t = cos_t; p.sin_t = sin_t; p.slots = slots;
+    p.k_pool_w = const_cast<bf16*>(k_pool); p.v_pool_w = const_cast<bf16*>(v_pool);
     return d == 64 ? launch<64>(p, num_tiles, decode_mode, s) : launch<128>(p, num_tiles, decode_mode, s);
+}
+
+LLMIE_API int llmie_paged_attention_mma(const bf16* q, int q_stride, const bf16* k_pool, const bf16* v_pool, const int* block_table,
+                                        int max_blocks, const int* token_seq, const int* positions, const int* tile_info, int num_tiles,
+                                        bf16* out, float* scratch_o, float* scratch_ml, int* counters, int nq, int nkv, int d,
+                                        int page_size, float scale, int window, int num_splits, int decode_mode, int cluster, cudaStream_t s) {
+    return run_mma(q, q_stride, k_pool, v_pool, block_table, max_blocks, token_seq, positions, tile_info, num_tiles, out, scratch_o, scratch_ml,
+                   counters, nq, nkv, d, page_size, scale, window, num_splits, decode_mode, cluster, nullptr, 0, nullptr, nullptr, nullptr,
+                   nullptr, s);
+}
+
+// Decode steps (every tile one token, at most 8 query heads per key/value head): the same attention, with the queries, keys and
+// values of the step's tokens taken from `qkv_acc`, the float32 sums [tokens][acc_stride] of the fused q/k/v projection
+// before bias and rotation (nothing clears them here). The kernel adds `bias` (or none), rotates queries and keys by
+// cos_t / sin_t [tokens][d / 2] and, where `slots` is given, writes each token's key and value into its cache slot.
+LLMIE_API int llmie_paged_attention_mma_acc(const float* qkv_acc, int acc_stride, const float* bias, const float* cos_t, const float* sin_t,
+                                            const int* slots, bf16* k_pool, bf16* v_pool, const int* block_table, int max_blocks,
+                                            const int* token_seq, const int* positions, int num_tokens, bf16* out, float* scratch_o,
+                                            float* scratch_ml, int* counters, int nq, int nkv, int d, int page_size, float scale, int window,
+                                            int num_splits, int cluster, cudaStream_t s) {
+    if (!qkv_acc) return LLMIE_ERR_BAD_ARGUMENT;
+    return run_mma(nullptr, 8, k_pool, v_pool, block_table, max_blocks, token_seq, positions, nullptr, num_tokens, out, scratch_o, scratch_ml,
+                   counters, nq, nkv, d, page_size, scale, window, num_splits, 1, cluster, qkv_acc, acc_stride, bias, cos_t, sin_t, slots, s);
 }

@@ -231,10 +231,17 @@ LLMIE_API int llmie_rope_kv_write(void* in, void* out, const float* bias, const 
 // ------------------------------------------------------------------------------------------------
 // out[n, i] = silu(gu[n, i]) * gu[n, I + i], silu(z) = z / (1 + exp(-z)) in 32-bit; `clear_in` zeroes what was read.
 // grid = (column blocks, rows); VEC = 4 moves four columns per thread.
+// `also_zero` (with `zero_n4` groups of four floats): another float32 accumulation buffer that this kernel clears on its way,
+// one that an earlier kernel of the step read but could not clear itself because several of its blocks read it.
 template <typename TI, typename TO, int VEC>
-__global__ void silu_mul_kernel(TI* __restrict__ gu, TO* __restrict__ out, int I, int clear_in) {
+__global__ void silu_mul_kernel(TI* __restrict__ gu, TO* __restrict__ out, int I, int clear_in, float* __restrict__ also_zero, int zero_n4) {
     pdl_trigger();
     pdl_wait();
+    if (also_zero) {
+        const int threads = gridDim.x * gridDim.y * blockDim.x;
+        for (int i = (blockIdx.y * gridDim.x + blockIdx.x) * blockDim.x + threadIdx.x; i < zero_n4; i += threads)
+            reinterpret_cast<float4*>(also_zero)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
     constexpr int PER = VEC == 4 ? 2 : 1;  // vectors per thread: two loads of gate and two of up are in flight together
     const int i0 = (blockIdx.x * blockDim.x + threadIdx.x) * VEC * PER;
     TI* row = gu + (size_t)blockIdx.y * 2 * I;
@@ -302,30 +309,35 @@ __global__ void __launch_bounds__(256) silu_mul_bf16x8_kernel(const bf16* __rest
 }
 
 template <typename TI, typename TO>
-static int launch_silu_mul(TI* gu, TO* out, int N, int I, int clear_in, cudaStream_t s) {
+static int launch_silu_mul(TI* gu, TO* out, int N, int I, int clear_in, float* also_zero, int zero_n4, cudaStream_t s) {
     if (N > 65535) {  // rows ride in grid.y; more rows than that go in slabs
         for (int n0 = 0; n0 < N; n0 += 65535) {
-            const int rc = launch_silu_mul<TI, TO>(gu + (size_t)n0 * 2 * I, out + (size_t)n0 * I, min(65535, N - n0), I, clear_in, s);
+            const int rc = launch_silu_mul<TI, TO>(gu + (size_t)n0 * 2 * I, out + (size_t)n0 * I, min(65535, N - n0), I, clear_in,
+                                                   n0 == 0 ? also_zero : nullptr, zero_n4, s);
             if (rc) return rc;
         }
         return 0;
     }
     const bool vec = I % 4 == 0 && ((uintptr_t)gu % 16 == 0) && ((uintptr_t)out % 16 == 0);
-    if (vec) return launch_kernel(silu_mul_kernel<TI, TO, 4>, dim3(((I + 7) / 8 + 127) / 128, N), dim3(128), 0, s, gu, out, I, clear_in);
-    return launch_kernel(silu_mul_kernel<TI, TO, 1>, dim3((I + 127) / 128, N), dim3(128), 0, s, gu, out, I, clear_in);
+    if (vec) return launch_kernel(silu_mul_kernel<TI, TO, 4>, dim3(((I + 7) / 8 + 127) / 128, N), dim3(128), 0, s, gu, out, I, clear_in, also_zero, zero_n4);
+    return launch_kernel(silu_mul_kernel<TI, TO, 1>, dim3((I + 127) / 128, N), dim3(128), 0, s, gu, out, I, clear_in, also_zero, zero_n4);
 }
 
-LLMIE_API int llmie_silu_mul(void* gu, void* out, int N, int I, int clear_in, int in_dtype, int out_dtype, cudaStream_t s) {
+// also_zero / zero_floats: a float32 buffer (16-byte aligned, a multiple of 4 floats) that is cleared as well, or null.
+LLMIE_API int llmie_silu_mul(void* gu, void* out, int N, int I, int clear_in, int in_dtype, int out_dtype, float* also_zero,
+                             long long zero_floats, cudaStream_t s) {
     if (N <= 0) return 0;
-    if (in_dtype == DT_F32 && out_dtype == DT_F32) return launch_silu_mul<float, float>((float*)gu, (float*)out, N, I, clear_in, s);
+    if (also_zero && (((uintptr_t)also_zero & 15) || (zero_floats & 3) || zero_floats > (1ll << 32))) return LLMIE_ERR_BAD_ARGUMENT;
+    const int n4 = also_zero ? (int)(zero_floats / 4) : 0;
+    if (in_dtype == DT_F32 && out_dtype == DT_F32) return launch_silu_mul<float, float>((float*)gu, (float*)out, N, I, clear_in, also_zero, n4, s);
     if (in_dtype == DT_BF16 && out_dtype == DT_BF16) {
-        if (!clear_in && I % 8 == 0 && ((uintptr_t)gu % 16 == 0) && ((uintptr_t)out % 16 == 0)) {
+        if (!clear_in && !also_zero && I % 8 == 0 && ((uintptr_t)gu % 16 == 0) && ((uintptr_t)out % 16 == 0)) {
             const long long items = (long long)N * (I / 8);
             return launch_kernel(silu_mul_bf16x8_kernel, dim3((unsigned)(((items + 1) / 2 + 255) / 256)), dim3(256), 0, s, (const bf16*)gu, (bf16*)out, I, items);
         }
-        return launch_silu_mul<bf16, bf16>((bf16*)gu, (bf16*)out, N, I, clear_in, s);
+        return launch_silu_mul<bf16, bf16>((bf16*)gu, (bf16*)out, N, I, clear_in, also_zero, n4, s);
     }
-    if (in_dtype == DT_F32 && out_dtype == DT_BF16) return launch_silu_mul<float, bf16>((float*)gu, (bf16*)out, N, I, clear_in, s);
+    if (in_dtype == DT_F32 && out_dtype == DT_BF16) return launch_silu_mul<float, bf16>((float*)gu, (bf16*)out, N, I, clear_in, also_zero, n4, s);
     return LLMIE_ERR_BAD_ARGUMENT;
 }
 

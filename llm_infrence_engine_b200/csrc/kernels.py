@@ -63,11 +63,14 @@ class CudaKernels:
         # the stream: that kernel is usually the norm, which adds and normalises in one pass (see ``flush``).
         self._pending_add: Optional[tuple] = None
         self._error_flag: Optional[torch.Tensor] = None
+        self._acc_qkv: Optional[torch.Tensor] = None   # float32 sums of a decode step's q/k/v product, read by the attention kernel
+        self._dirty_qkv: Optional[torch.Tensor] = None  # those sums while they still wait to be cleared
+        self.fuse_decode_rope = True   # decode steps: bias, rotation and cache write happen inside the attention kernel
         self._retired_acc: list = []   # accumulation buffers that were outgrown: captured graphs may still add into and clear them
         self._sms: dict = {}
         self.last_attention_plan = (1, False)   # (key slices, merged as a cluster) of the last tensor-core attention launch
         for fn in ("llmie_embed", "llmie_feed_tokens", "llmie_rope_tables", "llmie_add_rmsnorm", "llmie_rope_kv_write", "llmie_silu_mul",
-                   "llmie_gemm_simt", "llmie_gemm_tc", "llmie_qkv_rope_tc", "llmie_add_into", "llmie_attn_plan", "llmie_attn_tc_plan", "llmie_paged_attention_mma", "llmie_paged_attention_tc", "llmie_paged_attention_f32", "llmie_paged_attention_bf16", "llmie_argmax", "llmie_sample"):
+                   "llmie_gemm_simt", "llmie_gemm_tc", "llmie_qkv_rope_tc", "llmie_add_into", "llmie_attn_plan", "llmie_attn_tc_plan", "llmie_paged_attention_mma", "llmie_paged_attention_mma_acc", "llmie_paged_attention_tc", "llmie_paged_attention_f32", "llmie_paged_attention_bf16", "llmie_argmax", "llmie_sample"):
             getattr(self.lib, fn).restype = ctypes.c_int
         # kernels of a step overlap their set-up with the tail of the kernel before (programmatic dependent launch)
         self.lib.llmie_set_pdl(0 if os.environ.get("LLMIE_PDL", "1") == "0" else 1)
@@ -85,7 +88,8 @@ class CudaKernels:
         """After an exception in the middle of a step: nothing of it may reach the next one. An addition that was put off
         is dropped, and the accumulation buffers, which every product assumes to be zero, are cleared."""
         self._pending_add = None
-        for t in [self._acc, *self._retired_acc]:
+        self._dirty_qkv = None
+        for t in [self._acc, self._acc_qkv, *self._retired_acc]:
             if t is not None:
                 try:
                     t.zero_()
@@ -497,21 +501,13 @@ class CudaKernels:
             ctypes.c_float(scale), int(window), _ptr(self._errors(qkv.device)), self._stream()), "paged_attention (tcgen05)")
         return out
 
-    def _attention_mma(self, qkv, k_pool, v_pool, block_table, token_seq, positions, out, num_heads, num_kv_heads, head_dim,
-                       page_size, scale, window, span, batch, num_splits):
-        group = num_heads // num_kv_heads
-        decode = batch.max_seq_len == 1
-        N = qkv.shape[0]
-        if not decode:
-            done = self._attention_tc(qkv, k_pool, v_pool, block_table, token_seq, positions, out, num_heads, num_kv_heads, head_dim,
-                                      page_size, scale, window, span, batch, num_splits)
-            if done is not None:
-                return done
-        if decode:
-            tiles, tile_info, rows, chunk = N, None, 16, (32 if head_dim == 64 else 16)
-        else:
-            tiles, tile_info = self._tiles(batch, max(1, 64 // group), qkv.device)
-            rows, chunk = 64, 64
+    def _decode_plan(self, tokens, num_kv_heads, head_dim, span, num_splits, device):
+        return self._slices(tokens, num_kv_heads, head_dim, span, num_splits, True, device)
+
+    def _slices(self, tiles, num_kv_heads, head_dim, span, num_splits, decode, device):
+        """How the tensor-core attention (mma.sync kernels) cuts a tile's keys: (slices, merged as a cluster, scratch for the
+        outputs, scratch for maxima and sums, counters)."""
+        rows, chunk = (16, 32 if head_dim == 64 else 16) if decode else (64, 64)
         chunks = max(1, -(-span // chunk))
         explicit = num_splits
         if num_splits is None:
@@ -525,19 +521,109 @@ class CudaKernels:
         self.last_attention_plan = (num_splits, bool(cluster))
         if num_splits > 1 and not cluster:
             cells = tiles * num_kv_heads * num_splits * rows
-            buf = self._scratch(cells * (head_dim + 2), qkv.device)
+            buf = self._scratch(cells * (head_dim + 2), device)
             scratch_o, scratch_ml = buf, buf[cells * head_dim:]
             if tiles * num_kv_heads > (1 << 20):
                 raise KernelError("paged_attention: too many tiles for the split counters")
-            if self._attn_counters is None or self._attn_counters.device != qkv.device:
-                self._attn_counters = torch.zeros(1 << 20, dtype=torch.int32, device=qkv.device)
+            if self._attn_counters is None or self._attn_counters.device != device:
+                self._attn_counters = torch.zeros(1 << 20, dtype=torch.int32, device=device)
             counters = self._attn_counters
+        return num_splits, cluster, scratch_o, scratch_ml, counters
+
+    def _attention_mma(self, qkv, k_pool, v_pool, block_table, token_seq, positions, out, num_heads, num_kv_heads, head_dim,
+                       page_size, scale, window, span, batch, num_splits):
+        group = num_heads // num_kv_heads
+        decode = batch.max_seq_len == 1
+        N = qkv.shape[0]
+        if not decode:
+            done = self._attention_tc(qkv, k_pool, v_pool, block_table, token_seq, positions, out, num_heads, num_kv_heads, head_dim,
+                                      page_size, scale, window, span, batch, num_splits)
+            if done is not None:
+                return done
+        if decode:
+            tile_info = None
+            num_splits, cluster, scratch_o, scratch_ml, counters = self._decode_plan(N, num_kv_heads, head_dim, span, num_splits, qkv.device)
+            tiles = N
+        else:
+            tiles, tile_info = self._tiles(batch, max(1, 64 // group), qkv.device)
+            num_splits, cluster, scratch_o, scratch_ml, counters = self._slices(tiles, num_kv_heads, head_dim, span, num_splits, False, qkv.device)
         self._check(self.lib.llmie_paged_attention_mma(
             _ptr(qkv), qkv.shape[1], _ptr(k_pool), _ptr(v_pool), _ptr(block_table), block_table.shape[1], _ptr(token_seq),
             _ptr(positions), _ptr(tile_info), tiles, _ptr(out), _ptr(scratch_o), _ptr(scratch_ml), _ptr(counters), num_heads,
             num_kv_heads, head_dim, page_size, ctypes.c_float(scale), int(window), num_splits, int(decode), cluster, self._stream()),
             "paged_attention (tensor cores)")
         return out
+
+    def _clear_dirty(self) -> None:
+        """Clear, with a kernel of its own, the projection sums that a fused attention left behind, if no kernel since has done
+        it on its way (``silu_mul`` does)."""
+        if self._dirty_qkv is not None:
+            self._dirty_qkv.zero_()
+            self.launches += 1
+            self._dirty_qkv = None
+
+    def _qkv_sums(self, rows: int, width: int, device) -> torch.Tensor:
+        """Zeroed float32 ``[rows, width]`` that a decode step's q/k/v product adds into and the attention reads. (A buffer of
+        its own, not the one ``linear(transient=True)`` hands out: the gate/up product needs that one while this is still dirty.)"""
+        need = rows * width
+        if self._acc_qkv is None or self._acc_qkv.numel() < need or self._acc_qkv.device != device:
+            if self._acc_qkv is not None:
+                self._retired_acc.append(self._acc_qkv)
+            self._acc_qkv = torch.zeros(max(need, self.tc_max_rows * width), dtype=torch.float32, device=device)
+        return self._acc_qkv[:need].view(rows, width)
+
+    def qkv_attention(self, x, w, bias, cos, sin, slot_mapping, k_pool, v_pool, block_table, token_seq, positions, num_heads,
+                      num_kv_heads, head_dim, page_size, scale, window, max_context, batch=None, write_kv=True, out_dtype=None):
+        """The fused q/k/v projection of the step's rows (bias, rotation, cache write) and their attention over the pages.
+
+        Decode steps in bfloat16 (one row per request, heads of 64 or 128, at most 8 query heads per key/value head) take two
+        kernels: the small-batch tensor-core product, whose split-K blocks add into float32 sums, and the attention, which
+        adds the bias, rotates the queries in its registers and lets the one warp that owns a token's own position finish its
+        key and value, put them into its chunk of keys and write them to the cache. Everything else is ``qkv_rope`` followed
+        by ``paged_attention``."""
+        M, K_ = x.shape
+        group = num_heads // max(num_kv_heads, 1)
+        width = (num_heads + 2 * num_kv_heads) * head_dim
+        if (self.fuse_decode_rope and self.use_mma_attention and self.use_tc_gemm and batch is not None and batch.max_seq_len == 1
+                and x.dtype == torch.bfloat16 and (out_dtype or x.dtype) == torch.bfloat16 and head_dim in (64, 128) and group <= 8
+                and num_heads % max(num_kv_heads, 1) == 0 and M <= self.tc_max_rows and K_ % 8 == 0 and tuple(w.shape) == (width, K_)
+                and x.is_contiguous() and w.is_contiguous()):
+            self._need(cos, "cos", torch.float32, 2)
+            self._need(sin, "sin", torch.float32, 2)
+            if tuple(cos.shape) != (M, head_dim // 2) or tuple(sin.shape) != (M, head_dim // 2):
+                raise KernelError("qkv_attention: cos and sin must be [tokens, head_dim / 2]")
+            if bias is not None:
+                self._need(bias, "bias", torch.float32, 1)
+                if bias.shape[0] != width:
+                    raise KernelError("qkv_attention: bias does not match the projection's width")
+            for name, pool in (("k_pool", k_pool), ("v_pool", v_pool)):
+                self._need(pool, name, torch.bfloat16, 4)
+                if tuple(pool.shape[1:]) != (num_kv_heads, page_size, head_dim):
+                    raise KernelError(f"qkv_attention: {name} is {list(pool.shape)}, expected [pages, {num_kv_heads}, {page_size}, {head_dim}]")
+            self._need(block_table, "block_table", torch.int32, 2)
+            self._need(token_seq, "token_seq", torch.int32, 1)
+            self._need(positions, "positions", torch.int32, 1)
+            if write_kv:
+                self._need(slot_mapping, "slot_mapping", torch.int32, 1)
+            if block_table.shape[1] * page_size < max_context:
+                raise KernelError(f"qkv_attention: block tables of {block_table.shape[1]} pages cannot hold {max_context} tokens")
+            self._clear_dirty()
+            sums = self._qkv_sums(M, width, x.device)
+            self.linear_tc(x, w, out=sums, accumulate=True)
+            out = torch.empty((M, num_heads * head_dim), dtype=torch.bfloat16, device=x.device)
+            span = min(max_context, window) if window else max_context
+            num_splits, cluster, scratch_o, scratch_ml, counters = self._decode_plan(M, num_kv_heads, head_dim, span, None, x.device)
+            self._check(self.lib.llmie_paged_attention_mma_acc(
+                _ptr(sums), width, _ptr(bias), _ptr(cos), _ptr(sin), _ptr(slot_mapping if write_kv else None), _ptr(k_pool), _ptr(v_pool),
+                _ptr(block_table), block_table.shape[1], _ptr(token_seq), _ptr(positions), M, _ptr(out), _ptr(scratch_o), _ptr(scratch_ml),
+                _ptr(counters), num_heads, num_kv_heads, head_dim, page_size, ctypes.c_float(scale), int(window), num_splits, cluster,
+                self._stream()), "qkv_attention (tensor cores)")
+            self._dirty_qkv = sums
+            return out
+        qkv = self.qkv_rope(x, w, bias, cos, sin, slot_mapping, k_pool, v_pool, num_heads, num_kv_heads, head_dim, page_size, write_kv,
+                            out_dtype=out_dtype)
+        return self.paged_attention(qkv, k_pool, v_pool, block_table, token_seq, positions, num_heads, num_kv_heads, head_dim, page_size,
+                                    scale, window, max_context, batch=batch)
 
     def silu_mul(self, gu, out_dtype=None):
         """``silu(gate) * up`` of a fused gate/up projection ``[rows, 2 I]`` (gate first); a transient float32 input is consumed and cleared."""
@@ -546,8 +632,11 @@ class CudaKernels:
             raise KernelError("silu_mul: the row must hold gate and up halves of equal width")
         N, I = gu.shape[0], gu.shape[1] // 2
         out = torch.empty((N, I), dtype=out_dtype or gu.dtype, device=gu.device)
+        # a projection's sums that the attention read but could not clear (several of its blocks read them) are cleared here
+        dirty, self._dirty_qkv = self._dirty_qkv, None
         self._check(self.lib.llmie_silu_mul(_ptr(gu), _ptr(out), N, I, int(self._is_transient(gu)), self._dt(gu, "gate_up"),
-                                            self._dt(out, "out"), self._stream()), "silu_mul")
+                                            self._dt(out, "out"), _ptr(dirty), ctypes.c_longlong(0 if dirty is None else dirty.numel()),
+                                            self._stream()), "silu_mul")
         return out
 
     def argmax(self, logits):

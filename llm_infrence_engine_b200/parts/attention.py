@@ -17,7 +17,8 @@ class PagedAttention(Mixer):
 
     The three projections are kept as one matrix ``[(num_heads + 2 num_kv_heads) * head_dim, hidden]``
     so a step multiplies once; the bias (if any), the rotation of q and k and the write of k and v
-    into the request's pages are one kernel. A token at position ``p`` sees keys ``0..p`` of its own
+    into the request's pages are one kernel, or, in decode steps, the opening of the attention kernel itself
+    (``qkv_attention`` of the kernels object decides). A token at position ``p`` sees keys ``0..p`` of its own
     request, or ``p - window + 1 .. p`` when ``window`` is set; the mask is never a tensor.
     """
 
@@ -54,9 +55,8 @@ class PagedAttention(Mixer):
     def forward(self, ctx, h, cache, residual):
         K = ctx.K
         cos, sin = ctx.position_tables(self.position)
-        qkv = K.qkv_rope(h, self.w_qkv, self.b_qkv, cos, sin, ctx.slot_mapping[cache.group], cache.k, cache.v,
-                         self.num_heads, self.num_kv_heads, self.head_dim, ctx.page_size, cache.write, out_dtype=ctx.dtype)
-        attn = K.paged_attention(qkv, cache.k, cache.v, ctx.block_tables[cache.group], ctx.token_seq, ctx.positions,
-                                 self.num_heads, self.num_kv_heads, self.head_dim, ctx.page_size, self.scale,
-                                 self.window or 0, ctx.max_context, batch=ctx)
+        attn = K.qkv_attention(h, self.w_qkv, self.b_qkv, cos, sin, ctx.slot_mapping[cache.group], cache.k, cache.v,
+                               ctx.block_tables[cache.group], ctx.token_seq, ctx.positions, self.num_heads, self.num_kv_heads,
+                               self.head_dim, ctx.page_size, self.scale, self.window or 0, ctx.max_context, batch=ctx,
+                               write_kv=cache.write, out_dtype=ctx.dtype)
         K.linear(attn, self.w_o, add_to=residual)

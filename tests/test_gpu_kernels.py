@@ -349,6 +349,62 @@ def test_decode_attention_with_many_key_slices(K, monkeypatch, cluster, nq, nkv,
     assert K._attn_counters is None or K._attn_counters.abs().sum().item() == 0
 
 
+@pytest.mark.parametrize("cluster", [True, False])
+@pytest.mark.parametrize("nq,nkv,d,ps,H,lens,window,bias,write", [
+    (14, 2, 64, 16, 896, [300, 700, 5, 64, 65, 1, 33, 32], 0, True, True),   # page edges, a request of one token, chunk edges
+    (14, 2, 64, 16, 896, [8192] * 8, 0, True, True),                          # the headline decode step
+    (14, 2, 64, 16, 896, [4000, 17, 2100], 0, True, True),                    # several slices, one request far shorter
+    (12, 2, 128, 16, 1536, [513, 31, 1000, 2049], 0, True, True),             # heads of 128
+    (4, 4, 64, 8, 200, [90, 33, 41], 40, False, True),                        # a window, no bias, no grouping, pages of 8
+    (6, 3, 64, 32, 96, [70, 200], 0, True, False),                            # keys and values are in the cache already
+    (16, 2, 128, 64, 256, [130, 64], 0, True, True),                          # 8 heads per key/value head, pages of 64
+])
+def test_qkv_attention_of_a_decode_step(K, monkeypatch, cluster, nq, nkv, d, ps, H, lens, window, bias, write):
+    """Decode steps: the q/k/v product leaves float32 sums, and the attention kernel itself adds the bias, rotates and writes
+    the token's key and value into the cache, against product, rotation kernel and attention one after the other in plain
+    torch. The tokens' own cache slots (and everything behind them) hold NaN beforehand: nothing stale may be read."""
+    monkeypatch.setattr(K, "cluster_merge", cluster)
+    g = torch.Generator().manual_seed(50)
+    B = len(lens)
+    qlens = [1] * B
+    _, kp, vp, table, tseq, pos = _attention_case(torch.bfloat16, nq, nkv, d, ps, lens, qlens, window, 51)
+    width = (nq + 2 * nkv) * d
+    x = torch.randn(B, H, generator=g).to(torch.bfloat16)
+    w = (torch.randn(width, H, generator=g) / math.sqrt(H)).to(torch.bfloat16)
+    b = torch.randn(width, generator=g) if bias else None
+    inv = 1.0 / (1e6 ** (torch.arange(0, d, 2).float() / d))
+    cos, sin = REF.rope_tables(pos, inv)
+    slots = torch.tensor([int(table[r, (L - 1) // ps]) * ps + (L - 1) % ps for r, L in enumerate(lens)], dtype=torch.int32)
+    scale = 1.0 / math.sqrt(d)
+    kp_ref, vp_ref = kp.float(), vp.float()
+    want = REF.qkv_attention(x.float(), w.float(), b, cos, sin, slots, kp_ref, vp_ref, table, tseq, pos, nq, nkv, d, ps, scale, window,
+                             max(lens), write_kv=True)   # the plain side always writes: with write off, the engine's cache holds them already
+    kp_in, vp_in = (kp_ref.to(torch.bfloat16), vp_ref.to(torch.bfloat16)) if not write else (kp.clone(), vp.clone())
+    if write:   # never written: the token's own slot and the rest of its page
+        for r, L in enumerate(lens):
+            page = int(table[r, (L - 1) // ps])
+            kp_in[page, :, (L - 1) % ps:] = float("nan")
+            vp_in[page, :, (L - 1) % ps:] = float("nan")
+    kp_gpu, vp_gpu = kp_in.cuda(), vp_in.cuda()
+    dev = [t.cuda() for t in (x, w, cos, sin, slots, table, tseq, pos)]
+    for _ in range(2):
+        before = K.launches
+        got = K.qkv_attention(dev[0], dev[1], None if b is None else b.cuda(), dev[2], dev[3], dev[4], kp_gpu, vp_gpu, dev[5], dev[6], dev[7],
+                              nq, nkv, d, ps, scale, window, max(lens), batch=_Batch(qlens), write_kv=write)
+        K.check_device_errors()
+        assert K.launches - before == 2 and K._dirty_qkv is not None     # the product and the attention, nothing else
+        assert not torch.isnan(got).any()
+        close(got, want, 1e-2)
+        own_k = torch.stack([kp_gpu[int(s) // ps, :, int(s) % ps] for s in slots]).float().cpu()
+        own_v = torch.stack([vp_gpu[int(s) // ps, :, int(s) % ps] for s in slots]).float().cpu()
+        close(own_k, torch.stack([kp_ref[int(s) // ps, :, int(s) % ps] for s in slots]), 1e-2)
+        close(own_v, torch.stack([vp_ref[int(s) // ps, :, int(s) % ps] for s in slots]), 1e-2)
+        # the sums wait to be cleared by the next kernel that can do it on its way
+        K.silu_mul(torch.randn(B, 64, device="cuda").to(torch.bfloat16))
+        assert K._dirty_qkv is None and K._acc_qkv.abs().sum().item() == 0
+    assert K._attn_counters is None or K._attn_counters.abs().sum().item() == 0
+
+
 @pytest.mark.parametrize("nq,nkv,ps,lens,qlens,window", [
     (14, 2, 16, [2048], [2048], 0),                       # the bench's prompt: 18 tokens x 7 heads per tile
     (14, 2, 16, [3000], [40], 0),                         # a short portion far into a long request: few tiles, their keys in slices
