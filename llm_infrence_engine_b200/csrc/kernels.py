@@ -55,6 +55,7 @@ class CudaKernels:
         self.use_tc_attention = True   # prompt portions of head size 64: scores and outputs through tcgen05 and tensor memory
         self.cluster_merge = True      # decode attention: the key slices of a token form a cluster and merge in shared memory
         self.use_tc_gemm = True
+        self.use_tc_gate_up = True     # prompt portions: gate/up product with the activation as its epilogue, one tcgen05 kernel
         self.use_tc_qkv = True         # prompt portions, head size 64: q/k/v product with bias, rotation and cache write in one kernel
         self.tc_max_rows = 128        # batches up to this many rows take the small-batch tensor-core product
         self.slice_keys = 1024         # generic attention: keys per slice, at fixed places of a request (a multiple of 32)
@@ -70,7 +71,7 @@ class CudaKernels:
         self._sms: dict = {}
         self.last_attention_plan = (1, False)   # (key slices, merged as a cluster) of the last tensor-core attention launch
         for fn in ("llmie_embed", "llmie_feed_tokens", "llmie_rope_tables", "llmie_add_rmsnorm", "llmie_rope_kv_write", "llmie_silu_mul",
-                   "llmie_gemm_simt", "llmie_gemm_tc", "llmie_qkv_rope_tc", "llmie_add_into", "llmie_attn_plan", "llmie_attn_tc_plan", "llmie_paged_attention_mma", "llmie_paged_attention_mma_acc", "llmie_paged_attention_tc", "llmie_paged_attention_f32", "llmie_paged_attention_bf16", "llmie_argmax", "llmie_sample"):
+                   "llmie_gemm_simt", "llmie_gemm_tc", "llmie_gateup_silu_tc", "llmie_qkv_rope_tc", "llmie_add_into", "llmie_attn_plan", "llmie_attn_tc_plan", "llmie_paged_attention_mma", "llmie_paged_attention_mma_acc", "llmie_paged_attention_tc", "llmie_paged_attention_f32", "llmie_paged_attention_bf16", "llmie_argmax", "llmie_sample"):
             getattr(self.lib, fn).restype = ctypes.c_int
         # kernels of a step overlap their set-up with the tail of the kernel before (programmatic dependent launch)
         self.lib.llmie_set_pdl(0 if os.environ.get("LLMIE_PDL", "1") == "0" else 1)
@@ -624,6 +625,22 @@ class CudaKernels:
                             out_dtype=out_dtype)
         return self.paged_attention(qkv, k_pool, v_pool, block_table, token_seq, positions, num_heads, num_kv_heads, head_dim, page_size,
                                     scale, window, max_context, batch=batch)
+
+    def gate_up_act(self, x, w_gate_up, out_dtype=None):
+        """``silu(x Wg^T) * (x Wu^T)`` for the fused matrix ``w_gate_up`` ``[2 I, K]`` (gate rows first). Prompt portions in
+        bfloat16 take one tcgen05 kernel whose epilogue is the activation (the float32 sums stay in tensor memory; nothing of
+        width 2 I is written); everything else is the product followed by ``silu_mul``."""
+        out_dtype = out_dtype or x.dtype
+        M, K_ = x.shape
+        if (self.use_tc_gate_up and x.dtype == torch.bfloat16 and out_dtype == torch.bfloat16 and M > self.tc_max_rows and K_ % 8 == 0
+                and w_gate_up.dim() == 2 and w_gate_up.shape[0] % 16 == 0 and w_gate_up.shape[1] == K_ and x.is_contiguous()
+                and w_gate_up.is_contiguous() and w_gate_up.dtype == torch.bfloat16):
+            I = w_gate_up.shape[0] // 2
+            out = torch.empty((M, I), dtype=torch.bfloat16, device=x.device)
+            self._check(self.lib.llmie_gateup_silu_tc(_ptr(x), _ptr(w_gate_up), _ptr(out), M, I, K_, self.num_sms, _ptr(self._errors(x.device)),
+                                                      self._stream()), "gate_up_act (tcgen05)")
+            return out
+        return self.silu_mul(self.linear(x, w_gate_up, transient=True), out_dtype)
 
     def silu_mul(self, gu, out_dtype=None):
         """``silu(gate) * up`` of a fused gate/up projection ``[rows, 2 I]`` (gate first); a transient float32 input is consumed and cleared."""

@@ -14,7 +14,8 @@ class GatedMLP(FeedForward):
     """``down(act(gate(x)) * up(x))`` without biases (src/miniserve/model.py:164-165).
 
     ``gate`` and ``up`` are kept as one matrix ``[2 * intermediate, hidden]`` (gate rows first) so a
-    step multiplies once; the activation and the product are one kernel over its output.
+    step multiplies once; the activation and the product of the two halves are the epilogue of that product
+    (prompt portions) or one kernel over its float32 sums (decode steps): ``gate_up_act`` of the kernels object decides.
     """
 
     graph_safe = True
@@ -35,5 +36,4 @@ class GatedMLP(FeedForward):
 
     def forward(self, ctx, h, residual):
         K = ctx.K
-        gu = K.linear(h, self.w_gate_up, transient=True)
-        K.linear(K.silu_mul(gu, ctx.dtype), self.w_down, add_to=residual)
+        K.linear(K.gate_up_act(h, self.w_gate_up, ctx.dtype), self.w_down, add_to=residual)

@@ -228,6 +228,33 @@ def test_silu_mul(K, dtype):
         close(K.silu_mul(gu.cuda()), REF.silu_mul(gu), tol(dtype, 1e-6, 8e-3))
 
 
+@pytest.mark.parametrize("M,H,I", [
+    (2048, 896, 4864),     # the bench's prompt: 16 x 38 tiles on a persistent grid
+    (129, 96, 200),        # one row more than a tile; inner size and width ragged
+    (300, 200, 328),
+    (513, 1536, 8960),     # the 1.5B model's widths
+    (1000, 72, 64),        # fewer output columns than a tile is wide
+])
+def test_gate_up_act_tcgen05(K, M, H, I):
+    """The gate/up product of prompt portions with silu(gate) * up as its epilogue (one tcgen05 kernel, the float32 sums stay
+    in tensor memory) against product and activation one after the other in 32-bit."""
+    g = torch.Generator().manual_seed(60)
+    x = torch.randn(M, H, generator=g).to(torch.bfloat16)
+    w = (torch.randn(2 * I, H, generator=g) / math.sqrt(H) * 2).to(torch.bfloat16)
+    gu = x.float() @ w.float().T
+    want = torch.nn.functional.silu(gu[:, :I]) * gu[:, I:]
+    before = K.launches
+    for _ in range(2):
+        got = K.gate_up_act(x.cuda(), w.cuda())
+        K.check_device_errors()
+        assert got.dtype == torch.bfloat16 and tuple(got.shape) == (M, I)
+        close(got, want, 8e-3)
+    assert K.launches - before == 2   # one kernel per call
+    small = K.gate_up_act(x[:5].contiguous().cuda(), w.cuda())   # a decode-sized batch: product into float32 sums, then the activation kernel
+    close(small, want[:5], 8e-3)
+    assert K._acc.abs().sum().item() == 0
+
+
 @pytest.mark.parametrize("V", [17, 320, 151936])
 def test_argmax(K, V):
     g = torch.Generator().manual_seed(6)

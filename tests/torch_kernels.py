@@ -108,6 +108,9 @@ class TorchKernels:
                 out[t, h] = pr @ v[:, h // rep]
         return out.reshape(N, num_heads * d).to(qkv.dtype)
 
+    def gate_up_act(self, x, w_gate_up, out_dtype=None):
+        return self.silu_mul(self.linear(x, w_gate_up, out_dtype=torch.float32)).to(out_dtype or x.dtype)
+
     def silu_mul(self, gu, out_dtype=None):
         i = gu.shape[1] // 2
         g, u = gu[:, :i].float(), gu[:, i:].float()
