@@ -234,10 +234,15 @@ def test_silu_mul(K, dtype):
     (300, 200, 328),
     (513, 1536, 8960),     # the 1.5B model's widths
     (1000, 72, 64),        # fewer output columns than a tile is wide
+    (385, 128, 136),       # four tiles of rows, the last of one row: its partner in the pair has nothing to store
 ])
-def test_gate_up_act_tcgen05(K, M, H, I):
+@pytest.mark.parametrize("cluster", [True, False])
+def test_gate_up_act_tcgen05(K, monkeypatch, cluster, M, H, I):
     """The gate/up product of prompt portions with silu(gate) * up as its epilogue (one tcgen05 kernel, the float32 sums stay
     in tensor memory) against product and activation one after the other in 32-bit."""
+    if cluster and K._gate_up_cluster is None:
+        pytest.skip("the library was built without the optional cluster kernel")
+    monkeypatch.setattr(K, "use_cluster_gate_up", cluster)
     g = torch.Generator().manual_seed(60)
     x = torch.randn(M, H, generator=g).to(torch.bfloat16)
     w = (torch.randn(2 * I, H, generator=g) / math.sqrt(H) * 2).to(torch.bfloat16)
