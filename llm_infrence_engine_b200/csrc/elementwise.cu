@@ -46,6 +46,26 @@ LLMIE_API int llmie_feed_tokens(int* ids, const int* src, const int* previous, i
 }
 
 // ------------------------------------------------------------------------------------------------
+// Fixed-size per-request state starts at zero: state[slots[r], :] = 0 for every request r of the step whose first token of
+// this step is the first of the request (position 0). Decided on the device from the step's own arrays, so the step can be
+// replayed from a graph. One block per request.
+__global__ void zero_fresh_state_kernel(float* __restrict__ state, long long row_floats, const int* __restrict__ slots,
+                                        const int* __restrict__ starts, const int* __restrict__ positions) {
+    pdl_trigger();
+    pdl_wait();
+    const int r = blockIdx.x;
+    if (positions[starts[r]] != 0) return;
+    float* row = state + (long long)slots[r] * row_floats;
+    for (long long i = threadIdx.x; i < row_floats; i += blockDim.x) row[i] = 0.f;
+}
+
+LLMIE_API int llmie_zero_fresh_state(float* state, long long row_floats, const int* slots, const int* starts, const int* positions,
+                                     int num_seqs, cudaStream_t s) {
+    if (num_seqs <= 0 || row_floats <= 0) return 0;
+    return launch_kernel(zero_fresh_state_kernel, dim3(num_seqs), dim3(128), 0, s, state, row_floats, slots, starts, positions);
+}
+
+// ------------------------------------------------------------------------------------------------
 // cos/sin[n, j] of the angle float(position[n]) * inv_freq[j], all in 32-bit
 __global__ void rope_tables_kernel(const int* __restrict__ pos, const float* __restrict__ inv_freq, float* __restrict__ cos_out,
                                    float* __restrict__ sin_out, int N, int half) {

@@ -71,7 +71,7 @@ class CudaKernels:
         self._retired_acc: list = []   # accumulation buffers that were outgrown: captured graphs may still add into and clear them
         self._sms: dict = {}
         self.last_attention_plan = (1, False)   # (key slices, merged as a cluster) of the last tensor-core attention launch
-        for fn in ("llmie_embed", "llmie_feed_tokens", "llmie_rope_tables", "llmie_add_rmsnorm", "llmie_rope_kv_write", "llmie_silu_mul",
+        for fn in ("llmie_embed", "llmie_feed_tokens", "llmie_zero_fresh_state", "llmie_rope_tables", "llmie_add_rmsnorm", "llmie_rope_kv_write", "llmie_silu_mul",
                    "llmie_gemm_simt", "llmie_gemm_tc", "llmie_gateup_silu_tc", "llmie_qkv_rope_tc", "llmie_add_into", "llmie_attn_plan", "llmie_attn_tc_plan", "llmie_paged_attention_mma", "llmie_paged_attention_mma_acc", "llmie_paged_attention_tc", "llmie_paged_attention_f32", "llmie_paged_attention_bf16", "llmie_argmax", "llmie_sample"):
             getattr(self.lib, fn).restype = ctypes.c_int
         try:   # an optional source file: the library also builds without it
@@ -151,6 +151,19 @@ class CudaKernels:
             raise KernelError("feed_tokens: one source row per token is needed")
         self._check(self.lib.llmie_feed_tokens(_ptr(token_ids), _ptr(source_rows), _ptr(previous_tokens), token_ids.shape[0],
                                                self._stream()), "feed_tokens")
+
+    def zero_fresh_state(self, state, seq_slots, seq_starts, positions):
+        """``state[seq_slots[r]] = 0`` for every request ``r`` of the step whose rows begin at position 0 (its first portion, or
+        a recomputation): fixed-size state of a request starts from zero. Decided on the device: a captured step does it too."""
+        self._need(state, "state", torch.float32)
+        for name, t in (("seq_slots", seq_slots), ("seq_starts", seq_starts), ("positions", positions)):
+            self._need(t, name, torch.int32, 1)
+        R = seq_slots.shape[0]
+        if seq_starts.shape[0] < R:
+            raise KernelError("zero_fresh_state: one start per request is needed")
+        if R and state.dim() >= 1 and state.shape[0]:
+            self._check(self.lib.llmie_zero_fresh_state(_ptr(state), ctypes.c_longlong(state.numel() // state.shape[0]), _ptr(seq_slots),
+                                                        _ptr(seq_starts), _ptr(positions), R, self._stream()), "zero_fresh_state")
 
     def rope_tables(self, positions, inv_freq):
         self._need(positions, "positions", torch.int32, 1)

@@ -26,7 +26,7 @@ from typing import Dict, List, Optional, Sequence
 
 import torch
 
-from .step import StateBinding, StepContext, StepEntry, step_layout
+from .step import StepContext, StepEntry, step_layout
 
 
 def bucket_sizes(max_batch: int) -> List[int]:
@@ -55,8 +55,7 @@ class _Captured:
 class DecodeGraphs:
     def __init__(self, runner):
         self.runner = runner
-        self.usable = runner.device.type == "cuda" and all(getattr(p, "graph_safe", False) for p in runner.spec.parts()) \
-            and not any(isinstance(b, StateBinding) for b in runner.bindings)
+        self.usable = runner.device.type == "cuda" and all(getattr(p, "graph_safe", False) for p in runner.spec.parts())
         self.buckets = bucket_sizes(runner.max_seqs)
         self.captured: Dict[int, _Captured] = {}
         self.shapes: "OrderedDict[tuple, _Captured]" = OrderedDict()  # captured prompt-portion steps, least recently used first
@@ -185,6 +184,7 @@ class DecodeGraphs:
         # padding values, so that warm-up and capture run on harmless inputs
         lay = step_layout(B, B, B, len(r.cache.groups))
         static_in[lay["tok_slot"][0]:lay["tok_slot"][0] + B] = r.max_seqs
+        static_in[lay["slots"][0]:lay["slots"][0] + B] = r.max_seqs   # padding requests own the spare row of every per-request array
         static_in[lay["starts"][0]:lay["starts"][0] + B + 1] = torch.arange(B + 1, dtype=torch.int32, device=r.device)
         static_in[lay["rows"][0]:lay["rows"][0] + B] = torch.arange(B, dtype=torch.int32, device=r.device)
         static_in[lay["feed"][0]:lay["feed"][0] + B] = -1

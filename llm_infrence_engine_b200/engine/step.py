@@ -49,7 +49,7 @@ class PagedKVBinding:
 class StateBinding:
     """What a mixer with fixed-size state gets: ``state[slot]`` is the request's own, zero at its first token."""
 
-    state: torch.Tensor  # [max_seqs, *shape], float32
+    state: torch.Tensor  # [max_seqs + 1, *shape], float32 (the last row belongs to the padding rows of a captured step)
     write: bool = True
 
 
@@ -115,7 +115,7 @@ class ModelRunner:
                 self.bindings.append(PagedKVBinding(group_of_entry[entry], k, v))
                 self.kv_bytes_per_token += 2 * cs.num_kv_heads * cs.head_dim * k.element_size()
             elif isinstance(cs, FixedStateSpec):
-                self.bindings.append(StateBinding(torch.zeros((max_seqs,) + tuple(cs.shape), dtype=torch.float32, device=self.device)))
+                self.bindings.append(StateBinding(torch.zeros((max_seqs + 1,) + tuple(cs.shape), dtype=torch.float32, device=self.device)))
             elif cs is None:
                 self.bindings.append(None)
             else:
@@ -183,7 +183,7 @@ class ModelRunner:
                     raise ValueError(f"request {e.req!r}: only a single token can come from the previous step's tokens")
                 feed[int(st)] = int(e.from_previous)
         parts = [ids, np.zeros(pad, np.int64), pos, np.zeros(pad, np.int64), tok_slot, np.full(pad, self.max_seqs, np.int64),
-                 np.asarray(slots, dtype=np.int64), np.zeros(pad, np.int64),
+                 np.asarray(slots, dtype=np.int64), np.full(pad, self.max_seqs, np.int64),
                  starts, np.arange(N, N + pad + 1, dtype=np.int64),
                  np.asarray(rows, dtype=np.int64), np.arange(N, N + pad, dtype=np.int64) if pad_to else np.zeros(0, np.int64),
                  feed]
@@ -241,7 +241,7 @@ class ModelRunner:
         pad = max(0, pad_to - R)
         zeros = [0] * pad
         feed = [-1 if e.from_previous is None else int(e.from_previous) for e in entries] + [-1] * pad
-        packed = (ids + zeros + ctxs + zeros + slots + [self.max_seqs] * pad + slots + zeros + list(range(R + pad + 1)) + rows
+        packed = (ids + zeros + ctxs + zeros + slots + [self.max_seqs] * pad + slots + [self.max_seqs] * pad + list(range(R + pad + 1)) + rows
                   + (list(range(R, R + pad)) if pad_to else []) + feed)
         for g in range(groups):
             for e, c in zip(entries, ctxs):
@@ -367,11 +367,6 @@ class ModelRunner:
                 return logits
         ctx, logit_rows = self.make_context(entries)
         self.feed(ctx, entries, previous_tokens)
-        fresh = [s for s, c in zip(ctx.seq_slot_list, ctx.seq_context) if c == 0]
-        if fresh:
-            for b in self.bindings:
-                if isinstance(b, StateBinding):
-                    b.state[fresh] = 0
         return self.forward(ctx, logit_rows)
 
     def forward(self, ctx: StepContext, logit_rows: torch.Tensor) -> Optional[torch.Tensor]:
@@ -387,6 +382,9 @@ class ModelRunner:
 
     def _forward(self, ctx: StepContext, logit_rows: torch.Tensor) -> Optional[torch.Tensor]:
         spec = self.spec
+        for b in self.bindings:   # a request's fixed-size state starts from zero: decided on the device, so captured steps do it too
+            if isinstance(b, StateBinding):
+                self.K.zero_fresh_state(b.state, ctx.seq_slots, ctx.seq_starts_dev, ctx.positions)
         residual = spec.embedding.forward(ctx)
         for call in spec.schedule:
             b = self.bindings[call.cache]

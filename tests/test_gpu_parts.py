@@ -177,7 +177,7 @@ def test_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
     prompts = {"a": random_prompt(90, 50, 1), "b": random_prompt(90, 23, 2)}
     want = {k: _toy_plain(cfg, w, p) for k, p in prompts.items()}
     rp = TraceReplayer(str(folder), "float32", 128)
-    assert rp.cache.groups == [] and rp.runner.bindings[0].state.shape == (4, 41)
+    assert rp.cache.groups == [] and rp.runner.bindings[0].state.shape == (4 + 1, 41)   # a row per request slot and one for padding rows
     # whole, then cut into portions and interleaved with the other request: the state must carry over exactly
     for k, p in prompts.items():
         got = rp.step({"step": 0, "entries": [{"id": k, "tokens": p, "want": list(range(len(p)))}], "end": [k]})
@@ -250,3 +250,235 @@ def test_running_order_is_data(tmp_path):
     got = torch.cat([rp.step({"step": 0, "entries": [{"id": "r", "tokens": p[:30], "want": list(range(30))}], "end": []}),
                      rp.step({"step": 1, "entries": [{"id": "r", "tokens": p[30:], "want": list(range(15))}], "end": ["r"]})])
     assert (got - want).abs().max() < 2e-5
+
+
+# ------------------------------------------------------------------------------------------------
+# Two more parts that only this file defines, put together with the package's own attention: a feed-forward that routes every
+# token to one of several small experts, and a position encoding of its own (rotary angles of positions scaled down by a
+# factor). Neither is a model of anyone's; they show what the interfaces take.
+def _routed_parts():
+    from llm_infrence_engine_b200.models import ModelSpec, sequential
+    from llm_infrence_engine_b200.parts import (FeedForward, OutputHead, PagedAttention, ParamSpec, PositionEncoding, PreNormBlock, RMSNorm,
+                                                Source, TokenEmbedding)
+
+    class ScaledRotary(PositionEncoding):
+        """Angles ``(position / factor) * theta^(-2j/d)``: the tables the package's attention asks for, made another way."""
+
+        graph_safe = True
+
+        def __init__(self, head_dim, theta, factor):
+            self.head_dim, self.theta, self.factor = head_dim, theta, factor
+
+        def key(self):
+            return ("scaled rotary", self.head_dim, self.theta, self.factor)
+
+        def tables(self, ctx):
+            inv = 1.0 / (self.theta ** (torch.arange(0, self.head_dim, 2, device=ctx.device).float() / self.head_dim))
+            ang = (ctx.positions.float() / self.factor)[:, None] * inv[None, :]
+            return ang.cos().contiguous(), ang.sin().contiguous()
+
+    class TopOneExperts(FeedForward):
+        """Router logits in 32-bit; every token goes to its best expert, whose output is weighted by the softmax probability."""
+
+        def __init__(self, hidden, inner, experts, prefix):
+            self.hidden, self.inner, self.experts, self.prefix = hidden, inner, experts, prefix
+
+        def params(self):
+            p = {"router": ParamSpec((Source(f"{self.prefix}.router.weight", (self.experts, self.hidden)),))}
+            for e in range(self.experts):
+                p[f"up{e}"] = ParamSpec((Source(f"{self.prefix}.experts.{e}.up.weight", (self.inner, self.hidden)),))
+                p[f"down{e}"] = ParamSpec((Source(f"{self.prefix}.experts.{e}.down.weight", (self.hidden, self.inner)),))
+            return p
+
+        def forward(self, ctx, h, residual):
+            K = ctx.K
+            probs = torch.softmax(K.linear(h, self.router, out_dtype=torch.float32), dim=-1)
+            best = probs.argmax(-1)
+            for e in range(self.experts):
+                rows = (best == e).nonzero().flatten()
+                if rows.numel() == 0:
+                    continue
+                x = h[rows].contiguous()
+                y = K.linear(torch.relu(K.linear(x, getattr(self, f"up{e}"))), getattr(self, f"down{e}"), out_dtype=torch.float32)
+                K.flush()
+                residual.index_add_(0, rows, y * probs[rows, e][:, None])
+
+    @dataclass(frozen=True)
+    class RoutedConfig:
+        vocab_size: int
+        hidden_size: int
+        num_hidden_layers: int
+        num_attention_heads: int
+        num_key_value_heads: int
+        head_dim: int
+        expert_size: int
+        num_experts: int
+        rope_factor: float
+        rms_norm_eps: float
+
+        @classmethod
+        def from_dict(cls, d):
+            return cls(*(d[f] for f in cls.__dataclass_fields__))
+
+    def build(cfg):
+        pos = ScaledRotary(cfg.head_dim, 10000.0, cfg.rope_factor)
+        emb = TokenEmbedding(cfg.vocab_size, cfg.hidden_size, "emb.weight")
+        layers = [PreNormBlock(RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, f"l{i}.n1.weight"),
+                               PagedAttention(cfg.hidden_size, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, pos,
+                                              f"l{i}.attn", bias=False),
+                               RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, f"l{i}.n2.weight"),
+                               TopOneExperts(cfg.hidden_size, cfg.expert_size, cfg.num_experts, f"l{i}.moe"))
+                  for i in range(cfg.num_hidden_layers)]
+        return ModelSpec(cfg, emb, layers, sequential(cfg.num_hidden_layers), RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, "out_norm.weight"),
+                         OutputHead(cfg.vocab_size, cfg.hidden_size, "head.weight"))
+
+    return RoutedConfig, build
+
+
+def _routed_plain(cfg, w, ids):
+    T, d, nq, nkv = len(ids), cfg["head_dim"], cfg["num_attention_heads"], cfg["num_key_value_heads"]
+    inv = 1.0 / (10000.0 ** (torch.arange(0, d, 2).float() / d))
+    ang = (torch.arange(T).float() / cfg["rope_factor"])[:, None] * inv[None, :]
+    cos, sin = torch.cat([ang.cos()] * 2, -1), torch.cat([ang.sin()] * 2, -1)
+    c = {"head_dim": d, "heads": nq, "kv_heads": nkv}
+    x = w["emb.weight"][torch.tensor(ids)]
+    for i in range(cfg["num_hidden_layers"]):
+        h = plain_rmsnorm(x, w[f"l{i}.n1.weight"], cfg["rms_norm_eps"])
+        names = {f"p.{n}_proj.weight": w[f"l{i}.attn.{n}_proj.weight"] for n in "qkvo"}
+        x = x + plain_attention(h, names, "p", c, cos, sin)
+        h = plain_rmsnorm(x, w[f"l{i}.n2.weight"], cfg["rms_norm_eps"])
+        probs = torch.softmax(h @ w[f"l{i}.moe.router.weight"].T, -1)
+        best = probs.argmax(-1)
+        y = torch.zeros_like(x)
+        for e in range(cfg["num_experts"]):
+            rows = best == e
+            y[rows] = (torch.relu(h[rows] @ w[f"l{i}.moe.experts.{e}.up.weight"].T) @ w[f"l{i}.moe.experts.{e}.down.weight"].T) * probs[rows, e][:, None]
+        x = x + y
+    return plain_rmsnorm(x, w["out_norm.weight"], cfg["rms_norm_eps"]) @ w["head.weight"].T
+
+
+@pytest.mark.parametrize("dtype,tol", [("float32", 2e-5), ("bfloat16", 4e-2)])
+def test_toy_routed_feed_forward_and_another_position_encoding(tmp_path, dtype, tol):
+    """A feed-forward with routing and a position encoding that the package does not have, defined above, combined with the
+    package's own attention, registered as an architecture and stepped whole, in portions and mixed, through the package's files."""
+    from llm_infrence_engine_b200.engine import TraceReplayer
+    from llm_infrence_engine_b200.models import register_architecture
+    from llm_infrence_engine_b200.weights import write_random_model
+
+    RoutedConfig, build = _routed_parts()
+    register_architecture("ToyRoutedLM", RoutedConfig, build, replace=True)
+    cfg = {"architectures": ["ToyRoutedLM"], "vocab_size": 75, "hidden_size": 48, "num_hidden_layers": 2, "num_attention_heads": 4,
+           "num_key_value_heads": 2, "head_dim": 16, "expert_size": 40, "num_experts": 3, "rope_factor": 4.0, "rms_norm_eps": 1e-5}
+    folder = write_random_model(cfg, tmp_path / "routed", 9, dtype, std=0.15)
+    _, w = plain_load(folder)
+    prompts = {"a": random_prompt(75, 60, 1), "b": random_prompt(75, 33, 2)}
+    want = {k: _routed_plain(cfg, w, p) for k, p in prompts.items()}
+    # every expert gets tokens, and the scaled positions matter
+    h0 = plain_rmsnorm(w["emb.weight"][torch.tensor(prompts["a"])], w["l0.n2.weight"], 1e-5)
+    assert len(set((h0 @ w["l0.moe.router.weight"].T).argmax(-1).tolist())) == 3
+    assert (want["a"] - _routed_plain(dict(cfg, rope_factor=1.0), w, prompts["a"])).abs().max() > 10 * tol
+    rp = TraceReplayer(str(folder), dtype, 128)
+    for k, p in prompts.items():
+        got = rp.step({"step": 0, "entries": [{"id": k, "tokens": p, "want": list(range(len(p)))}], "end": [k]})
+        bad = ((got - want[k]).abs().max(-1).values > tol * max(1.0, want[k].abs().max().item())).nonzero().flatten()
+        if dtype == "bfloat16":   # a token whose two best experts are nearly tied may go the other way: a few rows, not most
+            assert len(bad) <= 3, f"{k}: {len(bad)} rows differ"
+        else:
+            assert len(bad) == 0, f"{k}: first wrong position {int(bad[0])}"
+    if dtype == "float32":
+        got = {"a": [], "b": []}
+        cuts = {"a": [(0, 17), (17, 19), (19, 59), (59, 60)], "b": [(0, 1), (1, 2), (2, 33)]}
+        for step in range(4):
+            entries = [{"id": k, "tokens": prompts[k][lo:hi], "want": list(range(hi - lo))} for k in ("a", "b") if step < len(cuts[k])
+                       for lo, hi in [cuts[k][step]]]
+            out = rp.step({"step": step, "entries": entries, "end": [k for k in ("a", "b") if step == len(cuts[k]) - 1]})
+            o = 0
+            for e in entries:
+                got[e["id"]].append(out[o:o + len(e["tokens"])])
+                o += len(e["tokens"])
+        for k in prompts:
+            assert (torch.cat(got[k]) - want[k]).abs().max() < tol * max(1.0, want[k].abs().max().item())
+
+
+def test_stateful_mixer_decodes_from_cuda_graphs(tmp_path):
+    """A mixer with fixed-size state whose decode path only launches kernels (``graph_safe``): its decode steps are captured
+    and replayed like any other, the state of a slot that is used again starts from zero (the step function clears it on
+    the device), and the tokens are the plain ones."""
+    from llm_infrence_engine_b200.cache import FixedStateSpec
+    from llm_infrence_engine_b200.engine import Engine, Request
+    from llm_infrence_engine_b200.models import ModelSpec, register_architecture, sequential
+    from llm_infrence_engine_b200.parts import GatedMLP, Mixer, OutputHead, ParamSpec, PreNormBlock, RMSNorm, Source, TokenEmbedding
+    from llm_infrence_engine_b200.weights import write_random_model
+
+    class RunningSumMixer(Mixer):
+        """state = sum of the inputs so far; out_t = W (x_t + state_t / 8)."""
+
+        graph_safe = True
+
+        def __init__(self, hidden, prefix):
+            self.hidden, self.prefix, self.w = hidden, prefix, None
+
+        def params(self):
+            return {"w": ParamSpec((Source(f"{self.prefix}.w.weight", (self.hidden, self.hidden)),))}
+
+        def cache_spec(self):
+            return FixedStateSpec((self.hidden,))
+
+        def forward(self, ctx, h, cache, residual):
+            x = h.float()
+            if ctx.max_seq_len == 1:   # decode: one row per request, nothing is read on the host
+                slots = ctx.token_seq.long()
+                cache.state.index_add_(0, slots, x)
+                sums = cache.state[slots]
+            else:
+                sums = torch.empty_like(x)
+                for start, n, slot in zip(ctx.seq_starts, ctx.seq_lens, ctx.seq_slot_list):
+                    sums[start:start + n] = cache.state[slot] + x[start:start + n].cumsum(0)
+                    cache.state[slot] = sums[start + n - 1]
+            ctx.K.linear((x + sums / 8).to(h.dtype), self.w, add_to=residual)
+
+    @dataclass(frozen=True)
+    class Cfg:
+        vocab_size: int
+        hidden_size: int
+        intermediate_size: int
+        num_hidden_layers: int
+        rms_norm_eps: float
+
+        @classmethod
+        def from_dict(cls, d):
+            return cls(*(d[f] for f in cls.__dataclass_fields__))
+
+    def build(cfg):
+        emb = TokenEmbedding(cfg.vocab_size, cfg.hidden_size, "emb.weight")
+        layers = [PreNormBlock(RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, f"l{i}.n1.weight"), RunningSumMixer(cfg.hidden_size, f"l{i}.mix"),
+                               RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, f"l{i}.n2.weight"),
+                               GatedMLP(cfg.hidden_size, cfg.intermediate_size, f"l{i}.mlp")) for i in range(cfg.num_hidden_layers)]
+        return ModelSpec(cfg, emb, layers, sequential(cfg.num_hidden_layers), RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, "out_norm.weight"),
+                         OutputHead(cfg.vocab_size, cfg.hidden_size, "head.weight", tied_to=emb))
+
+    def plain(cfg, w, ids):
+        x = w["emb.weight"][torch.tensor(ids)]
+        for i in range(cfg["num_hidden_layers"]):
+            h = plain_rmsnorm(x, w[f"l{i}.n1.weight"], cfg["rms_norm_eps"])
+            x = x + (h + h.cumsum(0) / 8) @ w[f"l{i}.mix.w.weight"].T
+            x = x + plain_mlp(plain_rmsnorm(x, w[f"l{i}.n2.weight"], cfg["rms_norm_eps"]),
+                              {f"m.{n}_proj.weight": w[f"l{i}.mlp.{n}_proj.weight"] for n in ("gate", "up", "down")}, "m")
+        return plain_rmsnorm(x, w["out_norm.weight"], cfg["rms_norm_eps"]) @ w["emb.weight"].T
+
+    register_architecture("ToyRunningSumLM", Cfg, build, replace=True)
+    cfg = {"architectures": ["ToyRunningSumLM"], "vocab_size": 90, "hidden_size": 40, "intermediate_size": 56, "num_hidden_layers": 2,
+           "rms_norm_eps": 1e-5}
+    folder = write_random_model(cfg, tmp_path / "sum", 5, "float32", std=0.1)
+    _, w = plain_load(folder)
+    eng = Engine(str(folder), dtype="float32", max_seqs=2, max_len=64, max_num_batched_tokens=16, cuda_graphs=True)
+    assert eng.runner.graphs.usable
+    prompts = [random_prompt(90, n, 10 + n) for n in (20, 7, 13, 4, 9)]   # five requests through two slots: slots are used again
+    reqs = [eng.add_request(Request(p, max_new_tokens=6)) for p in prompts]
+    eng.run_until_idle()
+    for r, p in zip(reqs, prompts):
+        ref = []
+        for _ in range(6):
+            ref.append(int(plain(cfg, w, list(p) + ref)[-1].argmax()))
+        assert r.output_ids == ref
+    assert eng.runner.graphs.replays > 0

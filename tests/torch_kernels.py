@@ -27,6 +27,10 @@ class TorchKernels:
         take = source_rows >= 0
         token_ids[take] = previous_tokens[source_rows[take].long()]
 
+    def zero_fresh_state(self, state, seq_slots, seq_starts, positions):
+        fresh = positions[seq_starts[: seq_slots.shape[0]].long()] == 0
+        state[seq_slots[fresh].long()] = 0
+
     def rope_tables(self, positions, inv_freq):
         ang = positions.float()[:, None] * inv_freq.float()[None, :]
         return ang.cos(), ang.sin()
