@@ -28,12 +28,14 @@
 
 namespace {
 
-constexpr int BM = 128, BN = 128, BK = 64, STAGES = 4, UMMA_K = 16;
-constexpr int A_BYTES = BM * BK * 2, B_BYTES = 2 * BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int BM = 128, BK = 64, STAGES = 4, UMMA_K = 16;
+constexpr int A_BYTES = BM * BK * 2;
 constexpr int EPI_THREADS = 128, THREADS = 64 + EPI_THREADS;
 
+template <int BN>
 __global__ void __launch_bounds__(THREADS) gateup_silu_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
                                                                   bf16* __restrict__ out, int M, int I, int K, int* error_flag) {
+    constexpr int B_BYTES = 2 * BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;   // BN gate rows and BN up rows per K step
     extern __shared__ unsigned char raw[];
     unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~(uintptr_t)1023);
     uint64_t* full = reinterpret_cast<uint64_t*>(tiles + STAGES * STAGE_BYTES);
@@ -167,6 +169,39 @@ __global__ void __launch_bounds__(THREADS) gateup_silu_tc_kernel(const __grid_co
     if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "n"(512) : "memory");
 }
 
+// The tile's width in output columns: the one of 128, 112, 96, 80, 64 whose tiles fill the persistent grid's rounds best
+// (608 tiles of 128 columns on 148 blocks are 4.1 rounds, so five; 704 tiles of 112 columns are 4.8 rounds, also five, of
+// seven eighths the length).
+inline int best_tile_width(long long m_tiles, int I, int blocks) {
+    int best = 128;
+    long long best_cost = -1;
+    for (int bn = 128; bn >= 64; bn -= 16) {
+        const long long tiles = m_tiles * ((I + bn - 1) / bn);
+        const long long cost = ((tiles + blocks - 1) / blocks) * (bn + 8);   // + 8: what a tile costs whatever its width
+        if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = bn; }
+    }
+    return best;
+}
+
+template <int BN>
+int launch_gateup(const bf16* x, const bf16* w, bf16* out, int M, int I, int K, int num_blocks, int* error_flag, cudaStream_t s) {
+    CUtensorMap mx, mw;
+    int rc = tensor_map(x, M, K, BM, &mx);
+    if (rc) return rc;
+    rc = tensor_map(w, 2 * I, K, BN, &mw);
+    if (rc) return rc;
+    constexpr size_t smem = (size_t)STAGES * (A_BYTES + 2 * BN * BK * 2) + 1024 + 256;
+    static bool set = false;
+    if (!set) {
+        cudaError_t e = cudaFuncSetAttribute(gateup_silu_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        set = true;
+    }
+    const long long tiles = (long long)((M + BM - 1) / BM) * ((I + BN - 1) / BN);
+    const int grid = (int)(tiles < num_blocks ? tiles : num_blocks);
+    return launch_kernel(gateup_silu_tc_kernel<BN>, dim3(grid), dim3(THREADS), smem, s, mx, mw, out, M, I, K, error_flag);
+}
+
 }  // namespace
 
 // x [M, K] and w [2 I, K] bfloat16 row-major (K and I multiples of 8, bases 16-byte aligned), out bfloat16 [M, I].
@@ -176,19 +211,11 @@ LLMIE_API int llmie_gateup_silu_tc(const bf16* x, const bf16* w, bf16* out, int 
     if (M <= 0 || I <= 0) return 0;
     if (K <= 0 || K % 8 || I % 8 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15) || ((uintptr_t)out & 15) || !error_flag || num_blocks < 1)
         return LLMIE_ERR_BAD_ARGUMENT;
-    CUtensorMap mx, mw;
-    int rc = tensor_map(x, M, K, BM, &mx);
-    if (rc) return rc;
-    rc = tensor_map(w, 2 * I, K, BN, &mw);
-    if (rc) return rc;
-    constexpr size_t smem = (size_t)STAGES * STAGE_BYTES + 1024 + 256;
-    static bool set = false;
-    if (!set) {
-        cudaError_t e = cudaFuncSetAttribute(gateup_silu_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return (int)e;
-        set = true;
+    switch (best_tile_width((M + BM - 1) / BM, I, num_blocks)) {
+        case 112: return launch_gateup<112>(x, w, out, M, I, K, num_blocks, error_flag, s);
+        case 96: return launch_gateup<96>(x, w, out, M, I, K, num_blocks, error_flag, s);
+        case 80: return launch_gateup<80>(x, w, out, M, I, K, num_blocks, error_flag, s);
+        case 64: return launch_gateup<64>(x, w, out, M, I, K, num_blocks, error_flag, s);
+        default: return launch_gateup<128>(x, w, out, M, I, K, num_blocks, error_flag, s);
     }
-    const long long tiles = (long long)((M + BM - 1) / BM) * ((I + BN - 1) / BN);
-    const int grid = (int)(tiles < num_blocks ? tiles : num_blocks);
-    return launch_kernel(gateup_silu_tc_kernel, dim3(grid), dim3(THREADS), smem, s, mx, mw, out, M, I, K, error_flag);
 }

@@ -18,8 +18,8 @@
 
 namespace {
 
-constexpr int BM = 128, BN = 128, BK = 64, STAGES = 4, UMMA_K = 16;
-constexpr int A_BYTES = BM * BK * 2, B_BYTES = 2 * BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int BM = 128, BK = 64, STAGES = 4, UMMA_K = 16;
+constexpr int A_BYTES = BM * BK * 2;
 constexpr int EPI_THREADS = 128, THREADS = 64 + EPI_THREADS;
 
 __device__ __forceinline__ void tma_load_2d_multicast(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar, uint16_t mask) {
@@ -36,8 +36,10 @@ __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
 }
 
+template <int BN>
 __global__ void __launch_bounds__(THREADS) gateup_silu_tc_cluster_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
                                                                   bf16* __restrict__ out, int M, int I, int K, int* error_flag) {
+    constexpr int B_BYTES = 2 * BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;   // BN gate rows and BN up rows per K step
     extern __shared__ unsigned char raw[];
     unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~(uintptr_t)1023);
     uint64_t* full = reinterpret_cast<uint64_t*>(tiles + STAGES * STAGE_BYTES);
@@ -175,23 +177,28 @@ __global__ void __launch_bounds__(THREADS) gateup_silu_tc_cluster_kernel(const _
     cluster_sync_all();  // the other block may still send copies and arrivals here until it has come this far too
 }
 
-}  // namespace
+inline int best_tile_width(long long m_pairs, int I, int pairs_at_once) {
+    int best = 128;
+    long long best_cost = -1;
+    for (int bn = 128; bn >= 64; bn -= 16) {
+        const long long tiles = m_pairs * ((I + bn - 1) / bn);
+        const long long cost = ((tiles + pairs_at_once - 1) / pairs_at_once) * (bn + 8);
+        if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = bn; }
+    }
+    return best;
+}
 
-// As llmie_gateup_silu_tc; num_blocks is rounded down to an even number (clusters of two blocks).
-LLMIE_API int llmie_gateup_silu_tc_cluster(const bf16* x, const bf16* w, bf16* out, int M, int I, int K, int num_blocks, int* error_flag,
-                                           cudaStream_t s) {
-    if (M <= 0 || I <= 0) return 0;
-    if (K <= 0 || K % 8 || I % 8 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15) || ((uintptr_t)out & 15) || !error_flag || num_blocks < 2)
-        return LLMIE_ERR_BAD_ARGUMENT;
+template <int BN>
+int launch_gateup_cluster(const bf16* x, const bf16* w, bf16* out, int M, int I, int K, int num_blocks, int* error_flag, cudaStream_t s) {
     CUtensorMap mx, mw;
     int rc = tensor_map(x, M, K, BM, &mx);
     if (rc) return rc;
     rc = tensor_map(w, 2 * I, K, BN, &mw);
     if (rc) return rc;
-    constexpr size_t smem = (size_t)STAGES * STAGE_BYTES + 1024 + 256;
+    constexpr size_t smem = (size_t)STAGES * (A_BYTES + 2 * BN * BK * 2) + 1024 + 256;
     static bool set = false;
     if (!set) {
-        cudaError_t e = cudaFuncSetAttribute(gateup_silu_tc_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(gateup_silu_tc_cluster_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         set = true;
     }
@@ -211,5 +218,22 @@ LLMIE_API int llmie_gateup_silu_tc_cluster(const bf16* x, const bf16* w, bf16* o
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = llmie_pdl_flag ? 2 : 1;
-    return (int)cudaLaunchKernelEx(&cfg, gateup_silu_tc_cluster_kernel, mx, mw, out, M, I, K, error_flag);
+    return (int)cudaLaunchKernelEx(&cfg, gateup_silu_tc_cluster_kernel<BN>, mx, mw, out, M, I, K, error_flag);
+}
+
+}  // namespace
+
+// As llmie_gateup_silu_tc; num_blocks is rounded down to an even number (clusters of two blocks).
+LLMIE_API int llmie_gateup_silu_tc_cluster(const bf16* x, const bf16* w, bf16* out, int M, int I, int K, int num_blocks, int* error_flag,
+                                           cudaStream_t s) {
+    if (M <= 0 || I <= 0) return 0;
+    if (K <= 0 || K % 8 || I % 8 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15) || ((uintptr_t)out & 15) || !error_flag || num_blocks < 2)
+        return LLMIE_ERR_BAD_ARGUMENT;
+    switch (best_tile_width(((M + BM - 1) / BM + 1) / 2, I, num_blocks / 2)) {
+        case 112: return launch_gateup_cluster<112>(x, w, out, M, I, K, num_blocks, error_flag, s);
+        case 96: return launch_gateup_cluster<96>(x, w, out, M, I, K, num_blocks, error_flag, s);
+        case 80: return launch_gateup_cluster<80>(x, w, out, M, I, K, num_blocks, error_flag, s);
+        case 64: return launch_gateup_cluster<64>(x, w, out, M, I, K, num_blocks, error_flag, s);
+        default: return launch_gateup_cluster<128>(x, w, out, M, I, K, num_blocks, error_flag, s);
+    }
 }

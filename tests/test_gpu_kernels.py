@@ -235,6 +235,8 @@ def test_silu_mul(K, dtype):
     (513, 1536, 8960),     # the 1.5B model's widths
     (1000, 72, 64),        # fewer output columns than a tile is wide
     (385, 128, 136),       # four tiles of rows, the last of one row: its partner in the pair has nothing to store
+    (512, 64, 4736),       # 4 x 37 tiles of 128 columns are exactly one round of 148 blocks: the widest tile is chosen
+    (512, 64, 3552),       # ... and here tiles of 96 columns are
 ])
 @pytest.mark.parametrize("cluster", [True, False])
 def test_gate_up_act_tcgen05(K, monkeypatch, cluster, M, H, I):
