@@ -67,7 +67,10 @@ class CudaKernels:
         self._error_flag: Optional[torch.Tensor] = None
         self._acc_qkv: Optional[torch.Tensor] = None   # float32 sums of a decode step's q/k/v product, read by the attention kernel
         self._dirty_qkv: Optional[torch.Tensor] = None  # those sums while they still wait to be cleared
-        self.fuse_decode_rope = True   # decode steps: bias, rotation and cache write happen inside the attention kernel
+        self.fuse_decode_rope = True   # decode steps: bias, rotation and cache write happen inside the attention kernel ...
+        # ... for heads of 64: 2 to 7 % of a step. The kernel also takes heads of 128, but there it measured 3 % slower at
+        # batch 1 and even beyond (a lane then finishes twice as many elements before its first MMA)
+        self.fuse_decode_rope_head_dims = (64,)
         self._retired_acc: list = []   # accumulation buffers that were outgrown: captured graphs may still add into and clear them
         self._sms: dict = {}
         self.last_attention_plan = (1, False)   # (key slices, merged as a cluster) of the last tensor-core attention launch
@@ -596,7 +599,7 @@ class CudaKernels:
                       num_kv_heads, head_dim, page_size, scale, window, max_context, batch=None, write_kv=True, out_dtype=None):
         """The fused q/k/v projection of the step's rows (bias, rotation, cache write) and their attention over the pages.
 
-        Decode steps in bfloat16 (one row per request, heads of 64 or 128, at most 8 query heads per key/value head) take two
+        Decode steps in bfloat16 (one row per request, heads of 64, at most 8 query heads per key/value head) take two
         kernels: the small-batch tensor-core product, whose split-K blocks add into float32 sums, and the attention, which
         adds the bias, rotates the queries in its registers and lets the one warp that owns a token's own position finish its
         key and value, put them into its chunk of keys and write them to the cache. Everything else is ``qkv_rope`` followed
@@ -605,7 +608,7 @@ class CudaKernels:
         group = num_heads // max(num_kv_heads, 1)
         width = (num_heads + 2 * num_kv_heads) * head_dim
         if (self.fuse_decode_rope and self.use_mma_attention and self.use_tc_gemm and batch is not None and batch.max_seq_len == 1
-                and x.dtype == torch.bfloat16 and (out_dtype or x.dtype) == torch.bfloat16 and head_dim in (64, 128) and group <= 8
+                and x.dtype == torch.bfloat16 and (out_dtype or x.dtype) == torch.bfloat16 and head_dim in self.fuse_decode_rope_head_dims and group <= 8
                 and num_heads % max(num_kv_heads, 1) == 0 and M <= self.tc_max_rows and K_ % 8 == 0 and tuple(w.shape) == (width, K_)
                 and x.is_contiguous() and w.is_contiguous()):
             self._need(cos, "cos", torch.float32, 2)

@@ -398,6 +398,7 @@ def test_qkv_attention_of_a_decode_step(K, monkeypatch, cluster, nq, nkv, d, ps,
     the token's key and value into the cache, against product, rotation kernel and attention one after the other in plain
     torch. The tokens' own cache slots (and everything behind them) hold NaN beforehand: nothing stale may be read."""
     monkeypatch.setattr(K, "cluster_merge", cluster)
+    monkeypatch.setattr(K, "fuse_decode_rope_head_dims", (64, 128))   # serving fuses heads of 64 only (measured); the kernel takes both
     g = torch.Generator().manual_seed(50)
     B = len(lens)
     qlens = [1] * B
