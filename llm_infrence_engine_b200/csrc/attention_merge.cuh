@@ -41,6 +41,84 @@ __device__ __forceinline__ void finish_tile(const Params& p, const float* row_m,
     }
     __syncthreads();
     if (!*flag_smem) return;
+    if constexpr (ROWS * D / 4 > THREADS) {
+        // A tile of prompt rows, cut into a few slices: many steps per thread and few threads, so what a step costs in
+        // instructions counts as much as the trips to memory. The block's own slice is still in shared memory; the first
+        // steps' loads of the other slices leave at once, and while they travel one thread per row makes the slices' weights
+        // e^(m_s - M) / L from the rows' (max, sum) pairs. A step is then four loads' worth of multiply-adds and a store.
+        constexpr int STEPS = 4, OTHERS = 3;
+        if (num_splits <= OTHERS + 1) {
+            const int n = nrows * D;
+            float4 a[STEPS][OTHERS];
+            auto fetch = [&](int i0) {
+#pragma unroll
+                for (int u = 0; u < STEPS; ++u) {
+                    const int i = i0 + u * THREADS * 4;
+#pragma unroll
+                    for (int k = 0; k < OTHERS; ++k) {
+                        const int s = k < split ? k : k + 1;  // the slices that are not this block's
+                        if (i < n && s < num_splits)
+                            a[u][k] = __ldcg(reinterpret_cast<const float4*>(p.part_o + (part_base + s * part_stride) * ROWS * D + i));
+                    }
+                }
+            };
+            auto combine = [&](int i0) {
+#pragma unroll
+                for (int u = 0; u < STEPS; ++u) {
+                    const int i = i0 + u * THREADS * 4;
+                    if (i >= n) continue;
+                    const int r = i / D, dim = i % D;
+                    const float w_own = sums[r];
+                    const float4 own = *reinterpret_cast<const float4*>(row_o + i);
+                    float4 O = make_float4(own.x * w_own, own.y * w_own, own.z * w_own, own.w * w_own);
+#pragma unroll
+                    for (int k = 0; k < OTHERS; ++k) {
+                        if (k + 1 < num_splits) {
+                            const float w = sums[(k + 1) * nrows + r];
+                            O.x = fmaf(a[u][k].x, w, O.x); O.y = fmaf(a[u][k].y, w, O.y); O.z = fmaf(a[u][k].z, w, O.z); O.w = fmaf(a[u][k].w, w, O.w);
+                        }
+                    }
+                    const __nv_bfloat162 lo = __floats2bfloat162_rn(O.x, O.y), hi = __floats2bfloat162_rn(O.z, O.w);
+                    uint2 packed;
+                    packed.x = *reinterpret_cast<const uint32_t*>(&lo);
+                    packed.y = *reinterpret_cast<const uint32_t*>(&hi);
+                    *reinterpret_cast<uint2*>(p.out + (size_t)(n0 + r / G) * p.nq * D + (size_t)(kvh * G + r % G) * D + dim) = packed;
+                }
+            };
+            fetch(tid * 4);
+            for (int r = tid; r < nrows; r += THREADS) {
+                float2 ml[OTHERS];
+                float M = row_m[r];
+#pragma unroll
+                for (int k = 0; k < OTHERS; ++k) {
+                    const int s = k < split ? k : k + 1;
+                    ml[k] = make_float2(-INFINITY, 0.f);
+                    if (s < num_splits) ml[k] = __ldcg(reinterpret_cast<const float2*>(p.part_ml + (part_base + s * part_stride) * ROWS * 2 + 2 * r));
+                    M = fmaxf(M, ml[k].x);
+                }
+                float w[OTHERS + 1];
+                w[0] = M > -INFINITY ? exp2f(row_m[r] - M) : 0.f;
+                float L = row_l[r] * w[0];
+#pragma unroll
+                for (int k = 0; k < OTHERS; ++k) {
+                    w[k + 1] = M > -INFINITY ? exp2f(ml[k].x - M) : 0.f;
+                    L = fmaf(ml[k].y, w[k + 1], L);
+                }
+                const float inv = L > 0.f ? 1.f / L : 0.f;
+#pragma unroll
+                for (int k = 0; k <= OTHERS; ++k)
+                    if (k < num_splits) sums[k * nrows + r] = w[k] * inv;  // [0] the block's own slice, [k + 1] the k-th other one
+            }
+            __syncthreads();
+            combine(tid * 4);
+            for (int i0 = tid * 4 + THREADS * 4 * STEPS; i0 < n; i0 += THREADS * 4 * STEPS) {
+                fetch(i0);
+                combine(i0);
+            }
+            if (tid == 0) p.counters[counter] = 0;  // ready for the next launch
+            return;
+        }
+    }
     // Last block of the tile. One trip to memory brings every slice's (max, sum) pair into shared memory (the block's own
     // row_m / row_l / row_o are not needed any more); from these each row's thread makes the slices' weights
     // e^(m_s - M) and 1 / L; then every output element is one weighted sum whose loads do not depend on each other.
@@ -65,30 +143,77 @@ __device__ __forceinline__ void finish_tile(const Params& p, const float* row_m,
     }
     __syncthreads();
     // four neighbouring outputs of a row per thread and step (16-byte loads that do not depend on each other)
-    for (int i = tid * 4; i < nrows * D; i += THREADS * 4) {
+    auto store4 = [&](int i, const float4& O) {
         const int r = i / D, dim = i % D;
-        float4 O = make_float4(0.f, 0.f, 0.f, 0.f);
-        // the slices in groups of GROUP whose loads all leave before the first of them is used: one trip to memory per group
-        constexpr int GROUP = 12;
-        for (int s0 = 0; s0 < num_splits; s0 += GROUP) {
-            float4 a[GROUP];
-#pragma unroll
-            for (int k = 0; k < GROUP; ++k)
-                if (s0 + k < num_splits) a[k] = __ldcg(reinterpret_cast<const float4*>(p.part_o + (part_base + (s0 + k) * part_stride) * ROWS * D + i));
-#pragma unroll
-            for (int k = 0; k < GROUP; ++k) {
-                if (s0 + k < num_splits) {
-                    const float w = wgt[(s0 + k) * nrows + r];
-                    O.x = fmaf(a[k].x, w, O.x); O.y = fmaf(a[k].y, w, O.y); O.z = fmaf(a[k].z, w, O.z); O.w = fmaf(a[k].w, w, O.w);
-                }
-            }
-        }
         const float inv = row_l[r];
         const __nv_bfloat162 lo = __floats2bfloat162_rn(O.x * inv, O.y * inv), hi = __floats2bfloat162_rn(O.z * inv, O.w * inv);
         uint2 packed;
         packed.x = *reinterpret_cast<const uint32_t*>(&lo);
         packed.y = *reinterpret_cast<const uint32_t*>(&hi);
         *reinterpret_cast<uint2*>(p.out + (size_t)(n0 + r / G) * p.nq * D + (size_t)(kvh * G + r % G) * D + dim) = packed;
+    };
+    if constexpr (ROWS * D / 4 <= THREADS) {
+        // at most one step per thread (a decode tile): the slices in groups of GROUP whose loads all leave before the first of
+        // them is used, one trip to memory per group
+        for (int i = tid * 4; i < nrows * D; i += THREADS * 4) {
+            const int r = i / D;
+            float4 O = make_float4(0.f, 0.f, 0.f, 0.f);
+            constexpr int GROUP = 12;
+            for (int s0 = 0; s0 < num_splits; s0 += GROUP) {
+                float4 a[GROUP];
+#pragma unroll
+                for (int k = 0; k < GROUP; ++k)
+                    if (s0 + k < num_splits) a[k] = __ldcg(reinterpret_cast<const float4*>(p.part_o + (part_base + (s0 + k) * part_stride) * ROWS * D + i));
+#pragma unroll
+                for (int k = 0; k < GROUP; ++k) {
+                    if (s0 + k < num_splits) {
+                        const float w = wgt[(s0 + k) * nrows + r];
+                        O.x = fmaf(a[k].x, w, O.x); O.y = fmaf(a[k].y, w, O.y); O.z = fmaf(a[k].z, w, O.z); O.w = fmaf(a[k].w, w, O.w);
+                    }
+                }
+            }
+            store4(i, O);
+        }
+    } else {
+        // many steps per thread (a tile of prompt rows, few slices): four steps at a time, each with up to four slices, so that
+        // sixteen loads are on their way together instead of one step's after the other's (a trip to memory per step was most
+        // of what a slice cost)
+        constexpr int STEPS = 4, GROUP = 4;
+        for (int i0 = tid * 4; i0 < nrows * D; i0 += THREADS * 4 * STEPS) {
+            float4 O[STEPS];
+#pragma unroll
+            for (int u = 0; u < STEPS; ++u) O[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int s0 = 0; s0 < num_splits; s0 += GROUP) {
+                float4 a[STEPS][GROUP];
+#pragma unroll
+                for (int u = 0; u < STEPS; ++u) {
+                    const int i = i0 + u * THREADS * 4;
+#pragma unroll
+                    for (int k = 0; k < GROUP; ++k)
+                        if (i < nrows * D && s0 + k < num_splits)
+                            a[u][k] = __ldcg(reinterpret_cast<const float4*>(p.part_o + (part_base + (s0 + k) * part_stride) * ROWS * D + i));
+                }
+#pragma unroll
+                for (int u = 0; u < STEPS; ++u) {
+                    const int i = i0 + u * THREADS * 4;
+                    if (i >= nrows * D) continue;
+                    const int r = i / D;
+#pragma unroll
+                    for (int k = 0; k < GROUP; ++k) {
+                        if (s0 + k < num_splits) {
+                            const float w = wgt[(s0 + k) * nrows + r];
+                            O[u].x = fmaf(a[u][k].x, w, O[u].x); O[u].y = fmaf(a[u][k].y, w, O[u].y);
+                            O[u].z = fmaf(a[u][k].z, w, O[u].z); O[u].w = fmaf(a[u][k].w, w, O[u].w);
+                        }
+                    }
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < STEPS; ++u) {
+                const int i = i0 + u * THREADS * 4;
+                if (i < nrows * D) store4(i, O[u]);
+            }
+        }
     }
     if (tid == 0) p.counters[counter] = 0;  // ready for the next launch
 }
