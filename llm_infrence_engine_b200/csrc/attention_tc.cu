@@ -1,4 +1,4 @@
-// Paged attention for prompt portions on the 5th-generation tensor cores of sm_100a (head size 64, bfloat16).
+// Paged attention for prompt portions on the 5th-generation tensor cores of sm_100a (head sizes 64 and 128, bfloat16).
 //
 // One block owns a tile of up to 128 query rows: 128 / G consecutive tokens of one request times the G query
 // heads that share one key/value head. Row i of the tile is lane i of tensor memory and thread i of the block.
@@ -38,10 +38,21 @@
 
 namespace {
 
-constexpr int D = 64, BM = 128, BN = 64, STAGES = 3, THREADS = 192;  // STAGES: depth of the key ring and of the value ring
-constexpr int Q_BYTES = BM * D * 2, P_BYTES = BM * BN * 2, K_BYTES = BN * D * 2;
+constexpr int BM = 128, BN = 64, THREADS = 192;
+constexpr int P_BYTES = BM * BN * 2;
 constexpr int S_BUFS = 3;       // score buffers in tensor memory: the scores run up to two chunks ahead of the softmax
-constexpr int TMEM_COLS = 256;  // S0 [0, 64), S1 [64, 128), S2 [128, 192), O [192, 256)
+// What depends on the head size D (64 or 128). Operands lie in shared memory in blocks of 64 elements (128 bytes, the width
+// of the swizzle) along D: a tile of Q or of keys is D / 64 such blocks one behind the other, a chunk of values likewise
+// (its blocks are the MMA's N there). Heads of 64: two blocks per SM. Heads of 128: one (192 KB of tiles, 320 columns of
+// tensor memory), with a deeper ring.
+template <int D> struct Sizes {
+    static constexpr int ATOMS = D / 64;
+    static constexpr int STAGES = D == 64 ? 3 : 4;          // depth of the key ring and of the value ring
+    static constexpr int Q_BYTES = BM * D * 2, K_BYTES = BN * D * 2;
+    static constexpr int TMEM_COLS = D == 64 ? 256 : 512;   // S0 [0, 64), S1 [64, 128), S2 [128, 192), O [192, 192 + D)
+    static constexpr int BLOCKS_PER_SM = D == 64 ? 2 : 1;
+    static constexpr size_t SMEM = Q_BYTES + 2 * P_BYTES + 2 * STAGES * K_BYTES + 1024 + 256;
+};
 constexpr float RESCALE_AFTER = 8.f;  // log2: a row's reference lags its running maximum by at most this much
 constexpr float LOG2E = 1.4426950408889634f;
 
@@ -97,11 +108,12 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     return *reinterpret_cast<const uint32_t*>(&v);
 }
 
-// MN-major operand: [k][64 elements of 2 bytes] rows of 128 bytes, 128-byte swizzle, groups of 8 k-rows 1024 bytes apart.
-__device__ __forceinline__ uint64_t umma_desc_mn(uint32_t smem_addr) {
+// MN-major operand: [k][64 elements of 2 bytes] rows of 128 bytes, 128-byte swizzle, groups of 8 k-rows 1024 bytes apart;
+// blocks of 64 columns `block_bytes` apart.
+__device__ __forceinline__ uint64_t umma_desc_mn(uint32_t smem_addr, uint32_t block_bytes) {
     uint64_t d = 0;
     d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
-    d |= (uint64_t)(1024 >> 4) << 16;  // leading byte offset: between 64-element column blocks (one block here: not used)
+    d |= (uint64_t)(block_bytes >> 4) << 16;  // leading byte offset: between 64-element column blocks
     d |= (uint64_t)(1024 >> 4) << 32;  // stride byte offset: between groups of 8 k-rows
     d |= (uint64_t)1 << 46;
     d |= (uint64_t)2 << 61;
@@ -112,8 +124,11 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
 }
 
-__global__ void __launch_bounds__(THREADS, 2) attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap tmap_k,
-                                                                     const __grid_constant__ CUtensorMap tmap_v, const TcParams p) {
+template <int D>
+__global__ void __launch_bounds__(THREADS, Sizes<D>::BLOCKS_PER_SM) attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap tmap_k,
+                                                                                          const __grid_constant__ CUtensorMap tmap_v, const TcParams p) {
+    constexpr int ATOMS = Sizes<D>::ATOMS, STAGES = Sizes<D>::STAGES, Q_BYTES = Sizes<D>::Q_BYTES, K_BYTES = Sizes<D>::K_BYTES;
+    constexpr int TMEM_COLS = Sizes<D>::TMEM_COLS;
     extern __shared__ unsigned char raw[];
     unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~(uintptr_t)1023);
     unsigned char* q_s = base;
@@ -232,10 +247,12 @@ __global__ void __launch_bounds__(THREADS, 2) attn_tc_prefill_kernel(const __gri
             }
             ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
             if (!ok) break;
-            if (lane < boxes) {
-                if (keys) tma_load_2d(k_s + kst * K_BYTES + lane * p.box_rows * 128, &tmap_k, 0, row_k, k_full + kst);
-            } else if (lane < 2 * boxes) {
-                if (values) tma_load_2d(v_s + vst * K_BYTES + (lane - boxes) * p.box_rows * 128, &tmap_v, 0, row_v, v_full + vst);
+            // lane = (block of 64 dims) * boxes + box for the keys, the same again behind them for the values
+            const int atom = (lane >> box_shift) % ATOMS;
+            if (lane < boxes * ATOMS) {
+                if (keys) tma_load_2d(k_s + kst * K_BYTES + atom * (BN * 128) + my_box * p.box_rows * 128, &tmap_k, atom * 64, row_k, k_full + kst);
+            } else if (lane < 2 * boxes * ATOMS) {
+                if (values) tma_load_2d(v_s + vst * K_BYTES + atom * (BN * 128) + my_box * p.box_rows * 128, &tmap_v, atom * 64, row_v, v_full + vst);
             }
             __syncwarp();
             if (lane == 0) { if (keys) issued[0] = c + 1; if (values) issued[1] = c; }
@@ -246,11 +263,12 @@ __global__ void __launch_bounds__(THREADS, 2) attn_tc_prefill_kernel(const __gri
             // D float32, A and B bfloat16, M = 128, N = 64; for P V the B operand (values) is MN-major
             constexpr uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
             constexpr uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(D >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-            const uint64_t q_desc = umma_desc(smem_u32(q_s));
             auto issue_s = [&](int c) {
-                const uint64_t k_desc = umma_desc(smem_u32(k_s + (c % STAGES) * K_BYTES));
+                const uint32_t k_addr = smem_u32(k_s + (c % STAGES) * K_BYTES);
 #pragma unroll
-                for (int k = 0; k < D / 16; ++k) umma_bf16(tmem + (c % S_BUFS) * BN, q_desc + 2 * k, k_desc + 2 * k, idesc_s, k > 0 ? 1u : 0u);
+                for (int k = 0; k < D / 16; ++k)  // 16 dims per step: 32 bytes along a row, four steps per block of 64 dims
+                    umma_bf16(tmem + (c % S_BUFS) * BN, umma_desc(smem_u32(q_s) + (k / 4) * (BM * 128)) + 2 * (k % 4),
+                              umma_desc(k_addr + (k / 4) * (BN * 128)) + 2 * (k % 4), idesc_s, k > 0 ? 1u : 0u);
                 umma_commit(s_ready + c % S_BUFS);
                 umma_commit(k_empty + c % STAGES);
             };
@@ -302,7 +320,7 @@ __global__ void __launch_bounds__(THREADS, 2) attn_tc_prefill_kernel(const __gri
                 const uint64_t p_desc = umma_desc(smem_u32(p_s + (c & 1) * P_BYTES));
 #pragma unroll
                 for (int k = 0; k < BN / 16; ++k)  // 16 keys per step: 32 bytes along a row of P, 2048 bytes down the values
-                    umma_bf16(tmem + S_BUFS * BN, p_desc + 2 * k, umma_desc_mn(v_addr + k * 2048), idesc_o, (c > 0 || k > 0) ? 1u : 0u);
+                    umma_bf16(tmem + S_BUFS * BN, p_desc + 2 * k, umma_desc_mn(v_addr + k * 2048, BN * 128), idesc_o, (c > 0 || k > 0) ? 1u : 0u);
                 umma_commit(o_ready);
                 if (c == chunks - 1) umma_commit(o_done);
                 umma_commit(v_empty + c % STAGES);
@@ -318,9 +336,9 @@ __global__ void __launch_bounds__(THREADS, 2) attn_tc_prefill_kernel(const __gri
             // this thread's query row into the swizzled tile (zeros for rows beyond the tile)
             const uint4* src = reinterpret_cast<const uint4*>(p.q + (size_t)(n0 + tok) * p.q_stride + (size_t)(kvh * G + (row_ok ? row % G : 0)) * D);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
+            for (int j = 0; j < D / 8; ++j) {
                 const uint4 v = row_ok ? src[j] : make_uint4(0, 0, 0, 0);
-                *reinterpret_cast<uint4*>(q_s + row * 128 + ((j ^ (row & 7)) << 4)) = v;
+                *reinterpret_cast<uint4*>(q_s + (j / 8) * (BM * 128) + row * 128 + (((j % 8) ^ (row & 7)) << 4)) = v;
             }
             asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
             __syncwarp();
@@ -387,15 +405,18 @@ __global__ void __launch_bounds__(THREADS, 2) attn_tc_prefill_kernel(const __gri
                 ok = __all_sync(0xffffffffu, mbar_wait(o_ready, (c - 1) & 1, abort_flag, p.error_flag, 16));
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                uint32_t v[D];
+#pragma unroll 1
+                for (int part = 0; part < D; part += 64) {
+                    uint32_t v[64];
 #pragma unroll
-                for (int j = 0; j < D; j += 16) tmem_ld16(o_addr + j, v + j);
-                asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+                    for (int j = 0; j < 64; j += 16) tmem_ld16(o_addr + part + j, v + j);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
 #pragma unroll
-                for (int i = 0; i < D; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * corr);
+                    for (int i = 0; i < 64; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * corr);
 #pragma unroll
-                for (int j = 0; j < D; j += 16) tmem_st16(o_addr + j, v + j);
-                asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
+                    for (int j = 0; j < 64; j += 16) tmem_st16(o_addr + part + j, v + j);
+                    asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
+                }
             }
             // all 64 exponentials first, in place and independent of each other (the special-function unit is the narrow
             // place of this loop and must not wait for the sums and stores that follow)
@@ -430,52 +451,60 @@ __global__ void __launch_bounds__(THREADS, 2) attn_tc_prefill_kernel(const __gri
                 const int first_bad = hi - key0;
                 ok = __all_sync(0xffffffffu, mbar_wait(v_full + c % STAGES, (c / STAGES) & 1, abort_flag, p.error_flag, 18));  // the values have landed
                 if (!ok) break;
-                for (int i = tid; i < (BN - first_bad) * 8; i += BM)
-                    *reinterpret_cast<uint4*>(v_c + (first_bad + (i >> 3)) * 128 + ((i & 7) << 4)) = make_uint4(0, 0, 0, 0);
+                for (int i = tid; i < (BN - first_bad) * 8 * ATOMS; i += BM) {
+                    const int in_block = i % ((BN - first_bad) * 8);  // which 16 bytes of the bad rows of a block of 64 dims
+                    *reinterpret_cast<uint4*>(v_c + (i / ((BN - first_bad) * 8)) * (BN * 128) + (first_bad + (in_block >> 3)) * 128 + ((in_block & 7) << 4)) =
+                        make_uint4(0, 0, 0, 0);
+                }
             }
             asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // the tensor core reads shared memory through the async proxy
             asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
             __syncwarp();  // every lane's writes (and reads of S) are done and fenced: one arrival speaks for the warp
             if (lane == 0) mbar_arrive(p_ready + (c & 1));
         }
-        // the row's outputs, once: everything the tensor core has added up, relative to ref like the sum
-        float o[D];
-#pragma unroll
-        for (int i = 0; i < D; ++i) o[i] = 0.f;
+        // the row's outputs, once: everything the tensor core has added up, relative to ref like the sum; 64 at a time
         if (ok && chunks > 0) {
             ok = __all_sync(0xffffffffu, mbar_wait(o_done, 0, abort_flag, p.error_flag, 16));
-            if (ok) {
-                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                uint32_t v[D];
-#pragma unroll
-                for (int j = 0; j < D; j += 16) tmem_ld16(o_addr + j, v + j);
-                asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-#pragma unroll
-                for (int i = 0; i < D; ++i) o[i] = __uint_as_float(v[i]);
-            }
+            if (ok) asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
         }
-        if (ok && num_splits == 1) {
-            if (row_ok) {
-                const float inv = l > 0.f ? 1.f / l : 0.f;
-                uint4* dst = reinterpret_cast<uint4*>(p.out + (size_t)(n0 + tok) * p.nq * D + (size_t)(kvh * G + row % G) * D);
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    uint4 packed;
-                    packed.x = pack_bf16x2(o[8 * j] * inv, o[8 * j + 1] * inv); packed.y = pack_bf16x2(o[8 * j + 2] * inv, o[8 * j + 3] * inv);
-                    packed.z = pack_bf16x2(o[8 * j + 4] * inv, o[8 * j + 5] * inv); packed.w = pack_bf16x2(o[8 * j + 6] * inv, o[8 * j + 7] * inv);
-                    dst[j] = packed;
-                }
-            }
-        } else if (ok) {
-            // one slice of several: (max, sum, outputs) of the row go to shared memory (every product has been waited for and
-            // no copy is in flight: the tiles' space is free), from where the whole block hands them on below
-            float* fm = reinterpret_cast<float*>(p_s);
-            float* fl = fm + BM;
-            float* fo = fl + BM;
+        // one slice of several: (max, sum, outputs) of the row go to shared memory (every product has been waited for and no
+        // copy is in flight: the tiles' space is free), from where the whole block hands them on below
+        float* fm = reinterpret_cast<float*>(p_s);
+        float* fl = fm + BM;
+        float* fo = fl + BM;
+        if (ok && num_splits > 1) {
             fm[row] = ref;  // what the sum and the outputs are relative to
             fl[row] = l;
+        }
+        const float inv = l > 0.f ? 1.f / l : 0.f;
+#pragma unroll 1
+        for (int part = 0; part < D && ok; part += 64) {
+            float o[64];
 #pragma unroll
-            for (int i = 0; i < D; i += 4) *reinterpret_cast<float4*>(fo + row * D + i) = make_float4(o[i], o[i + 1], o[i + 2], o[i + 3]);
+            for (int i = 0; i < 64; ++i) o[i] = 0.f;
+            if (chunks > 0) {
+                uint32_t v[64];
+#pragma unroll
+                for (int j = 0; j < 64; j += 16) tmem_ld16(o_addr + part + j, v + j);
+                asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+                for (int i = 0; i < 64; ++i) o[i] = __uint_as_float(v[i]);
+            }
+            if (num_splits == 1) {
+                if (row_ok) {
+                    uint4* dst = reinterpret_cast<uint4*>(p.out + (size_t)(n0 + tok) * p.nq * D + (size_t)(kvh * G + row % G) * D + part);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        uint4 packed;
+                        packed.x = pack_bf16x2(o[8 * j] * inv, o[8 * j + 1] * inv); packed.y = pack_bf16x2(o[8 * j + 2] * inv, o[8 * j + 3] * inv);
+                        packed.z = pack_bf16x2(o[8 * j + 4] * inv, o[8 * j + 5] * inv); packed.w = pack_bf16x2(o[8 * j + 6] * inv, o[8 * j + 7] * inv);
+                        dst[j] = packed;
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 64; i += 4) *reinterpret_cast<float4*>(fo + row * D + part + i) = make_float4(o[i], o[i + 1], o[i + 2], o[i + 3]);
+            }
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
@@ -615,10 +644,10 @@ LLMIE_API int llmie_attn_tc_plan(const int* tile_info, int num_tiles, const int*
                          page_size < BN ? page_size : BN, capacity, fixed_splits, max_items, work, tmp);
 }
 
-// Attention of prompt portions over the paged cache on the tcgen05 tensor cores: head size 64, bfloat16, up to 128 rows
-// (tokens x heads of a group) per tile. page_size must be a multiple of 8 that divides 64 or is a multiple of 64. Pools:
-// [pages][nkv][page_size][64]. `work` is the plan that llmie_attn_tc_plan made for the step's num_tiles tiles, its positions,
-// this window and page size, with the same max_items. The slices of a tile meet in scratch_o [max_items * nkv * 128 * 64]
+// Attention of prompt portions over the paged cache on the tcgen05 tensor cores: head size d = 64 or 128, bfloat16, up to 128
+// rows (tokens x heads of a group) per tile. page_size must be a multiple of 8 that divides 64 or is a multiple of 64. Pools:
+// [pages][nkv][page_size][d]. `work` is the plan that llmie_attn_tc_plan made for the step's num_tiles tiles, its positions,
+// this window and page size, with the same max_items. The slices of a tile meet in scratch_o [max_items * nkv * 128 * d]
 // and scratch_ml [max_items * nkv * 128 * 2] floats; the block that finishes a tile last (counters [tiles * nkv], zero before and
 // after) merges them.
 LLMIE_API int llmie_paged_attention_tc(const bf16* q, int q_stride, const bf16* k_pool, const bf16* v_pool, long long pool_pages,
@@ -626,7 +655,7 @@ LLMIE_API int llmie_paged_attention_tc(const bf16* q, int q_stride, const bf16* 
                                        float* scratch_ml, int* counters, int nq, int nkv, int d, int page_size, float scale, int window,
                                        int* error_flag, cudaStream_t s) {
     if (num_tiles <= 0) return 0;
-    if (d != D || nkv <= 0 || nq % nkv || nq / nkv > BM || page_size <= 0 || page_size % 8 || q_stride % 8 ||
+    if ((d != 64 && d != 128) || nkv <= 0 || nq % nkv || nq / nkv > BM || page_size <= 0 || page_size % 8 || q_stride % 8 ||
         !(BN % page_size == 0 || page_size % BN == 0) || !error_flag || pool_pages <= 0 || ((uintptr_t)q & 15) ||
         ((uintptr_t)out & 15) || pool_pages * nkv * page_size > 0x7fffffffLL || !work || ((uintptr_t)work & 15) || max_items < num_tiles ||
         !scratch_o || !scratch_ml || !counters)
@@ -638,18 +667,20 @@ LLMIE_API int llmie_paged_attention_tc(const bf16* q, int q_stride, const bf16* 
     p.window = window; p.box_rows = page_size < BN ? page_size : BN; p.scale_log2 = scale * LOG2E;
     CUtensorMap mk, mv;
     const int rows = (int)(pool_pages * nkv * page_size);
-    int rc = tensor_map(k_pool, rows, D, p.box_rows, &mk);
+    int rc = tensor_map(k_pool, rows, d, p.box_rows, &mk);
     if (rc) return rc;
-    rc = tensor_map(v_pool, rows, D, p.box_rows, &mv);
+    rc = tensor_map(v_pool, rows, d, p.box_rows, &mv);
     if (rc) return rc;
-    constexpr size_t smem = Q_BYTES + 2 * P_BYTES + 2 * STAGES * K_BYTES + 1024 + 256;
-    static bool set = false;
-    if (!set) {
-        cudaError_t e = cudaFuncSetAttribute(attn_tc_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return (int)e;
-        set = true;
-    }
     const long long blocks = (long long)max_items * nkv;
     if (blocks > 0x7fffffffLL) return LLMIE_ERR_BAD_ARGUMENT;
-    return launch_kernel(attn_tc_prefill_kernel, dim3((unsigned)blocks), dim3(THREADS), smem, s, mk, mv, p);
+    static bool set[2] = {false, false};
+    auto launch = [&](auto kernel, size_t smem, int which) -> int {
+        if (!set[which]) {
+            cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return (int)e;
+            set[which] = true;
+        }
+        return launch_kernel(kernel, dim3((unsigned)blocks), dim3(THREADS), smem, s, mk, mv, p);
+    };
+    return d == 64 ? launch(attn_tc_prefill_kernel<64>, Sizes<64>::SMEM, 0) : launch(attn_tc_prefill_kernel<128>, Sizes<128>::SMEM, 1);
 }

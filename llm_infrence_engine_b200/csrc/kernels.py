@@ -52,7 +52,7 @@ class CudaKernels:
         self._attn_counters: Optional[torch.Tensor] = None
         self._retired: list = []
         self.use_mma_attention = True
-        self.use_tc_attention = True   # prompt portions of head size 64: scores and outputs through tcgen05 and tensor memory
+        self.use_tc_attention = True   # prompt portions of head size 64 or 128: scores and outputs through tcgen05 and tensor memory
         self.cluster_merge = True      # decode attention: the key slices of a token form a cluster and merge in shared memory
         self.use_tc_gemm = True
         self.use_cluster_gate_up = True  # ... by pairs of blocks that share their weight rows (TMA multicast within a cluster of two)
@@ -491,7 +491,7 @@ class CudaKernels:
                       page_size, scale, window, span, batch, num_splits):
         """The tcgen05 kernel for prompt portions, if it takes this case: returns ``out`` or None."""
         group = num_heads // num_kv_heads
-        if not (self.use_tc_attention and head_dim == 64 and batch.max_seq_len > 1 and group <= 128 and page_size % 8 == 0
+        if not (self.use_tc_attention and head_dim in (64, 128) and batch.max_seq_len > 1 and group <= 128 and page_size % 8 == 0
                 and (64 % page_size == 0 or page_size % 64 == 0) and (num_splits is None or 1 <= num_splits <= 16)):
             return None
         tiles, tile_info = self._tiles(batch, 128 // group, qkv.device)
@@ -499,9 +499,9 @@ class CudaKernels:
             return None
         # A tile's chunks run one after the other, about a microsecond each, and a prompt's last tiles have many times the
         # chunks of its first ones. The plan (made on the device from the step's positions, once per step) cuts the keys of
-        # long tiles into slices, as many pieces as fit on the device at once (two blocks per SM), and starts long pieces first.
+        # long tiles into slices, as many pieces as fit on the device at once, and starts long pieces first.
         fixed = int(num_splits or 0)
-        capacity = max(1, 2 * self.num_sms // num_kv_heads)
+        capacity = max(1, (2 if head_dim == 64 else 1) * self.num_sms // num_kv_heads)  # heads of 128: one block per SM
         # (tiles of up to 16 chunks are never cut: a slice costs about 8 chunks' time and is at least 8 chunks long)
         max_items = tiles * fixed if fixed else max(tiles, min(capacity, 16 * tiles)) if span > 16 * 64 else tiles
         key = ("tcgen05 attention plan", group, num_kv_heads, page_size, int(window), fixed)

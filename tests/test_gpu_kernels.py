@@ -440,22 +440,28 @@ def test_qkv_attention_of_a_decode_step(K, monkeypatch, cluster, nq, nkv, d, ps,
     assert K._attn_counters is None or K._attn_counters.abs().sum().item() == 0
 
 
-@pytest.mark.parametrize("nq,nkv,ps,lens,qlens,window", [
-    (14, 2, 16, [2048], [2048], 0),                       # the bench's prompt: 18 tokens x 7 heads per tile
-    (14, 2, 16, [3000], [40], 0),                         # a short portion far into a long request: few tiles, their keys in slices
-    (4, 1, 16, [1500, 700], [100, 5], 0),                 # slices, and a tile whose later slices are empty
-    (14, 2, 16, [300, 77, 500], [300, 1, 37], 0),        # a decode token and a late portion beside a prompt
-    (8, 8, 8, [700, 130], [700, 2], 0),                   # no grouping: 128 tokens per tile; pages of 8
-    (16, 1, 32, [257, 90], [257, 64], 0),                 # 16 heads on one key/value head
-    (6, 3, 64, [200, 1000], [200, 520], 48),              # window; a page is a whole chunk
-    (12, 4, 128, [640], [400], 0),                        # pages larger than a chunk
-    (5, 5, 16, [333], [333], 100),                        # window longer than a chunk
-    (3, 1, 16, [4500], [4500], 0),
+@pytest.mark.parametrize("nq,nkv,d,ps,lens,qlens,window", [
+    (14, 2, 64, 16, [2048], [2048], 0),                       # the bench's prompt: 18 tokens x 7 heads per tile
+    (14, 2, 64, 16, [3000], [40], 0),                         # a short portion far into a long request: few tiles, their keys in slices
+    (4, 1, 64, 16, [1500, 700], [100, 5], 0),                 # slices, and a tile whose later slices are empty
+    (14, 2, 64, 16, [300, 77, 500], [300, 1, 37], 0),        # a decode token and a late portion beside a prompt
+    (8, 8, 64, 8, [700, 130], [700, 2], 0),                   # no grouping: 128 tokens per tile; pages of 8
+    (16, 1, 64, 32, [257, 90], [257, 64], 0),                 # 16 heads on one key/value head
+    (6, 3, 64, 64, [200, 1000], [200, 520], 48),              # window; a page is a whole chunk
+    (12, 4, 64, 128, [640], [400], 0),                        # pages larger than a chunk
+    (5, 5, 64, 16, [333], [333], 100),                        # window longer than a chunk
+    (3, 1, 64, 16, [4500], [4500], 0),
+    (12, 2, 128, 16, [2048], [2048], 0),                      # heads of 128: two blocks of 64 dims per operand, one block per SM
+    (28, 4, 128, 16, [1500, 700], [100, 5], 0),               # 7 heads per group, slices, empty later slices
+    (4, 1, 128, 16, [3000], [40], 0),                         # few tiles far into a long request: many slices
+    (8, 8, 128, 8, [700, 130], [700, 2], 0),                  # pages of 8: all 32 lanes of the producer issue a box
+    (12, 4, 128, 128, [640], [400], 0),                       # pages larger than a chunk
+    (6, 3, 128, 64, [200, 1000], [200, 520], 48),             # window
+    (12, 2, 128, 16, [300, 77, 500], [300, 1, 37], 0),
 ])
-def test_paged_attention_tcgen05(K, monkeypatch, nq, nkv, ps, lens, qlens, window):
-    """Prompt portions of head size 64 through tcgen05 and tensor memory. Every slot of the cache that no visible key
+def test_paged_attention_tcgen05(K, monkeypatch, nq, nkv, d, ps, lens, qlens, window):
+    """Prompt portions of head size 64 or 128 through tcgen05 and tensor memory. Every slot of the cache that no visible key
     occupies holds NaN (free pages, the null page, the rest of each request's last page): nothing of it may reach a result."""
-    d = 64
     taken = []
     inner = K._attention_tc
     monkeypatch.setattr(K, "_attention_tc", lambda *a: (taken.append(inner(*a)), taken[-1])[1])
@@ -480,13 +486,14 @@ def test_paged_attention_tcgen05(K, monkeypatch, nq, nkv, ps, lens, qlens, windo
     assert K._attn_counters is None or K._attn_counters.abs().sum().item() == 0  # the slice counters are back at zero
 
 
+@pytest.mark.parametrize("d", [64, 128])
 @pytest.mark.parametrize("lens,qlens,splits", [([1500], [1500], None), ([1500, 900], [300, 64], None), ([1300], [40], 5)])
-def test_paged_attention_tcgen05_when_the_maximum_keeps_growing(K, lens, qlens, splits):
+def test_paged_attention_tcgen05_when_the_maximum_keeps_growing(K, d, lens, qlens, splits):
     """The tcgen05 kernel takes P relative to a reference that follows a row's running maximum only when it lags by more
     than 2^8, and then scales the row's outputs down in tensor memory. Here the scores of the even heads climb along the
     sequence (by about 55 powers of two over 1,500 keys, so a row is rescaled every few chunks), those of the odd heads
     fall (never rescaled), and both kinds sit in the same warp."""
-    nq, nkv, d, ps = 14, 2, 64, 16
+    nq, nkv, ps = 14, 2, 16
     qkv, kp, vp, table, tseq, pos = _attention_case(torch.bfloat16, nq, nkv, d, ps, lens, qlens, 0, 31)
     g = torch.Generator().manual_seed(32)
     u = torch.randn(d, generator=g)
