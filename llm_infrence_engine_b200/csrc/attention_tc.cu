@@ -351,11 +351,16 @@ __global__ void __launch_bounds__(THREADS, Sizes<D>::BLOCKS_PER_SM) attn_tc_pref
         const uint32_t o_addr = lane_base + S_BUFS * BN;
         // the scores of chunk c are waited for during chunk c - 1 (see below): only the first ones here
         bool ok = chunks == 0 || __all_sync(0xffffffffu, mbar_wait(s_ready, 0, abort_flag, p.error_flag, 15));
-        for (int c = 0; c < chunks && ok; ++c) {
+        // The row's scores of a chunk are asked for at the end of the chunk before it (they are ready by then, see below), so
+        // that their way from tensor memory lies under that chunk's fences, arrival and loop instead of at the head of the
+        // next one; only the first chunk's are asked for here.
+        uint32_t s[BN];
+        if (ok && chunks > 0) {
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-            uint32_t s[BN];
 #pragma unroll
-            for (int j = 0; j < BN; j += 16) tmem_ld16(lane_base + (c % S_BUFS) * BN + j, s + j);
+            for (int j = 0; j < BN; j += 16) tmem_ld16(lane_base + j, s + j);
+        }
+        for (int c = 0; c < chunks && ok; ++c) {
             asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
             const int key0 = lo_al + (chunk0 + c) * BN;
             // A chunk that every row of the tile sees in full needs no mask arithmetic (rows beyond the tile have zero
@@ -461,7 +466,14 @@ __global__ void __launch_bounds__(THREADS, Sizes<D>::BLOCKS_PER_SM) attn_tc_pref
             asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
             __syncwarp();  // every lane's writes (and reads of S) are done and fenced: one arrival speaks for the warp
             if (lane == 0) mbar_arrive(p_ready + (c & 1));
+            if (c + 1 < chunks) {
+                // S(c + 1) is complete (waited for above) and stays until S(c + 4) is made, which waits for P(c + 1)
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+#pragma unroll
+                for (int j = 0; j < BN; j += 16) tmem_ld16(lane_base + ((c + 1) % S_BUFS) * BN + j, s + j);
+            }
         }
+        asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");  // (a loop left early may have a read in flight)
         // the row's outputs, once: everything the tensor core has added up, relative to ref like the sum; 64 at a time
         if (ok && chunks > 0) {
             ok = __all_sync(0xffffffffu, mbar_wait(o_done, 0, abort_flag, p.error_flag, 16));

@@ -55,7 +55,9 @@ class CudaKernels:
         self.use_tc_attention = True   # prompt portions of head size 64 or 128: scores and outputs through tcgen05 and tensor memory
         self.cluster_merge = True      # decode attention: the key slices of a token form a cluster and merge in shared memory
         self.use_tc_gemm = True
-        self.use_cluster_gate_up = True  # ... by pairs of blocks that share their weight rows (TMA multicast within a cluster of two)
+        self.use_cluster_gate_up = False  # ... by pairs of blocks that share their weight rows (TMA multicast within a cluster of two)
+        self.use_pair_gate_up = True     # ... by pairs of multiprocessors on tiles of 256 rows (tcgen05 cta_group::2) ...
+        self.pair_gate_up_min_rows = 1024  # ... from this many rows on (measured: 3 to 8 % faster at 2,048 rows, 5 % slower at 512)
         self.use_tc_gate_up = True     # prompt portions: gate/up product with the activation as its epilogue, one tcgen05 kernel
         self.use_tc_qkv = True         # prompt portions, head size 64: q/k/v product with bias, rotation and cache write in one kernel
         self.tc_max_rows = 128        # batches up to this many rows take the small-batch tensor-core product
@@ -75,7 +77,7 @@ class CudaKernels:
         self._sms: dict = {}
         self.last_attention_plan = (1, False)   # (key slices, merged as a cluster) of the last tensor-core attention launch
         for fn in ("llmie_embed", "llmie_feed_tokens", "llmie_zero_fresh_state", "llmie_rope_tables", "llmie_add_rmsnorm", "llmie_rope_kv_write", "llmie_silu_mul",
-                   "llmie_gemm_simt", "llmie_gemm_tc", "llmie_gateup_silu_tc", "llmie_qkv_rope_tc", "llmie_add_into", "llmie_attn_plan", "llmie_attn_tc_plan", "llmie_paged_attention_mma", "llmie_paged_attention_mma_acc", "llmie_paged_attention_tc", "llmie_paged_attention_f32", "llmie_paged_attention_bf16", "llmie_argmax", "llmie_sample"):
+                   "llmie_gemm_simt", "llmie_gemm_tc", "llmie_gateup_silu_tc", "llmie_gateup_silu_tc_pair", "llmie_qkv_rope_tc", "llmie_add_into", "llmie_attn_plan", "llmie_attn_tc_plan", "llmie_paged_attention_mma", "llmie_paged_attention_mma_acc", "llmie_paged_attention_tc", "llmie_paged_attention_f32", "llmie_paged_attention_bf16", "llmie_argmax", "llmie_sample"):
             getattr(self.lib, fn).restype = ctypes.c_int
         try:   # an optional source file: the library also builds without it
             self._gate_up_cluster = self.lib.llmie_gateup_silu_tc_cluster
@@ -659,9 +661,12 @@ class CudaKernels:
                 and w_gate_up.is_contiguous() and w_gate_up.dtype == torch.bfloat16):
             I = w_gate_up.shape[0] // 2
             out = torch.empty((M, I), dtype=torch.bfloat16, device=x.device)
-            # pairs of blocks that share their weight rows by TMA multicast, where the library was built with that kernel (an
-            # optional source file) and there are at least two tiles of rows to pair
+            # three forms of the kernel: one block per tile of 128 rows; pairs of multiprocessors on tiles of 256 rows
+            # (cta_group::2), the default for long portions; pairs of blocks that share their weight rows by TMA multicast,
+            # where the library was built with that optional source file (off by default: measured no faster)
             fn = self._gate_up_cluster if (self.use_cluster_gate_up and M > 128) else None
+            if self.use_pair_gate_up and M >= self.pair_gate_up_min_rows:
+                fn = self.lib.llmie_gateup_silu_tc_pair
             fn = fn or self.lib.llmie_gateup_silu_tc
             self._check(fn(_ptr(x), _ptr(w_gate_up), _ptr(out), M, I, K_, self.num_sms, _ptr(self._errors(x.device)), self._stream()),
                         "gate_up_act (tcgen05)")

@@ -238,13 +238,15 @@ def test_silu_mul(K, dtype):
     (512, 64, 4736),       # 4 x 37 tiles of 128 columns are exactly one round of 148 blocks: the widest tile is chosen
     (512, 64, 3552),       # ... and here tiles of 96 columns are
 ])
-@pytest.mark.parametrize("cluster", [True, False])
-def test_gate_up_act_tcgen05(K, monkeypatch, cluster, M, H, I):
+@pytest.mark.parametrize("form", ["one block per tile", "pairs of blocks on tiles of 256 rows", "pairs of blocks that share weights by multicast"])
+def test_gate_up_act_tcgen05(K, monkeypatch, form, M, H, I):
     """The gate/up product of prompt portions with silu(gate) * up as its epilogue (one tcgen05 kernel, the float32 sums stay
-    in tensor memory) against product and activation one after the other in 32-bit."""
-    if cluster and K._gate_up_cluster is None:
+    in tensor memory) against product and activation one after the other in 32-bit; all three forms of the kernel."""
+    if form.endswith("multicast") and K._gate_up_cluster is None:
         pytest.skip("the library was built without the optional cluster kernel")
-    monkeypatch.setattr(K, "use_cluster_gate_up", cluster)
+    monkeypatch.setattr(K, "use_cluster_gate_up", form.endswith("multicast"))
+    monkeypatch.setattr(K, "use_pair_gate_up", form.startswith("pairs of blocks on"))
+    monkeypatch.setattr(K, "pair_gate_up_min_rows", 129)
     g = torch.Generator().manual_seed(60)
     x = torch.randn(M, H, generator=g).to(torch.bfloat16)
     w = (torch.randn(2 * I, H, generator=g) / math.sqrt(H) * 2).to(torch.bfloat16)
