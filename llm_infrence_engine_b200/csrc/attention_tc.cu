@@ -5,22 +5,24 @@
 // The keys go by in chunks of 64:
 //
 //   S  = Q K^T        tcgen05.mma, A = Q tile (shared memory, K-major), B = key chunk (K-major), D = S in tensor
-//                     memory [128 lanes x 64 columns, float32]; three S buffers, so the scores run up to two chunks
+//                     memory [128 lanes x 64 columns, float32]; three S buffers (two for heads of 128), so the scores run
 //                     ahead of the threads and never keep them waiting
 //   P  = softmax step every thread reads ITS row of S with tcgen05.ld (no shuffles: one thread, one row), masks, keeps
-//                     the running maximum and sum in 32-bit, and writes its row of P as bfloat16 into shared memory
-//                     in the swizzled K-major layout an A operand has
-//   O += P V          tcgen05.mma, A = P, B = value chunk as it lies in the cache ([key][dim]: MN-major), D = O in
-//                     tensor memory, accumulated over all chunks. P is exp2(score - reference) with a reference that
-//                     follows the row's running maximum lazily: only when the maximum has grown by more than 2^8 over
-//                     the reference does the thread scale its row of O (and its sum) down in tensor memory, between
+//                     the running maximum and sum in 32-bit, and writes its row of P as bfloat16 back into tensor memory
+//                     with tcgen05.st, over the scores it was made from (two values per column: 32 columns)
+//   O += P V          tcgen05.mma with A = P FROM TENSOR MEMORY, B = value chunk as it lies in the cache ([key][dim]:
+//                     MN-major), D = O in tensor memory, accumulated over all chunks. P is exp2(score - reference) with a
+//                     reference that follows the row's running maximum lazily: only when the maximum has grown by more than
+//                     2^8 over the reference does the thread scale its row of O (and its sum) down in tensor memory, between
 //                     two P V products. Softmax does not depend on the reference, P stays below 2^8, and after the
-//                     first chunks a row is hardly ever rescaled; O is read once, at the end. P has two buffers: the
-//                     threads go on to the scores of chunk c + 1 while the tensor core works on P V of chunk c
+//                     first chunks a row is hardly ever rescaled; O is read once, at the end. The MMAs of one thread run in
+//                     the order they were issued, so the scores that overwrite a buffer cannot overtake the P V product
+//                     that still reads P there
 //
 //   warps 0-3  the 128 row threads
-//   warp 4     producer: looks up the pages of a chunk in the block table and fetches them by TMA (one box per page
-//              and pool, 128-byte swizzle, no multicast) into two rings of STAGES buffers (keys, values) guarded by mbarriers
+//   warp 4     producer: looks up the pages of a chunk in the block table and fetches them by TMA (one box per page,
+//              pool and block of 64 dims, 128-byte swizzle, no multicast) into two rings of STAGES buffers (keys, values)
+//              guarded by mbarriers
 //   warp 5     one lane issues the MMAs and commits them to the barriers the other warps wait on
 //
 // A launch follows a plan made once per step on the device (attn_tc_plan_kernel): which pieces of work there are (a tile,
@@ -39,19 +41,18 @@
 namespace {
 
 constexpr int BM = 128, BN = 64, THREADS = 192;
-constexpr int P_BYTES = BM * BN * 2;
-constexpr int S_BUFS = 3;       // score buffers in tensor memory: the scores run up to two chunks ahead of the softmax
 // What depends on the head size D (64 or 128). Operands lie in shared memory in blocks of 64 elements (128 bytes, the width
 // of the swizzle) along D: a tile of Q or of keys is D / 64 such blocks one behind the other, a chunk of values likewise
-// (its blocks are the MMA's N there). Heads of 64: two blocks per SM. Heads of 128: one (192 KB of tiles, 320 columns of
-// tensor memory), with a deeper ring.
+// (its blocks are the MMA's N there). Two blocks share a multiprocessor: each has half of its tensor memory (256 columns:
+// the score buffers, in which P takes the place of the scores it was made from, and the outputs) and up to 113 KB of its
+// shared memory (the tile of Q and the two rings).
 template <int D> struct Sizes {
     static constexpr int ATOMS = D / 64;
-    static constexpr int STAGES = D == 64 ? 3 : 4;          // depth of the key ring and of the value ring
+    static constexpr int STAGES = D == 64 ? 4 : 2;          // depth of the key ring and of the value ring
+    static constexpr int S_BUFS = D == 64 ? 3 : 2;          // score buffers: the scores run S_BUFS - 1 chunks ahead of the softmax
     static constexpr int Q_BYTES = BM * D * 2, K_BYTES = BN * D * 2;
-    static constexpr int TMEM_COLS = D == 64 ? 256 : 512;   // S0 [0, 64), S1 [64, 128), S2 [128, 192), O [192, 192 + D)
-    static constexpr int BLOCKS_PER_SM = D == 64 ? 2 : 1;
-    static constexpr size_t SMEM = Q_BYTES + 2 * P_BYTES + 2 * STAGES * K_BYTES + 1024 + 256;
+    static constexpr int TMEM_COLS = 256;                   // S buffers of 64 columns, then O [S_BUFS * 64, S_BUFS * 64 + D)
+    static constexpr size_t SMEM = Q_BYTES + 2 * STAGES * K_BYTES + 1024 + 256;
 };
 constexpr float RESCALE_AFTER = 8.f;  // log2: a row's reference lags its running maximum by at most this much
 constexpr float LOG2E = 1.4426950408889634f;
@@ -120,20 +121,25 @@ __device__ __forceinline__ uint64_t umma_desc_mn(uint32_t smem_addr, uint32_t bl
     return d;
 }
 
+// D += A B with A in tensor memory (128 lanes x K 16-bit elements, two per column) and B in shared memory.
+__device__ __forceinline__ void umma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n" ::"r"(d_tmem),
+                 "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
 }
 
 template <int D>
-__global__ void __launch_bounds__(THREADS, Sizes<D>::BLOCKS_PER_SM) attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap tmap_k,
+__global__ void __launch_bounds__(THREADS, 2) attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap tmap_k,
                                                                                           const __grid_constant__ CUtensorMap tmap_v, const TcParams p) {
     constexpr int ATOMS = Sizes<D>::ATOMS, STAGES = Sizes<D>::STAGES, Q_BYTES = Sizes<D>::Q_BYTES, K_BYTES = Sizes<D>::K_BYTES;
-    constexpr int TMEM_COLS = Sizes<D>::TMEM_COLS;
+    constexpr int TMEM_COLS = Sizes<D>::TMEM_COLS, S_BUFS = Sizes<D>::S_BUFS;
     extern __shared__ unsigned char raw[];
     unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~(uintptr_t)1023);
     unsigned char* q_s = base;
-    unsigned char* p_s = base + Q_BYTES;
-    unsigned char* k_s = p_s + 2 * P_BYTES;      // [STAGES] key chunks; P has two buffers
+    unsigned char* k_s = base + Q_BYTES;           // [STAGES] key chunks
     unsigned char* v_s = k_s + STAGES * K_BYTES;  // [STAGES] value chunks
     // Keys and values have rings of their own: a key chunk is free again as soon as its scores are made, long before the
     // values of the same chunk have been used, so the next keys are on their way that much earlier.
@@ -317,10 +323,11 @@ __global__ void __launch_bounds__(THREADS, Sizes<D>::BLOCKS_PER_SM) attn_tc_pref
                 }
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
                 const uint32_t v_addr = smem_u32(v_s + (c % STAGES) * K_BYTES);
-                const uint64_t p_desc = umma_desc(smem_u32(p_s + (c & 1) * P_BYTES));
 #pragma unroll
-                for (int k = 0; k < BN / 16; ++k)  // 16 keys per step: 32 bytes along a row of P, 2048 bytes down the values
-                    umma_bf16(tmem + S_BUFS * BN, p_desc + 2 * k, umma_desc_mn(v_addr + k * 2048, BN * 128), idesc_o, (c > 0 || k > 0) ? 1u : 0u);
+                for (int k = 0; k < BN / 16; ++k) {  // 16 keys per step: 32 bytes along a row of P, 2048 bytes down the values
+                    // P lies where the chunk's scores lay: two bfloat16 per column, 8 columns per step
+                    umma_bf16_ts(tmem + S_BUFS * BN, tmem + (c % S_BUFS) * BN + 8 * k, umma_desc_mn(v_addr + k * 2048, BN * 128), idesc_o, (c > 0 || k > 0) ? 1u : 0u);
+                }
                 umma_commit(o_ready);
                 if (c == chunks - 1) umma_commit(o_done);
                 umma_commit(v_empty + c % STAGES);
@@ -444,8 +451,14 @@ __global__ void __launch_bounds__(THREADS, Sizes<D>::BLOCKS_PER_SM) attn_tc_pref
                 uint4 packed;
                 packed.x = pack_bf16x2(e[0], e[1]); packed.y = pack_bf16x2(e[2], e[3]);
                 packed.z = pack_bf16x2(e[4], e[5]); packed.w = pack_bf16x2(e[6], e[7]);
-                *reinterpret_cast<uint4*>(p_s + (c & 1) * P_BYTES + row * 128 + (((j >> 3) ^ (row & 7)) << 4)) = packed;
+                // (s[0 .. j + 7] are spent: the packed P of columns j .. j + 7 moves into s[j / 2 .. j / 2 + 3])
+                s[j / 2] = packed.x; s[j / 2 + 1] = packed.y; s[j / 2 + 2] = packed.z; s[j / 2 + 3] = packed.w;
             }
+            // P into tensor memory, over the scores it was made from (this thread has read them all): 32 columns of two
+            // bfloat16 each, the A operand of the P V product
+            tmem_st16(lane_base + (c % S_BUFS) * BN, s);
+            tmem_st16(lane_base + (c % S_BUFS) * BN + 16, s + 16);
+            asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
             float sum4[4];
             unpair(sum2[0], sum4[0], sum4[1]);
             unpair(sum2[1], sum4[2], sum4[3]);
@@ -462,7 +475,8 @@ __global__ void __launch_bounds__(THREADS, Sizes<D>::BLOCKS_PER_SM) attn_tc_pref
                         make_uint4(0, 0, 0, 0);
                 }
             }
-            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // the tensor core reads shared memory through the async proxy
+            if (key0 + BN > hi)
+                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // the zeros above: the tensor core reads shared memory through the async proxy
             asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
             __syncwarp();  // every lane's writes (and reads of S) are done and fenced: one arrival speaks for the warp
             if (lane == 0) mbar_arrive(p_ready + (c & 1));
@@ -481,7 +495,7 @@ __global__ void __launch_bounds__(THREADS, Sizes<D>::BLOCKS_PER_SM) attn_tc_pref
         }
         // one slice of several: (max, sum, outputs) of the row go to shared memory (every product has been waited for and no
         // copy is in flight: the tiles' space is free), from where the whole block hands them on below
-        float* fm = reinterpret_cast<float*>(p_s);
+        float* fm = reinterpret_cast<float*>(q_s);
         float* fl = fm + BM;
         float* fo = fl + BM;
         if (ok && num_splits > 1) {
@@ -537,7 +551,7 @@ __global__ void __launch_bounds__(THREADS, Sizes<D>::BLOCKS_PER_SM) attn_tc_pref
     __syncthreads();
     if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "n"(TMEM_COLS) : "memory");
     if (num_splits > 1 && !*abort_flag) {
-        float* fm = reinterpret_cast<float*>(p_s);
+        float* fm = reinterpret_cast<float*>(q_s);
         __shared__ int last_flag;
         finish_tile<D, BM, THREADS>(p, fm, fm + BM, fm + 2 * BM, num_splits, (size_t)job.w * p.nkv + kvh, (size_t)p.nkv, tile * p.nkv + kvh, kvh,
                                     split, n0, nrows, G, &last_flag, fm + 2 * BM + BM * D);

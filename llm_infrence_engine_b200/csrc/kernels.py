@@ -503,7 +503,7 @@ class CudaKernels:
         # chunks of its first ones. The plan (made on the device from the step's positions, once per step) cuts the keys of
         # long tiles into slices, as many pieces as fit on the device at once, and starts long pieces first.
         fixed = int(num_splits or 0)
-        capacity = max(1, (2 if head_dim == 64 else 1) * self.num_sms // num_kv_heads)  # heads of 128: one block per SM
+        capacity = max(1, 2 * self.num_sms // num_kv_heads)   # two blocks per SM
         # (tiles of up to 16 chunks are never cut: a slice costs about 8 chunks' time and is at least 8 chunks long)
         max_items = tiles * fixed if fixed else max(tiles, min(capacity, 16 * tiles)) if span > 16 * 64 else tiles
         key = ("tcgen05 attention plan", group, num_kv_heads, page_size, int(window), fixed)
