@@ -52,6 +52,7 @@ class CudaKernels:
         self._attn_counters: Optional[torch.Tensor] = None
         self._retired: list = []
         self.use_mma_attention = True
+        self.sample_single_block = False   # sampling by one block per row instead of a cluster per row (the slower, older kernel)
         self.use_tc_attention = True   # prompt portions of head size 64 or 128: scores and outputs through tcgen05 and tensor memory
         self.cluster_merge = True      # decode attention: the key slices of a token form a cluster and merge in shared memory
         self.use_tc_gemm = True
@@ -715,7 +716,7 @@ class CudaKernels:
                 raise KernelError(f"sample: {name} needs one value per row")
         out = torch.empty((M,), dtype=torch.int32, device=logits.device)
         self._check(self.lib.llmie_sample(_ptr(logits), _ptr(temperature), _ptr(top_k), _ptr(top_p), _ptr(uniform), _ptr(out), M, V,
-                                          self._stream()), "sample")
+                                          int(self.sample_single_block), self._stream()), "sample")
         return out
 
 

@@ -276,9 +276,14 @@ def test_argmax(K, V):
     assert got[1] == V // 2
 
 
-@pytest.mark.parametrize("V", [131, 320, 5000])
-def test_sample(K, V):
+@pytest.mark.parametrize("single_block", [False, True])
+@pytest.mark.parametrize("V", [131, 320, 5000, 20001, 40000, 151936])   # a cluster of 1, 1, 1, 2, 4 and 8 blocks per row
+def test_sample(K, monkeypatch, V, single_block):
+    """Both sampling kernels (a cluster of blocks per row with the row in shared memory; one block per row) draw the token the
+    plain sampler draws, for every combination of temperature, top-k and top-p and for draws at both ends of the range."""
     from plain_qwen2 import plain_draw, plain_logits_to_probs
+
+    monkeypatch.setattr(K, "sample_single_block", single_block)
 
     g = torch.Generator().manual_seed(7)
     rows = []
@@ -298,8 +303,10 @@ def test_sample(K, V):
             assert probs[got[i]] > 0 and edge < 1e-6, (i, rows[i], got[i], want)
 
 
-def test_sample_frequencies(K):
+@pytest.mark.parametrize("single_block", [False, True])
+def test_sample_frequencies(K, monkeypatch, single_block):
     """Empirical frequencies follow the distribution (the reference's test draws 4,000 times, tests/test_sampler.py:6-44)."""
+    monkeypatch.setattr(K, "sample_single_block", single_block)
     from plain_qwen2 import plain_logits_to_probs
     from llm_infrence_engine_b200.sampling import uniform_from
 

@@ -11,6 +11,7 @@ checks that a call beyond the array's size is refused. Collected last on purpose
 first failure has run everything else before.
 """
 import ctypes
+import gc
 import math
 
 import pytest
@@ -79,6 +80,7 @@ def test_no_alloc_entry_point_matches_ordinary_one(dtype):
         got = torch.full((N, nq * d), float("nan"), dtype=dtype, device="cuda")
         plain = TorchKernels().paged_attention(qkv.cpu(), kp.cpu(), vp.cpu(), table.cpu(), tseq.cpu(), pos.cpu(), nq, nkv, d, ps,
                                                1.0 / math.sqrt(d), window, max(lens))
+        gc.collect()   # (tensors of earlier tests that only a collection frees must not go while the call is measured)
         torch.cuda.synchronize()
         before = torch.cuda.memory_allocated()
         free_before = torch.cuda.mem_get_info()[0]   # the driver's own count: it would see an allocation by the library itself
