@@ -60,7 +60,8 @@ class CudaKernels:
         self.use_pair_gate_up = True     # ... by pairs of multiprocessors on tiles of 256 rows (tcgen05 cta_group::2) ...
         self.pair_gate_up_min_rows = 1024  # ... from this many rows on (measured: 3 to 8 % faster at 2,048 rows, 5 % slower at 512)
         self.use_tc_gate_up = True     # prompt portions: gate/up product with the activation as its epilogue, one tcgen05 kernel
-        self.use_tc_qkv = True         # prompt portions, head size 64: q/k/v product with bias, rotation and cache write in one kernel
+        self.use_tc_qkv = True         # prompt portions, head size 64: q/k/v product with bias, rotation and cache write in one kernel ...
+        self.tc_qkv_min_rows = 2048    # ... from this many rows on: below, the library product + the rotation kernel are 4 to 10 % of a step faster
         self.tc_max_rows = 128        # batches up to this many rows take the small-batch tensor-core product
         self.slice_keys = 1024         # generic attention: keys per slice, at fixed places of a request (a multiple of 32)
         self._acc: Optional[torch.Tensor] = None  # float32 zeros: split-K products add into it, their consumer clears it again
@@ -392,6 +393,7 @@ class CudaKernels:
         out_dtype = out_dtype or x.dtype
         M, K = x.shape
         if (self.use_tc_qkv and x.dtype == torch.bfloat16 and out_dtype == torch.bfloat16 and head_dim == 64 and M > self.tc_max_rows
+                and M >= self.tc_qkv_min_rows
                 and K % 8 == 0 and x.is_contiguous() and w.is_contiguous() and M <= 65535 * 128):
             self._need(w, "w", torch.bfloat16, 2)
             heads = num_heads + 2 * num_kv_heads

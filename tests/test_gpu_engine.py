@@ -379,9 +379,12 @@ def test_head_size_128(tmp_path, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_layer_sizes_of_the_half_billion_model(tmp_path, dtype):
+def test_layer_sizes_of_the_half_billion_model(tmp_path, monkeypatch, dtype):
     """Two layers with the real widths (hidden 896, 14 / 2 heads of 64, intermediate 4864, vocabulary 151936): the sizes
     at which serving runs the tensor-core kernels. Whole, cut into portions, decoded, mixed, and from CUDA graphs."""
+    from llm_infrence_engine_b200.csrc import get_kernels
+
+    monkeypatch.setattr(get_kernels(), "tc_qkv_min_rows", 129)   # the fused q/k/v kernel for these short prompts too
     from llm_infrence_engine_b200.config import EngineConfig
     from llm_infrence_engine_b200.engine import StepEntry, build_runner
     from llm_infrence_engine_b200.weights import write_random_model
@@ -475,14 +478,16 @@ def test_sharp_attention_shows_a_wrong_key(tmp_path, name):
 
 
 @pytest.mark.parametrize("which", ["D", "half_b"])
-def test_sharp_attention_in_bfloat16(tmp_path, which):
+def test_sharp_attention_in_bfloat16(tmp_path, monkeypatch, which):
     """The same in bfloat16, where the tensor-core kernels run (heads of 64): the tcgen05 attention and the fused q/k/v
     kernel for prompt portions, the small-batch products and the decode attention with its key slices, eagerly (two slices
     merged as a cluster once the context passes 1,024) and from graphs planned for 8,192 tokens (sixteen slices merged
     through scratch memory). The bound is twice what bfloat16 storage does to the plain model with these sharp weights;
     the unscaled model is many bounds away, so a key that is lost or misplaced cannot hide."""
+    from llm_infrence_engine_b200.csrc import get_kernels
     from llm_infrence_engine_b200.engine import TraceReplayer
 
+    monkeypatch.setattr(get_kernels(), "tc_qkv_min_rows", 129)   # the fused q/k/v kernel for these short prompts too
     n = 1200 if which == "D" else 150
     folder = _sharp_folder(tmp_path, which, 4.0, "bfloat16", None if which == "D" else HALF_B)
     cfg, w = plain_load(folder)

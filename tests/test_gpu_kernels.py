@@ -134,9 +134,10 @@ def test_rope_kv_write(K, dtype, nq, nkv, d, ps, bias):
     (513, 1536, 12, 2, 32, True, False),    # no cache write (a layer that reads another layer's cache)
     (200, 72, 1, 1, 16, True, True),        # three heads in one block of columns; two inner blocks, the second ragged
 ])
-def test_qkv_rope_tcgen05(K, N, H, nq, nkv, ps, bias, write):
+def test_qkv_rope_tcgen05(K, monkeypatch, N, H, nq, nkv, ps, bias, write):
     """The q/k/v product of prompt portions with bias, rotation and cache write in its epilogue (tcgen05, head size 64)
     against product, rotation and cache write one after the other in 32-bit. Some tokens have no slot (negative)."""
+    monkeypatch.setattr(K, "tc_qkv_min_rows", 129)   # (serving takes this kernel for long portions only)
     d = 64
     g = torch.Generator().manual_seed(13)
     x = torch.randn(N, H, generator=g).to(torch.bfloat16)
