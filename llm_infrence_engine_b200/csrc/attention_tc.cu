@@ -373,23 +373,28 @@ __global__ void __launch_bounds__(THREADS, 2) attn_tc_prefill_kernel(const __gri
             // A chunk that every row of the tile sees in full needs no mask arithmetic (rows beyond the tile have zero
             // queries and collect numbers nobody reads). The scale is positive: the maximum is taken over the raw scores.
             const bool interior = key0 >= lo && key0 + BN - 1 <= pos0 && (p.window <= 0 || key0 > hi - 1 - p.window);
+            if (__builtin_expect(!interior, 0)) {
+                // The columns this row sees are a run [first, last] of the chunk's 64: two words of bits say which, and a
+                // column outside is replaced (not multiplied: the score may be NaN) by -inf. Written small (three
+                // instructions a column) and marked unlikely: this code sits in the middle of the loop that every chunk runs,
+                // and what the loop's instructions occupy of the instruction cache shows in its time.
+                const int last = row_ok ? min(pos - key0, BN - 1) : -1;
+                const int first = p.window > 0 ? max(pos - p.window + 1 - key0, 0) : 0;
+                const uint64_t upto = last < 0 ? 0ull : (last >= 63 ? ~0ull : ((1ull << (last + 1)) - 1ull));
+                const uint64_t seen = first >= 64 ? 0ull : upto & ~((1ull << first) - 1ull);
+                const uint32_t seen_lo = (uint32_t)seen, seen_hi = (uint32_t)(seen >> 32);
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    if (!((seen_lo >> j) & 1u)) s[j] = 0xff800000u;
+                    if (!((seen_hi >> j) & 1u)) s[32 + j] = 0xff800000u;
+                }
+            }
             // four running maxima and sums each: a single chain of 64 dependent operations would cost its latency 64 times
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-            if (interior) {
 #pragma unroll
-                for (int j = 0; j < BN; j += 8) {
+            for (int j = 0; j < BN; j += 8) {
 #pragma unroll
-                    for (int k = 0; k < 4; ++k) mx4[k] = max3(mx4[k], __uint_as_float(s[j + k]), __uint_as_float(s[j + 4 + k]));
-                }
-            } else {
-#pragma unroll
-                for (int j = 0; j < BN; ++j) {
-                    const int key = key0 + j;
-                    const bool seen = row_ok && key <= pos && (p.window <= 0 || key > pos - p.window);
-                    const float x = seen ? __uint_as_float(s[j]) : -INFINITY;  // replaced, not multiplied: the score may be NaN
-                    s[j] = __float_as_uint(x);
-                    mx4[j & 3] = fmaxf(mx4[j & 3], x);
-                }
+                for (int k = 0; k < 4; ++k) mx4[k] = max3(mx4[k], __uint_as_float(s[j + k]), __uint_as_float(s[j + 4 + k]));
             }
             const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             m = fmaxf(m, mx * p.scale_log2);
@@ -411,24 +416,24 @@ __global__ void __launch_bounds__(THREADS, 2) attn_tc_prefill_kernel(const __gri
             // one phase behind. The scores themselves were made a chunk ago; this wait hardly ever waits.
             ok = __all_sync(0xffffffffu, mbar_wait(s_ready + (c + 1) % S_BUFS, ((c + 1) / S_BUFS) & 1, abort_flag, p.error_flag, 15));
             if (!ok) break;
-            if (__any_sync(0xffffffffu, rescale)) {
+            if (__builtin_expect(__any_sync(0xffffffffu, rescale), 0)) {
                 // O holds the products up to chunk c - 1 (there is one: a row's first chunk never gets here). The product
-                // of chunk c waits for this chunk's P, so nothing else touches O meanwhile.
+                // of chunk c waits for this chunk's P, so nothing else touches O meanwhile. (Sixteen columns at a time in a
+                // loop that is not unrolled: after the first chunks this hardly ever runs, and it should take little room
+                // in the loop that always does.)
                 ok = __all_sync(0xffffffffu, mbar_wait(o_ready, (c - 1) & 1, abort_flag, p.error_flag, 16));
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
 #pragma unroll 1
-                for (int part = 0; part < D; part += 64) {
-                    uint32_t v[64];
-#pragma unroll
-                    for (int j = 0; j < 64; j += 16) tmem_ld16(o_addr + part + j, v + j);
+                for (int part = 0; part < D; part += 16) {
+                    uint32_t v[16];
+                    tmem_ld16(o_addr + part, v);
                     asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
 #pragma unroll
-                    for (int i = 0; i < 64; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * corr);
-#pragma unroll
-                    for (int j = 0; j < 64; j += 16) tmem_st16(o_addr + part + j, v + j);
-                    asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
+                    for (int i = 0; i < 16; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * corr);
+                    tmem_st16(o_addr + part, v);
                 }
+                asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
             }
             // all 64 exponentials first, in place and independent of each other (the special-function unit is the narrow
             // place of this loop and must not wait for the sums and stores that follow)
