@@ -156,7 +156,7 @@ __global__ void __launch_bounds__(THREADS, 1) qkv_rope_tc_kernel(const __grid_co
         const bool ok = __all_sync(0xffffffffu, mbar_wait(done, 0, abort_flag, p.error_flag, 23));
         if (ok) {
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-#pragma unroll
+#pragma unroll 1   // (the two heads run the same code: half as much to fetch, and the second time it is there)
             for (int h = 0; h < BN / D; ++h) {
                 const int head = n0 / D + h;
                 uint32_t v[D];
