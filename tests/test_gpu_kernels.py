@@ -374,6 +374,8 @@ def test_paged_attention_tensor_cores(K, nq, nkv, d, ps, lens, qlens, window, sp
     (12, 2, 128, 16, [4100, 900], 13),
     (28, 4, 128, 32, [6000, 64], 8),
     (16, 1, 64, 64, [3000, 3000, 2000], 25),      # 16 heads on one key/value head, pages of 64
+    (14, 2, 64, 16, [300 + 7 * i for i in range(100)], None),   # more blocks than multiprocessors, no slices: blocks of four warps, two per SM
+    (12, 2, 128, 16, [90 + 11 * i for i in range(80)], 1),
 ])
 def test_decode_attention_with_many_key_slices(K, monkeypatch, cluster, nq, nkv, d, ps, lens, splits):
     """Decoded tokens at long contexts: the keys of a token are cut into slices that run as blocks of their own and are
