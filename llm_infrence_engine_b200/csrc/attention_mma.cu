@@ -786,17 +786,10 @@ int launch(const Params& p, int num_tiles, int decode_mode, cudaStream_t s) {
         // tiles of one token with up to 8 heads per group: the transposed form, which spends nothing on padding rows
         const bool t8 = p.tile_info == nullptr && p.nq / p.nkv <= 8;
         // Eight warps (192 KB of rings: one block per multiprocessor) walk a block's keys fastest. When there are more
-        // blocks than multiprocessors and nothing is cut into slices, blocks of four warps (96 KB: two per multiprocessor)
-        // run all at once instead of in two rounds of which the second is half empty (96 requests of 8,192 keys: 94 us in
-        // two rounds).
-        static int sms = 0;
-        if (!sms) {
-            int dev = 0;
-            if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) sms = 1 << 30;
-        }
-        const long long blocks = (long long)num_tiles * p.nkv;
-        const bool four = p.num_splits == 1 && blocks > sms && blocks <= 2LL * sms;
-        if (four) return t8 ? launch_decode<D, true, 4>(p, grid, s) : launch_decode<D, false, 4>(p, grid, s);
+        // blocks than multiprocessors and nothing is cut into slices, the caller may ask for blocks of four warps (96 KB:
+        // two per multiprocessor), which then run in fewer, fuller rounds (96 requests of 8,192 keys: 94 us in two rounds of
+        // eight-warp blocks, the second half empty; 74.5 us at once).
+        if (decode_mode == 2 && p.num_splits == 1) return t8 ? launch_decode<D, true, 4>(p, grid, s) : launch_decode<D, false, 4>(p, grid, s);
         return t8 ? launch_decode<D, true, 8>(p, grid, s) : launch_decode<D, false, 8>(p, grid, s);
     } else {
         constexpr size_t tiles = (size_t)(64 * D + 3 * 2 * 64 * D) * sizeof(bf16);
@@ -820,7 +813,8 @@ LLMIE_API int llmie_attn_plan(const int* seq_starts, int num_seqs, int tokens_pe
     return launch_kernel(attn_plan_kernel, dim3(1), dim3(32), 0, s, seq_starts, num_seqs, tokens_per_tile, tile_info, max_tiles);
 }
 
-// decode_mode 1: every tile has at most 16 rows (tokens * group). 0: at most 64 rows.
+// decode_mode 1 or 2: every tile has at most 16 rows (tokens * group); 2 asks for blocks of four warps instead of eight when
+// nothing is cut into slices. 0: at most 64 rows.
 // scratch_o / scratch_ml / counters are needed for num_splits > 1 (counters zeroed once; the kernel leaves them zero), unless
 // `cluster` is set (decode mode, at most 8 slices): the slices then form one thread-block cluster and merge in shared memory.
 static int run_mma(const bf16* q, int q_stride, const bf16* k_pool, const bf16* v_pool, const int* block_table,
@@ -866,8 +860,8 @@ LLMIE_API int llmie_paged_attention_mma_acc(const float* qkv_acc, int acc_stride
                                             const int* slots, bf16* k_pool, bf16* v_pool, const int* block_table, int max_blocks,
                                             const int* token_seq, const int* positions, int num_tokens, bf16* out, float* scratch_o,
                                             float* scratch_ml, int* counters, int nq, int nkv, int d, int page_size, float scale, int window,
-                                            int num_splits, int cluster, cudaStream_t s) {
+                                            int num_splits, int cluster, int four_warps, cudaStream_t s) {
     if (!qkv_acc) return LLMIE_ERR_BAD_ARGUMENT;
     return run_mma(nullptr, 8, k_pool, v_pool, block_table, max_blocks, token_seq, positions, nullptr, num_tokens, out, scratch_o, scratch_ml,
-                   counters, nq, nkv, d, page_size, scale, window, num_splits, 1, cluster, qkv_acc, acc_stride, bias, cos_t, sin_t, slots, s);
+                   counters, nq, nkv, d, page_size, scale, window, num_splits, four_warps ? 2 : 1, cluster, qkv_acc, acc_stride, bias, cos_t, sin_t, slots, s);
 }

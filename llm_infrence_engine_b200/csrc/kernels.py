@@ -78,6 +78,7 @@ class CudaKernels:
         self._retired_acc: list = []   # accumulation buffers that were outgrown: captured graphs may still add into and clear them
         self._sms: dict = {}
         self.last_attention_plan = (1, False)   # (key slices, merged as a cluster) of the last tensor-core attention launch
+        self._decode_four_warps = False         # the last decode plan asked for blocks of four warps
         for fn in ("llmie_embed", "llmie_feed_tokens", "llmie_zero_fresh_state", "llmie_rope_tables", "llmie_add_rmsnorm", "llmie_rope_kv_write", "llmie_silu_mul",
                    "llmie_gemm_simt", "llmie_gemm_tc", "llmie_gateup_silu_tc", "llmie_gateup_silu_tc_pair", "llmie_qkv_rope_tc", "llmie_add_into", "llmie_attn_plan", "llmie_attn_tc_plan", "llmie_paged_attention_mma", "llmie_paged_attention_mma_acc", "llmie_paged_attention_tc", "llmie_paged_attention_f32", "llmie_paged_attention_bf16", "llmie_argmax", "llmie_sample"):
             getattr(self.lib, fn).restype = ctypes.c_int
@@ -549,6 +550,15 @@ class CudaKernels:
                     rounds = -(-(-(-chunks // n)) // 8)
                     return rounds * 0.55 + -(-n // 12) * 1.0
                 num_splits = min(range(12, num_splits + 1), key=lambda n: (cost(n), -n))
+        # Without slices and with more blocks than multiprocessors, blocks of four warps (two per multiprocessor) run in fewer,
+        # fuller rounds than blocks of eight (one per multiprocessor) but walk their keys half as fast: what a round costs is a
+        # block's start and merge (about 4 us) plus its walk (0.55 us per round of its warps over a chunk each).
+        self._decode_four_warps = False
+        if decode and num_splits == 1:
+            blocks = max(1, tiles * num_kv_heads)
+            if blocks > self.num_sms:
+                walk = -(-chunks // 8) * 0.55
+                self._decode_four_warps = -(-blocks // (2 * self.num_sms)) * (4.0 + 2 * walk) < -(-blocks // self.num_sms) * (4.0 + walk)
         scratch_o = scratch_ml = counters = None
         # Up to four slices of a token merge as one thread-block cluster through shared memory (no trip through global
         # memory); more slices than that go through scratch and a counter: clusters of eight blocks of this size do not
@@ -586,7 +596,8 @@ class CudaKernels:
         self._check(self.lib.llmie_paged_attention_mma(
             _ptr(qkv), qkv.shape[1], _ptr(k_pool), _ptr(v_pool), _ptr(block_table), block_table.shape[1], _ptr(token_seq),
             _ptr(positions), _ptr(tile_info), tiles, _ptr(out), _ptr(scratch_o), _ptr(scratch_ml), _ptr(counters), num_heads,
-            num_kv_heads, head_dim, page_size, ctypes.c_float(scale), int(window), num_splits, int(decode), cluster, self._stream()),
+            num_kv_heads, head_dim, page_size, ctypes.c_float(scale), int(window), num_splits,
+            2 if (decode and self._decode_four_warps) else int(decode), cluster, self._stream()),
             "paged_attention (tensor cores)")
         return out
 
@@ -653,7 +664,7 @@ class CudaKernels:
                 _ptr(sums), width, _ptr(bias), _ptr(cos), _ptr(sin), _ptr(slot_mapping if write_kv else None), _ptr(k_pool), _ptr(v_pool),
                 _ptr(block_table), block_table.shape[1], _ptr(token_seq), _ptr(positions), M, _ptr(out), _ptr(scratch_o), _ptr(scratch_ml),
                 _ptr(counters), num_heads, num_kv_heads, head_dim, page_size, ctypes.c_float(scale), int(window), num_splits, cluster,
-                self._stream()), "qkv_attention (tensor cores)")
+                int(self._decode_four_warps), self._stream()), "qkv_attention (tensor cores)")
             self._dirty_qkv = sums
             return out
         qkv = self.qkv_rope(x, w, bias, cos, sin, slot_mapping, k_pool, v_pool, num_heads, num_kv_heads, head_dim, page_size, write_kv,
