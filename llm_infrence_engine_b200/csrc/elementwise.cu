@@ -1,6 +1,8 @@
 // Embedding, rotary tables, residual add + RMS norm, QKV bias + rotation + cache write, SiLU * up.
 // Every kernel takes its sizes as arguments; T is the compute dtype (float or bfloat16). The
 // residual stream, the norms' reductions, the rotation angles and the activation are 32-bit.
+#include <type_traits>
+
 #include "common.cuh"
 
 int llmie_pdl_flag = 0;
@@ -214,12 +216,72 @@ __global__ void rope_kv_write_kernel(TI* __restrict__ in, TO* __restrict__ out, 
     }
 }
 
+// The same for many tokens in bfloat16 (prompt portions after a library product): 16-byte accesses, eight pairs (j, j + d/2)
+// per thread and step, bias and angles as float4, and 128 threads per token so that twice as many tokens are in flight per
+// multiprocessor (the kernel is one trip to memory and back per block: what counts is how many blocks are there at once).
+__global__ void __launch_bounds__(128) rope_kv_write_bf16x8_kernel(const bf16* in, bf16* out, const float* __restrict__ bias,   // (out may be in)
+                                                                    const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                                                    const int* __restrict__ slots, bf16* __restrict__ k_pool, bf16* __restrict__ v_pool,
+                                                                    int nq, int nkv, int d, int page_size, int write_kv) {
+    pdl_trigger();
+    pdl_wait();
+    const int n = blockIdx.x;
+    const int half = d >> 1;
+    const int heads = nq + 2 * nkv;
+    const bf16* src = in + (size_t)n * heads * d;
+    bf16* row = out + (size_t)n * heads * d;
+    const float* c = cos_t + (size_t)n * half;
+    const float* sn = sin_t + (size_t)n * half;
+    const int slot = write_kv ? slots[n] : -1;
+    const int page = slot >= 0 ? slot / page_size : 0, off = slot >= 0 ? slot % page_size : 0;
+    for (int i = threadIdx.x * 8; i < heads * half; i += blockDim.x * 8) {
+        const int h = i / half, j = i % half;
+        const int a = h * d + j, b = a + half;
+        float x1[8], x2[8];
+        load4(src + a, x1); load4(src + a + 4, x1 + 4);
+        load4(src + b, x2); load4(src + b + 4, x2 + 4);
+        if (bias) {
+            float t[8];
+            load4(bias + a, t); load4(bias + a + 4, t + 4);
+#pragma unroll
+            for (int v = 0; v < 8; ++v) x1[v] += t[v];
+            load4(bias + b, t); load4(bias + b + 4, t + 4);
+#pragma unroll
+            for (int v = 0; v < 8; ++v) x2[v] += t[v];
+        }
+        if (h < nq + nkv) {
+            float cs[8], ss[8];
+            load4(c + j, cs); load4(c + j + 4, cs + 4);
+            load4(sn + j, ss); load4(sn + j + 4, ss + 4);
+#pragma unroll
+            for (int v = 0; v < 8; ++v) {
+                const float y1 = x1[v] * cs[v] - x2[v] * ss[v], y2 = x2[v] * cs[v] + x1[v] * ss[v];
+                x1[v] = y1; x2[v] = y2;
+            }
+        }
+        store4(row + a, x1); store4(row + a + 4, x1 + 4);
+        store4(row + b, x2); store4(row + b + 4, x2 + 4);
+        if (slot >= 0 && h >= nq) {
+            const int kvh = h < nq + nkv ? h - nq : h - nq - nkv;
+            bf16* dst = (h < nq + nkv ? k_pool : v_pool) + (((size_t)page * nkv + kvh) * page_size + off) * d;
+            store4(dst + j, x1); store4(dst + j + 4, x1 + 4);
+            store4(dst + j + half, x2); store4(dst + j + half + 4, x2 + 4);
+        }
+    }
+}
+
 template <typename TI, typename TO>
 static int launch_rope(TI* in, TO* out, const float* bias, const float* cos_t, const float* sin_t, const int* slots, TO* k_pool, TO* v_pool,
                        int N, int nq, int nkv, int d, int page_size, int write_kv, int clear_in, cudaStream_t s) {
     const int work = (nq + 2 * nkv) * (d / 2);
     const bool vec = d % 8 == 0 && ((uintptr_t)in % 16 == 0) && ((uintptr_t)out % 16 == 0) && ((uintptr_t)k_pool % 16 == 0) &&
                      ((uintptr_t)v_pool % 16 == 0);
+    if constexpr (std::is_same<TI, bf16>::value && std::is_same<TO, bf16>::value) {
+        // (8-byte halves of 16-byte pieces: the same alignment rule as below, d a multiple of 16)
+        if (vec && d % 16 == 0 && N >= 64 && !clear_in && ((uintptr_t)bias % 16 == 0) && ((uintptr_t)cos_t % 16 == 0) && ((uintptr_t)sin_t % 16 == 0))
+            return launch_kernel(rope_kv_write_bf16x8_kernel, dim3(N), dim3(128), 0, s, (const bf16*)in, out, bias, cos_t, sin_t, slots, k_pool, v_pool,
+                                 nq, nkv, d, page_size, write_kv);
+    }
     if (vec) {
         const int threads = work / 4 >= 256 ? 256 : 128;
         return launch_kernel(rope_kv_write_kernel<TI, TO, 4>, dim3(N), dim3(threads), 0, s, in, out, bias, cos_t, sin_t, slots, k_pool, v_pool,

@@ -102,10 +102,12 @@ def test_linear_float32_is_true_32bit(K):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("nq,nkv,d,ps,bias", [(4, 2, 16, 16, True), (3, 1, 32, 8, True), (6, 3, 48, 16, False), (14, 2, 64, 16, True)])
-def test_rope_kv_write(K, dtype, nq, nkv, d, ps, bias):
+@pytest.mark.parametrize("N", [11, 200])   # (many tokens in bfloat16 take a kernel of their own with wider accesses)
+@pytest.mark.parametrize("nq,nkv,d,ps,bias", [(4, 2, 16, 16, True), (3, 1, 32, 8, True), (6, 3, 48, 16, False), (14, 2, 64, 16, True),
+                                              (12, 2, 128, 16, True), (5, 1, 24, 16, True)])
+def test_rope_kv_write(K, dtype, N, nq, nkv, d, ps, bias):
     g = torch.Generator().manual_seed(3)
-    N, pages = 11, 9
+    pages = -(-N // ps) + 8
     qkv = torch.randn(N, (nq + 2 * nkv) * d, generator=g).to(dtype)
     b = torch.randn((nq + 2 * nkv) * d, generator=g) if bias else None
     pos = torch.randint(0, 500, (N,), generator=g).int()
