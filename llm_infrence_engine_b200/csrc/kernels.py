@@ -80,13 +80,17 @@ class CudaKernels:
         self.last_attention_plan = (1, False)   # (key slices, merged as a cluster) of the last tensor-core attention launch
         self._decode_four_warps = False         # the last decode plan asked for blocks of four warps
         for fn in ("llmie_embed", "llmie_feed_tokens", "llmie_zero_fresh_state", "llmie_rope_tables", "llmie_add_rmsnorm", "llmie_rope_kv_write", "llmie_silu_mul",
-                   "llmie_gemm_simt", "llmie_gemm_tc", "llmie_gateup_silu_tc", "llmie_gateup_silu_tc_pair", "llmie_qkv_rope_tc", "llmie_add_into", "llmie_attn_plan", "llmie_attn_tc_plan", "llmie_paged_attention_mma", "llmie_paged_attention_mma_acc", "llmie_paged_attention_tc", "llmie_paged_attention_f32", "llmie_paged_attention_bf16", "llmie_argmax", "llmie_sample"):
+                   "llmie_gemm_simt", "llmie_gemm_tc", "llmie_gateup_silu_tc", "llmie_qkv_rope_tc", "llmie_add_into", "llmie_attn_plan", "llmie_attn_tc_plan", "llmie_paged_attention_mma", "llmie_paged_attention_mma_acc", "llmie_paged_attention_tc", "llmie_paged_attention_f32", "llmie_paged_attention_bf16", "llmie_argmax", "llmie_sample"):
             getattr(self.lib, fn).restype = ctypes.c_int
-        try:   # an optional source file: the library also builds without it
-            self._gate_up_cluster = self.lib.llmie_gateup_silu_tc_cluster
-            self._gate_up_cluster.restype = ctypes.c_int
-        except AttributeError:
-            self._gate_up_cluster = None
+        # two forms of the gate/up kernel live in source files of their own, and the library also builds without them
+        self._gate_up_cluster = self._gate_up_pair = None
+        for attr, name in (("_gate_up_cluster", "llmie_gateup_silu_tc_cluster"), ("_gate_up_pair", "llmie_gateup_silu_tc_pair")):
+            try:
+                fn = getattr(self.lib, name)
+                fn.restype = ctypes.c_int
+                setattr(self, attr, fn)
+            except AttributeError:
+                pass
         # kernels of a step overlap their set-up with the tail of the kernel before (programmatic dependent launch)
         self.lib.llmie_set_pdl(0 if os.environ.get("LLMIE_PDL", "1") == "0" else 1)
 
@@ -687,8 +691,8 @@ class CudaKernels:
             # (cta_group::2), the default for long portions; pairs of blocks that share their weight rows by TMA multicast,
             # where the library was built with that optional source file (off by default: measured no faster)
             fn = self._gate_up_cluster if (self.use_cluster_gate_up and M > 128) else None
-            if self.use_pair_gate_up and M >= self.pair_gate_up_min_rows:
-                fn = self.lib.llmie_gateup_silu_tc_pair
+            if self.use_pair_gate_up and self._gate_up_pair is not None and M >= self.pair_gate_up_min_rows:
+                fn = self._gate_up_pair
             fn = fn or self.lib.llmie_gateup_silu_tc
             self._check(fn(_ptr(x), _ptr(w_gate_up), _ptr(out), M, I, K_, self.num_sms, _ptr(self._errors(x.device)), self._stream()),
                         "gate_up_act (tcgen05)")

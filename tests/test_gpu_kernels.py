@@ -245,8 +245,8 @@ def test_silu_mul(K, dtype):
 def test_gate_up_act_tcgen05(K, monkeypatch, form, M, H, I):
     """The gate/up product of prompt portions with silu(gate) * up as its epilogue (one tcgen05 kernel, the float32 sums stay
     in tensor memory) against product and activation one after the other in 32-bit; all three forms of the kernel."""
-    if form.endswith("multicast") and K._gate_up_cluster is None:
-        pytest.skip("the library was built without the optional cluster kernel")
+    if (form.endswith("multicast") and K._gate_up_cluster is None) or (form.startswith("pairs of blocks on") and K._gate_up_pair is None):
+        pytest.skip("the library was built without this optional kernel")
     monkeypatch.setattr(K, "use_cluster_gate_up", form.endswith("multicast"))
     monkeypatch.setattr(K, "use_pair_gate_up", form.startswith("pairs of blocks on"))
     monkeypatch.setattr(K, "pair_gate_up_min_rows", 129)
