@@ -56,7 +56,7 @@ def test_rope_tables(K, half, theta):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("N,H,eps", [(5, 64, 1e-6), (3, 200, 1e-5), (2, 4100, 3e-6), (9, 896, 1e-6),
-                                     (70, 896, 1e-6), (40, 1536, 1e-5)])
+                                     (70, 896, 1e-6), (40, 1536, 1e-5), (200, 1536, 1e-5), (100, 72, 1e-5), (64, 4104, 1e-6)])
 def test_add_rmsnorm(K, dtype, N, H, eps):
     g = torch.Generator().manual_seed(1)
     res = torch.randn(N, H, generator=g) * 3
