@@ -148,7 +148,7 @@ __global__ void __launch_bounds__(THREADS, 2) attn_tc_prefill_kernel(const __gri
     uint64_t* v_full = k_empty + STAGES;
     uint64_t* v_empty = v_full + STAGES;
     uint64_t* s_ready = v_empty + STAGES;  // [S_BUFS]
-    uint64_t* p_ready = s_ready + S_BUFS;     // [2]: the row threads may finish chunk c + 1 before the P V product of chunk c has begun
+    uint64_t* p_ready = s_ready + S_BUFS;     // [2], taken in turn: the row threads may hand over P(c + 1) before the MMA thread has looked at P(c)'s barrier
     uint64_t* o_ready = p_ready + 2;     // completes once per chunk, after its P V product
     uint64_t* o_done = o_ready + 1;      // completes once, after the last chunk's P V product
     uint64_t* q_ready = o_done + 1;
@@ -278,10 +278,11 @@ __global__ void __launch_bounds__(THREADS, 2) attn_tc_prefill_kernel(const __gri
                 umma_commit(s_ready + c % S_BUFS);
                 umma_commit(k_empty + c % STAGES);
             };
-            // Scores are made as early as their keys and a buffer allow: S(n) goes into the buffer that S(n - S_BUFS) left, and
-            // the rows have read that one by the time they hand over P(n - S_BUFS). After the last chunk comes one commit
-            // without a product: the rows wait for "S(c + 1)" before they overwrite P(c - 2), because a commit completes only
-            // after everything this thread issued before it, and P V of chunk c - 2 is among that.
+            // Scores are made as early as their keys and a buffer allow: S(n) goes into the buffer in which P(n - S_BUFS) took the
+            // place of S(n - S_BUFS); the product that reads that P was issued by this thread before, and a thread's MMAs run in
+            // the order of their issue. After the last chunk comes one commit without a product: the rows wait for "S(c + 1)"
+            // in every chunk (it tells them that the P V products up to chunk c - S_BUFS + 1 are over: a commit completes only
+            // after everything this thread issued before it).
             int s_next = 0;
             auto more_scores = [&](int upto, bool wait) {
                 while (s_next <= upto && s_next <= chunks) {
@@ -410,10 +411,11 @@ __global__ void __launch_bounds__(THREADS, 2) attn_tc_prefill_kernel(const __gri
                 rescale = true;
             }
             const float use = ref == -INFINITY ? 0.f : ref;
-            // The scores of the next chunk (after the last chunk: a commit that stands for them) were issued after the P V
-            // product of chunk c - 2, and a commit completes only after everything issued before it. So from here on
-            // that product is over: its P buffer may be overwritten below, and the barrier of the P V products is at most
-            // one phase behind. The scores themselves were made a chunk ago; this wait hardly ever waits.
+            // The scores of the next chunk (after the last chunk: a commit that stands for them): they are asked for at the end
+            // of this chunk. They were issued after the P V product of chunk c - 2 (c - 1 with two score buffers), and a commit
+            // completes only after everything issued before it: from here on the barrier of the P V products is at most one
+            // phase behind, which the wait before a rescaling relies on. The scores themselves were made a chunk ago; this
+            // wait hardly ever waits.
             ok = __all_sync(0xffffffffu, mbar_wait(s_ready + (c + 1) % S_BUFS, ((c + 1) / S_BUFS) & 1, abort_flag, p.error_flag, 15));
             if (!ok) break;
             if (__builtin_expect(__any_sync(0xffffffffu, rescale), 0)) {
